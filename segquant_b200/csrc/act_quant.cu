@@ -1,0 +1,316 @@
+// Activation quantise kernels (HBM-bound).
+//
+// One pass over x: 128-bit loads, per-K-segment (or per-token) scale, int8 / e4m3 bytes out
+// through 128-bit stores.  Replaces real_quantize_scaled_kernel / real_quantize_dual_scaled_kernel
+// of segquant/src/real_quant/quantizer.cuh:159-206 (4 scalar elements per thread, a div/mod per
+// element) and the `.contiguous()` segment copy in segquant/optimum/optimizer.py:105.
+//
+// Work split: one warp walks one row; lane l takes the 16-element chunks l, l+32, ... so every
+// store instruction of a warp writes 512 contiguous bytes.
+#include "common.cuh"
+
+namespace sq {
+
+struct ActQuantParams {
+    const void* x;
+    const float* sx;
+    const float* sx_neg;
+    const float* smooth;
+    uint8_t* xq;
+    uint8_t* xq_neg;
+    float* sx_out;      // dynamic only
+    float* sx_neg_out;  // dynamic only
+    long long batch, M, K;
+    long long x_batch_stride, x_row_stride;
+    long long sx_batch_stride, sx_seg_stride, sx_row_stride;
+    long long xq_batch_stride, xq_row_stride;
+    int num_segs;
+    int uniform_seg;  // >0: every segment has this length
+    int seg_bounds[SQ_MAX_SEGS + 1];
+};
+
+__device__ __forceinline__ int find_segment(const ActQuantParams& p, int k) {
+    if (p.uniform_seg > 0) return k / p.uniform_seg;
+    int s = 0;
+    while (s + 1 < p.num_segs && k >= p.seg_bounds[s + 1]) ++s;
+    return s;
+}
+
+template <int OUT>
+__device__ __forceinline__ uint4 pack16(const float (&v)[16]) {
+    uint32_t w[4];
+    if constexpr (OUT == SQ_Q_INT8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = quant_int8(v[4 * i]) | (quant_int8(v[4 * i + 1]) << 8) | (quant_int8(v[4 * i + 2]) << 16) |
+                   (quant_int8(v[4 * i + 3]) << 24);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = quant_e4m3x2(v[4 * i], v[4 * i + 1]) | (quant_e4m3x2(v[4 * i + 2], v[4 * i + 3]) << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// DualScale: element >= 0 -> positive tensor (other side gets quantise(0) = byte 0), else the
+// negative tensor (quantizer.cuh:178-206).  The byte of a quantised +0.0f is 0 in both formats.
+template <int OUT>
+__device__ __forceinline__ void pack16_dual(const float (&x)[16], float sp, float sn, uint4& outp, uint4& outn) {
+    uint32_t wp[4] = {0, 0, 0, 0}, wn[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const bool pos = x[i] >= 0.0f;
+        const float scaled = x[i] * (pos ? sp : sn);
+        const uint32_t q = (OUT == SQ_Q_INT8) ? quant_int8(scaled) : quant_e4m3(scaled);
+        const uint32_t sh = (i & 3) * 8;
+        wp[i >> 2] |= (pos ? q : 0u) << sh;
+        wn[i >> 2] |= (pos ? 0u : q) << sh;
+    }
+    outp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+    outn = make_uint4(wn[0], wn[1], wn[2], wn[3]);
+}
+
+template <typename T, int OUT, bool DUAL, bool SMOOTH>
+__global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const long long rows = p.batch * p.M;
+    const int kch = static_cast<int>(p.K >> 4);
+    const T* __restrict__ x = static_cast<const T*>(p.x);
+
+    for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * warps_per_cta) {
+        const long long b = row / p.M;
+        const long long r = row - b * p.M;
+        const T* xr = x + b * p.x_batch_stride + r * p.x_row_stride;
+        const float* sxr = p.sx + b * p.sx_batch_stride + r * p.sx_row_stride;
+        const float* sxnr = DUAL ? p.sx_neg + b * p.sx_batch_stride + r * p.sx_row_stride : nullptr;
+        uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
+        uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
+
+#pragma unroll 2
+        for (int c = lane; c < kch; c += 32) {
+            const int k = c << 4;
+            float v[16];
+            load16<T>(xr + k, v);
+            if constexpr (SMOOTH) {
+                float sm[16];
+                load16<float>(p.smooth + k, sm);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = v[i] / sm[i];
+            }
+            const int s = find_segment(p, k);
+            const float sc = __ldg(sxr + s * p.sx_seg_stride);
+            if constexpr (!DUAL) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] *= sc;
+                *reinterpret_cast<uint4*>(qr + k) = pack16<OUT>(v);
+            } else {
+                const float scn = __ldg(sxnr + s * p.sx_seg_stride);
+                uint4 op, on;
+                pack16_dual<OUT>(v, sc, scn, op, on);
+                *reinterpret_cast<uint4*>(qr + k) = op;
+                *reinterpret_cast<uint4*>(qnr + k) = on;
+            }
+        }
+    }
+}
+
+// Dynamic per-token scales: one warp per (row, segment).  Pass 1 reduces |x| (or the positive and
+// negative extremes) with warp shuffles, pass 2 re-reads the row segment (at most 24 KB, an L1/L2
+// hit) and quantises.  The scale is rounded to the dtype of x because the reference computes
+// qmax / amax on a tensor of that dtype (segquant/quantizers/quantizer.py:209-217, :187-203).
+template <typename T, int OUT, bool DUAL>
+__global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_constant__ ActQuantParams p) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const long long rows = p.batch * p.M;
+    const long long items = rows * p.num_segs;
+    const T* __restrict__ x = static_cast<const T*>(p.x);
+    constexpr float kEps = 1.0f / 16777216.0f;
+    constexpr float kQmax = (OUT == SQ_Q_INT8) ? 127.0f : 448.0f;
+    constexpr float kQminAbs = (OUT == SQ_Q_INT8) ? 128.0f : 448.0f;
+
+    for (long long item = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); item < items;
+         item += static_cast<long long>(gridDim.x) * warps_per_cta) {
+        const long long row = item / p.num_segs;
+        const int s = static_cast<int>(item - row * p.num_segs);
+        const long long b = row / p.M;
+        const long long r = row - b * p.M;
+        const int k0 = p.seg_bounds[s], k1 = p.seg_bounds[s + 1];
+        const T* xr = x + b * p.x_batch_stride + r * p.x_row_stride;
+        uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
+        uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
+
+        float amax = 0.0f, nmax = 0.0f;
+        for (int k = k0 + (lane << 4); k < k1; k += 512) {
+            float v[16];
+            load16<T>(xr + k, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if constexpr (DUAL) {
+                    amax = fmaxf(amax, v[i]);    // max over x > 0 of x (0 if none)
+                    nmax = fmaxf(nmax, -v[i]);   // max over x < 0 of |x|
+                } else {
+                    amax = fmaxf(amax, fabsf(v[i]));
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if constexpr (DUAL) nmax = fmaxf(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+        }
+        const float sc = to_float<T>(from_float<T>(kQmax / fmaxf(amax, kEps)));
+        float scn = 0.0f;
+        if constexpr (DUAL) scn = to_float<T>(from_float<T>(kQminAbs / fmaxf(nmax, kEps)));
+        if (lane == 0) {
+            p.sx_out[(b * p.num_segs + s) * p.M + r] = sc;
+            if constexpr (DUAL) p.sx_neg_out[(b * p.num_segs + s) * p.M + r] = scn;
+        }
+        for (int k = k0 + (lane << 4); k < k1; k += 512) {
+            float v[16];
+            load16<T>(xr + k, v);
+            if constexpr (!DUAL) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] *= sc;
+                *reinterpret_cast<uint4*>(qr + k) = pack16<OUT>(v);
+            } else {
+                uint4 op, on;
+                pack16_dual<OUT>(v, sc, scn, op, on);
+                *reinterpret_cast<uint4*>(qr + k) = op;
+                *reinterpret_cast<uint4*>(qnr + k) = on;
+            }
+        }
+    }
+}
+
+static int validate(const sq_act_quant_args* a, bool dynamic) {
+    SQ_REQUIRE(a != nullptr, SQ_ERR_INVALID_ARG, "sq_quantize_act: args is NULL");
+    SQ_REQUIRE(a->x_dev && a->xq_dev, SQ_ERR_INVALID_ARG, "sq_quantize_act: x_dev / xq_dev is NULL");
+    SQ_REQUIRE(dynamic || a->sx_dev, SQ_ERR_INVALID_ARG, "sq_quantize_act: sx_dev is NULL");
+    SQ_REQUIRE(a->batch >= 0 && a->M >= 0 && a->K >= 0, SQ_ERR_INVALID_ARG, "sq_quantize_act: negative size");
+    SQ_REQUIRE(a->x_dtype == SQ_F32 || a->x_dtype == SQ_F16 || a->x_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
+               "sq_quantize_act: unknown x_dtype %d", a->x_dtype);
+    SQ_REQUIRE(a->out_kind == SQ_Q_INT8 || a->out_kind == SQ_Q_E4M3, SQ_ERR_UNSUPPORTED,
+               "sq_quantize_act: activations quantise to int8 or e4m3 only (got kind %d)", a->out_kind);
+    SQ_REQUIRE(a->num_segs >= 1 && a->num_segs <= SQ_MAX_SEGS, SQ_ERR_INVALID_ARG,
+               "sq_quantize_act: num_segs %d outside [1, %d]", a->num_segs, SQ_MAX_SEGS);
+    SQ_REQUIRE(a->K % 16 == 0, SQ_ERR_ALIGNMENT, "sq_quantize_act: K (%lld) must be divisible by 16",
+               static_cast<long long>(a->K));
+    SQ_REQUIRE(a->K < (1ll << 30), SQ_ERR_TOO_LARGE, "sq_quantize_act: K too large");
+    SQ_REQUIRE(a->seg_bounds[0] == 0 && a->seg_bounds[a->num_segs] == a->K, SQ_ERR_INVALID_ARG,
+               "sq_quantize_act: seg_bounds must run from 0 to K");
+    for (int s = 0; s < a->num_segs; ++s) {
+        SQ_REQUIRE(a->seg_bounds[s + 1] > a->seg_bounds[s] || a->K == 0, SQ_ERR_INVALID_ARG,
+                   "sq_quantize_act: seg_bounds not increasing at %d", s);
+        SQ_REQUIRE(a->seg_bounds[s + 1] % 16 == 0, SQ_ERR_ALIGNMENT,
+                   "sq_quantize_act: segment bound %d must be divisible by 16", a->seg_bounds[s + 1]);
+    }
+    const int esz = a->x_dtype == SQ_F32 ? 4 : 2;
+    SQ_REQUIRE((reinterpret_cast<uintptr_t>(a->x_dev) % 16) == 0 && (a->x_row_stride * esz) % 16 == 0 &&
+                   (a->x_batch_stride * esz) % 16 == 0,
+               SQ_ERR_ALIGNMENT, "sq_quantize_act: x pointer and strides must be 16-byte aligned");
+    SQ_REQUIRE((reinterpret_cast<uintptr_t>(a->xq_dev) % 16) == 0 && a->xq_row_stride % 16 == 0 &&
+                   a->xq_batch_stride % 16 == 0,
+               SQ_ERR_ALIGNMENT, "sq_quantize_act: xq pointer and strides must be 16-byte aligned");
+    if (a->xq_neg_dev) {
+        SQ_REQUIRE((reinterpret_cast<uintptr_t>(a->xq_neg_dev) % 16) == 0, SQ_ERR_ALIGNMENT,
+                   "sq_quantize_act: xq_neg pointer must be 16-byte aligned");
+        SQ_REQUIRE(dynamic || a->sx_neg_dev, SQ_ERR_INVALID_ARG, "sq_quantize_act: DualScale needs sx_neg_dev");
+    }
+    if (a->smooth_dev)
+        SQ_REQUIRE((reinterpret_cast<uintptr_t>(a->smooth_dev) % 16) == 0, SQ_ERR_ALIGNMENT,
+                   "sq_quantize_act: smooth pointer must be 16-byte aligned");
+    return SQ_OK;
+}
+
+static void fill_params(const sq_act_quant_args* a, ActQuantParams& p) {
+    p.x = a->x_dev; p.sx = a->sx_dev; p.sx_neg = a->sx_neg_dev; p.smooth = a->smooth_dev;
+    p.xq = static_cast<uint8_t*>(a->xq_dev); p.xq_neg = static_cast<uint8_t*>(a->xq_neg_dev);
+    p.sx_out = nullptr; p.sx_neg_out = nullptr;
+    p.batch = a->batch; p.M = a->M; p.K = a->K;
+    p.x_batch_stride = a->x_batch_stride; p.x_row_stride = a->x_row_stride;
+    p.sx_batch_stride = a->sx_batch_stride; p.sx_seg_stride = a->sx_seg_stride; p.sx_row_stride = a->sx_row_stride;
+    p.xq_batch_stride = a->xq_batch_stride; p.xq_row_stride = a->xq_row_stride;
+    p.num_segs = a->num_segs;
+    for (int s = 0; s <= SQ_MAX_SEGS; ++s) p.seg_bounds[s] = s <= a->num_segs ? a->seg_bounds[s] : 0;
+    int len = a->seg_bounds[1] - a->seg_bounds[0];
+    bool uniform = len > 0;
+    for (int s = 1; s < a->num_segs && uniform; ++s) uniform = (a->seg_bounds[s + 1] - a->seg_bounds[s]) == len;
+    p.uniform_seg = uniform ? len : 0;
+}
+
+static int grid_for(long long warp_items) {
+    long long ctas = (warp_items + 7) / 8;
+    const long long cap = static_cast<long long>(kNumSMs) * 8;  // 8 CTAs of 256 threads per SM
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    return static_cast<int>(ctas);
+}
+
+template <typename T, int OUT>
+static void launch_static(const ActQuantParams& p, bool dual, bool smooth, cudaStream_t st) {
+    const int grid = grid_for(p.batch * p.M);
+    if (dual) {
+        if (smooth) act_quant_kernel<T, OUT, true, true><<<grid, 256, 0, st>>>(p);
+        else act_quant_kernel<T, OUT, true, false><<<grid, 256, 0, st>>>(p);
+    } else {
+        if (smooth) act_quant_kernel<T, OUT, false, true><<<grid, 256, 0, st>>>(p);
+        else act_quant_kernel<T, OUT, false, false><<<grid, 256, 0, st>>>(p);
+    }
+}
+
+template <typename T, int OUT>
+static void launch_dynamic(const ActQuantParams& p, bool dual, cudaStream_t st) {
+    const int grid = grid_for(p.batch * p.M * p.num_segs);
+    if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 256, 0, st>>>(p);
+    else act_quant_dynamic_kernel<T, OUT, false><<<grid, 256, 0, st>>>(p);
+}
+
+int quantize_act(const sq_act_quant_args* a, cudaStream_t st) {
+    int rc = validate(a, false);
+    if (rc != SQ_OK) return rc;
+    if (a->batch * a->M * a->K == 0) return SQ_OK;
+    ActQuantParams p;
+    fill_params(a, p);
+    const bool dual = a->xq_neg_dev != nullptr, smooth = a->smooth_dev != nullptr;
+#define SQ_DISPATCH(T)                                                          \
+    do {                                                                        \
+        if (a->out_kind == SQ_Q_INT8) launch_static<T, SQ_Q_INT8>(p, dual, smooth, st); \
+        else launch_static<T, SQ_Q_E4M3>(p, dual, smooth, st);                  \
+    } while (0)
+    if (a->x_dtype == SQ_F32) SQ_DISPATCH(float);
+    else if (a->x_dtype == SQ_F16) SQ_DISPATCH(__half);
+    else SQ_DISPATCH(__nv_bfloat16);
+#undef SQ_DISPATCH
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
+}
+
+int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_neg_out, cudaStream_t st) {
+    int rc = validate(a, true);
+    if (rc != SQ_OK) return rc;
+    SQ_REQUIRE(sx_out != nullptr, SQ_ERR_INVALID_ARG, "sq_quantize_act_dynamic: sx_out_dev is NULL");
+    SQ_REQUIRE(a->smooth_dev == nullptr, SQ_ERR_UNSUPPORTED, "sq_quantize_act_dynamic: smooth_dev is not supported");
+    const bool dual = a->xq_neg_dev != nullptr;
+    SQ_REQUIRE(!dual || sx_neg_out != nullptr, SQ_ERR_INVALID_ARG,
+               "sq_quantize_act_dynamic: DualScale needs sx_neg_out_dev");
+    if (a->batch * a->M * a->K == 0) return SQ_OK;
+    ActQuantParams p;
+    fill_params(a, p);
+    p.sx_out = sx_out; p.sx_neg_out = sx_neg_out;
+#define SQ_DISPATCH(T)                                                       \
+    do {                                                                     \
+        if (a->out_kind == SQ_Q_INT8) launch_dynamic<T, SQ_Q_INT8>(p, dual, st); \
+        else launch_dynamic<T, SQ_Q_E4M3>(p, dual, st);                      \
+    } while (0)
+    if (a->x_dtype == SQ_F32) SQ_DISPATCH(float);
+    else if (a->x_dtype == SQ_F16) SQ_DISPATCH(__half);
+    else SQ_DISPATCH(__nv_bfloat16);
+#undef SQ_DISPATCH
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
+}
+
+}  // namespace sq

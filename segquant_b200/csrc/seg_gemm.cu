@@ -1,0 +1,821 @@
+// Segmented quantised GEMM with fused de-quantise epilogue for sm_100a.
+//
+//   TMA (cp.async.bulk.tensor, no multicast) -> 128B-swizzled shared memory -> tcgen05.mma
+//   (kind::i8 / kind::f8f6f4, cta_group::1, 128x256x32) -> int32 / fp32 accumulators in tensor
+//   memory -> tcgen05.ld -> per-unit scale, running fp32 sum in registers, bias, cast, store.
+//
+// It replaces the CUTLASS mma.sync GemmUniversal of segquant/src/real_quant/real_gemm.cu:208-305,
+// the fp32 scratch it writes, real_dequantize_{,dual_}scaled_kernel of
+// segquant/src/real_quant/dequantizer.cuh:35-73 and the torch-side segment sum / bias add of
+// segquant/layers/SegmentLinear.py:238-241.
+//
+// Persistent kernel, one CTA per SM, warp roles:
+//   warp 0      : TMA producer (one lane)
+//   warp 1      : allocates tensor memory, issues tcgen05.mma (one lane)
+//   warps 2-3   : idle
+//   warps 4-11  : epilogue, two warpgroups; warpgroup h owns tile columns [128h, 128h+128),
+//                 warp w reads TMEM lanes 32*(w%4) .. +31 (one output row per thread)
+//   warps 12-15 : (W4A8 only) expand packed int4 weights to int8 in shared memory
+//
+// K is cut into accumulation units (activation segments x weight-scale groups).  A unit's
+// products are accumulated exactly in tensor memory; at a unit boundary the MMA warp switches to
+// the other TMEM buffer while the epilogue drains the finished one into fp32 registers, so integer
+// sums never cross a scale boundary.  With DualScale the positive and the negative activation
+// tile share the weight tile: two MMAs per K step into the two TMEM buffers.
+//
+// Every wait in this file is bounded: when one runs out the kernel records a code in the device
+// status word, raises a CTA-wide abort flag and every role leaves its loop.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace sq {
+
+constexpr int BM = 128;        // tile rows (TMEM lanes)
+constexpr int BN = 256;        // tile columns (TMEM columns per buffer)
+constexpr int BK = 128;        // K elements per pipeline stage (= one 128-byte swizzle row)
+constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int kTmemCols = 512;
+constexpr int kEpiThreads = 256;
+
+constexpr uint32_t kABytes = BM * BK;          // 16 KB
+constexpr uint32_t kBBytes = BN * BK;          // 32 KB
+constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
+
+// status-word codes (low byte = which wait, rest = block index)
+enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitEpi = 7 };
+
+// Written (first writer wins) when a bounded wait gives up: (block index << 8) | WaitCode.
+// One copy per device that loads this library; read and cleared by read_device_status().
+__device__ unsigned long long g_wait_status = 0ull;
+
+struct GemmParams {
+    long long M, N, K;
+    int batch;
+    int num_segs;
+    int seg_bounds[SQ_MAX_SEGS + 1];
+    int group_size;
+    int w_seg_as_batch;
+    int a_batched;
+    const float* sx;
+    const float* sx_neg;
+    long long sx_bs, sx_ss, sx_rs;
+    const void* sw;
+    int sw_is_bf16;
+    long long sw_bs, sw_ss, sw_gs, sw_cs;
+    const void* bias;
+    int bias_dtype;
+    long long bias_bs;
+    void* y;
+    int out_dtype;
+    long long y_bs, y_rs;
+    void* acc_dump;
+    int units;
+    int tiles_m, tiles_n;
+    long long total_tiles;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up after ~2 s (or as soon as another role has raised the abort flag).
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > 2000000000ull) {
+                atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+#pragma unroll 1
+    for (int it = 0; it < 64; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, code);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// tcgen05.commit: the mbarrier gets one arrival when every tcgen05.mma issued so far by this
+// thread has finished reading shared memory and writing tensor memory.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == SQ_GEMM_W8A8_F8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <uint32_t N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <uint32_t N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA SWIZZLE_128B writes): 8-row groups are 1024 bytes apart (SBO), the
+// leading-dimension offset is unused for swizzled K-major layouts, version 1 = Blackwell,
+// layout type 2 = SWIZZLE_128B.  `addr` is the shared address of element (row 0, k 0 of this MMA).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
+    d |= static_cast<uint64_t>(1) << 16;            // LBO (ignored)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;    // SBO
+    d |= static_cast<uint64_t>(1) << 46;            // descriptor version
+    d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: dense, no negate, both operands K-major, D = 128 x 256.
+template <int KIND>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+    uint32_t d = 0;
+    if (KIND == SQ_GEMM_W8A8_F8) {
+        d |= 1u << 4;   // D format F32
+        d |= 0u << 7;   // A = E4M3
+        d |= 0u << 10;  // B = E4M3
+    } else {
+        d |= 2u << 4;   // D format S32
+        d |= 1u << 7;   // A = signed 8-bit
+        d |= 1u << 10;  // B = signed 8-bit
+    }
+    d |= static_cast<uint32_t>(BN >> 3) << 17;
+    d |= static_cast<uint32_t>(BM >> 4) << 24;
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel configuration
+// ---------------------------------------------------------------------------------------------
+template <int KIND, bool DUAL>
+struct Cfg {
+    static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
+    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes + (kW4 ? kBPackedBytes : 0);
+    static constexpr int kStages = (192 * 1024) / kStageBytes;
+    static constexpr int kThreads = kW4 ? 512 : 384;
+    static constexpr uint32_t kTxBytes = kABytes * (DUAL ? 2 : 1) + (kW4 ? kBPackedBytes : kBBytes);
+    // dynamic shared memory: 1 KB alignment slack + stages + scale tables (2 parities x 2 sides x BN floats)
+    static constexpr uint32_t kTabBytes = 2 * 2 * BN * sizeof(float);
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + 256;
+};
+
+struct UnitCursor {
+    int s, k, k_end, g;
+};
+
+__device__ __forceinline__ int unit_end(const GemmParams& p, int s, int k) {
+    int e = p.seg_bounds[s + 1];
+    if (p.group_size > 0) {
+        const int ge = (k / p.group_size + 1) * p.group_size;
+        e = ge < e ? ge : e;
+    }
+    return e;
+}
+
+__device__ __forceinline__ float load_sw(const GemmParams& p, long long idx) {
+    if (p.sw_is_bf16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.sw)[idx]);
+    return static_cast<const float*>(p.sw)[idx];
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[16], int valid, bool vec_ok) {
+    if (vec_ok && valid >= 16) {
+        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    OutT lo = from_float<OutT>(v[8 * i + 2 * j]);
+                    OutT hi = from_float<OutT>(v[8 * i + 2 * j + 1]);
+                    w[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+                           (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                }
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i < valid) dst[i] = from_float<OutT>(v[i]);
+    }
+}
+
+__device__ __forceinline__ float load_bias(const void* bias, int dtype, long long idx) {
+    if (dtype == SQ_F32) return __ldg(static_cast<const float*>(bias) + idx);
+    if (dtype == SQ_F16) return __half2float(__ldg(static_cast<const __half*>(bias) + idx));
+    return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + idx));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int KIND, bool DUAL>
+__global__ void __launch_bounds__(Cfg<KIND, DUAL>::kThreads, 1)
+seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
+                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ GemmParams p) {
+    using C = Cfg<KIND, DUAL>;
+    constexpr int kStages = C::kStages;
+    constexpr bool kW4 = C::kW4;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_tmem_full[2], bar_tmem_empty[2], bar_epi;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [2][2][BN]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    auto stage_a = [&](int st) { return smem_base + st * C::kStageBytes; };
+    auto stage_an = [&](int st) { return smem_base + st * C::kStageBytes + kABytes; };
+    auto stage_b = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1); };
+    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + kBBytes; };
+
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&bar_full[i]), 1);
+            mbar_init(smem_u32(&bar_empty[i]), 1);
+            mbar_init(smem_u32(&bar_cvt[i]), 4);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bar_tmem_full[i]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[i]), kEpiThreads / 32);
+        }
+        mbar_init(smem_u32(&bar_epi), kEpiThreads / 32);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_a);
+        if (DUAL) prefetch_tmap(&map_an);
+        prefetch_tmap(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producer / MMA warps
+        reg_dec<kW4 ? 40 : 56>();
+        if (warp == 0 && lane == 0) {
+            // ===== TMA producer =====
+            uint32_t it = 0;  // running stage counter
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+                const int b = static_cast<int>(tile / tiles_per_batch);
+                const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+                const int m0 = (rem / p.tiles_n) * BM;
+                const int n0 = (rem % p.tiles_n) * BN;
+                const int ab = p.a_batched ? b : 0;
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    for (int k = k_beg; k < k_end; k += BK, ++it) {
+                        const int st = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
+                        const uint32_t full = smem_u32(&bar_full[st]);
+                        mbar_arrive_expect_tx(full, C::kTxBytes);
+                        tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
+                        if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
+                        const int wk = p.w_seg_as_batch ? (k - k_beg) : k;
+                        const int wb = p.w_seg_as_batch ? s : b;
+                        if (kW4) tma_load_3d(stage_bp(st), &map_w, wk >> 1, n0, wb, full);
+                        else tma_load_3d(stage_b(st), &map_w, wk, n0, wb, full);
+                    }
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ===== MMA issuer =====
+            constexpr uint32_t idesc = make_idesc<KIND>();
+            uint32_t it = 0;   // stage counter
+            uint32_t au = 0;   // accumulation-unit counter (selects the TMEM buffer)
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    int u_end = k_beg;  // forces "new unit" at the first step of the segment
+                    uint32_t accumulate = 0;
+                    uint32_t d_pos = 0, d_neg = 0;
+                    for (int kb = k_beg; ok && kb < k_end; kb += BK, ++it) {
+                        const int st = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
+                        if (kW4) {
+                            if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
+                        }
+                        tc_fence_after();
+                        const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
+                        for (int kk = 0; kk < kmax; kk += UMMA_K) {
+                            const int k = kb + kk;
+                            if (k == u_end) {
+                                // unit boundary: hand the finished buffer to the epilogue, take the next one
+                                if (k != k_beg) {
+                                    umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));
+                                }
+                                const uint32_t buf = DUAL ? 0u : (au & 1u);
+                                const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
+                                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                                tc_fence_after();
+                                d_pos = tmem_base + buf * BN;
+                                d_neg = tmem_base + BN;
+                                accumulate = 0;
+                                u_end = unit_end(p, s, k);
+                                ++au;
+                            }
+                            const uint64_t db = make_smem_desc(stage_b(st) + kk);
+                            umma<KIND>(d_pos, make_smem_desc(stage_a(st) + kk), db, idesc, accumulate);
+                            if (DUAL) umma<KIND>(d_neg, make_smem_desc(stage_an(st) + kk), db, idesc, accumulate);
+                            accumulate = 1;
+                        }
+                        if (!ok) break;
+                        umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
+                    }
+                    if (ok) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));  // last unit of the segment
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------------------------------------------ epilogue warps
+        reg_inc<kW4 ? 192 : 216>();
+        const int epi_tid = threadIdx.x - 128;       // 0..255
+        const int q = warp & 3;                      // TMEM lane quarter of this warp
+        const int h = (warp - 4) >> 2;               // column half
+        const bool per_token = p.sx_rs != 0;
+        uint32_t au = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+            const int b = static_cast<int>(tile / tiles_per_batch);
+            const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+            const int m0 = (rem / p.tiles_n) * BM;
+            const int n0 = (rem % p.tiles_n) * BN;
+            const long long m = m0 + q * 32 + lane;
+            const bool row_ok = m < p.M;
+
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+
+            int unit_in_tile = 0;
+            for (int s = 0; ok && s < p.num_segs; ++s) {
+                const int k_end = p.seg_bounds[s + 1];
+                for (int k = p.seg_bounds[s]; ok && k < k_end; ++unit_in_tile) {
+                    const int ke = unit_end(p, s, k);
+                    const int g = p.group_size > 0 ? k / p.group_size : 0;
+                    const uint32_t par = au & 1u;
+                    // ---- per-column reciprocal scale table for this unit
+                    {
+                        const long long n = n0 + epi_tid;
+                        float r = 0.0f, rn = 0.0f;
+                        if (n < p.N) {
+                            const float swv = load_sw(p, b * p.sw_bs + s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
+                            const float sxv = per_token ? 1.0f : __ldg(p.sx + b * p.sx_bs + s * p.sx_ss);
+                            r = 1.0f / (sxv * swv);
+                            if (DUAL) {
+                                const float sxn = per_token ? 1.0f : __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss);
+                                rn = 1.0f / (sxn * swv);
+                            }
+                            if (kW4) { r *= 0.0625f; rn *= 0.0625f; }  // int4 weights are expanded as 16*w
+                        }
+                        rtab[(par * 2 + 0) * BN + epi_tid] = r;
+                        rtab[(par * 2 + 1) * BN + epi_tid] = rn;
+                    }
+                    // all 8 epilogue warps have written their table entries (bounded, unlike bar.sync)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
+                    if (!mbar_wait(smem_u32(&bar_epi), par, abort_flag, kWaitEpi)) { ok = false; break; }
+                    float rxm = 1.0f, rxnm = 1.0f;
+                    if (per_token && row_ok) {
+                        rxm = 1.0f / __ldg(p.sx + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
+                        if (DUAL) rxnm = 1.0f / __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
+                    }
+                    const uint32_t buf = DUAL ? 0u : (au & 1u);
+                    const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
+                    if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * 128;
+                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + BN + h * 128;
+                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * 128;
+                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * 128;
+                    int32_t* dump = nullptr;
+                    if (p.acc_dump != nullptr && row_ok) {
+                        const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
+                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * 128;
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        uint32_t v[16];
+                        tmem_ld_x16(t_pos + ch * 16, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
+                            float r = rt_pos[ch * 16 + j];
+                            if (per_token) r *= rxm;
+                            acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
+                        }
+                        if (dump != nullptr) {
+#pragma unroll 1
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + h * 128 + ch * 16 + j < p.N)
+                                    dump[ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
+                        }
+                        if (DUAL) {
+                            tmem_ld_x16(t_neg + ch * 16, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
+                                float r = rt_neg[ch * 16 + j];
+                                if (per_token) r *= rxnm;
+                                acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
+                            }
+                            if (dump != nullptr) {
+#pragma unroll 1
+                                for (int j = 0; j < 16; ++j)
+                                    if (n0 + h * 128 + ch * 16 + j < p.N)
+                                        dump[p.M * p.N + ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
+                            }
+                        }
+                    }
+                    // buffer drained: give it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+                    ++au;
+                    k = ke;
+                }
+            }
+            if (!ok) break;
+            // ---- bias, cast, store (one row of 128 consecutive columns per thread)
+            if (row_ok) {
+                const long long ncol0 = n0 + h * 128;
+                const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
+                uint8_t* yrow = static_cast<uint8_t*>(p.y) + (b * p.y_bs + m * p.y_rs + ncol0) * esz;
+                const bool vec_ok = (reinterpret_cast<uintptr_t>(yrow) & 15u) == 0;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const long long nc = ncol0 + ch * 16;
+                    int valid = static_cast<int>(p.N - nc);
+                    valid = valid > 16 ? 16 : valid;
+                    if (valid > 0) {
+                        float o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
+                        if (p.bias != nullptr) {
+                            const long long bo = b * p.bias_bs + nc;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (j < valid) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
+                        }
+                        if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
+                        else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
+                        else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ int4 -> int8 expansion warps (W4A8)
+        if constexpr (kW4) {
+            reg_dec<80>();
+            const int ct = threadIdx.x - 384;  // 0..127
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    for (int kb = k_beg; kb < k_end; kb += BK, ++it) {
+                        const int st = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
+                        uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
+                        // staging tile: 256 rows x 64 packed bytes; 16-byte chunk c = (row, quarter)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int c = ct + i * 128;
+                            const int row = c >> 2, qd = c & 3;
+                            const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
+                            const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
+                            uint32_t out[8];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                // int8 value = 16 * int4 value: nibble moved to the top of its byte
+                                const uint32_t lo = (in[j] << 4) & 0xF0F0F0F0u;  // even k
+                                const uint32_t hi = in[j] & 0xF0F0F0F0u;         // odd k
+                                out[2 * j] = __byte_perm(lo, hi, 0x5140);
+                                out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                            }
+                            // 32 int8 = two 16-byte chunks of the 128-byte row, XOR-swizzled by (row % 8)
+                            uint8_t* drow = dst + row * 128;
+                            const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
+                            *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+                            *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+                        }
+                        fence_proxy_async_smem();  // generic-proxy writes -> visible to tcgen05.mma
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_cvt[st]));
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before shared memory is released
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+long long read_device_status() {
+    unsigned long long v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(&v, g_wait_status, sizeof(v)) != cudaSuccess) return SQ_ERR_CUDA;
+    if (v != 0 && cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(zero)) != cudaSuccess) return SQ_ERR_CUDA;
+    return static_cast<long long>(v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+// 3-D uint8 tensor {inner bytes, rows, batch}.
+static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t row_stride,
+                    uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows, bool swizzle128, const char* what) {
+    auto fn = get_encode_fn();
+    SQ_REQUIRE(fn != nullptr, SQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {inner, rows, batch};
+    cuuint64_t strides[2] = {row_stride, batch_stride};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SQ_REQUIRE(r == CUDA_SUCCESS, SQ_ERR_CUDA,
+               "cuTensorMapEncodeTiled(%s) failed with CUresult %d (dims %llu x %llu x %llu, strides %llu, %llu)", what,
+               static_cast<int>(r), (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch,
+               (unsigned long long)row_stride, (unsigned long long)batch_stride);
+    return SQ_OK;
+}
+
+int gemm_num_units(int num_segs, const int* seg_bounds, int group_size) {
+    if (num_segs < 1 || num_segs > SQ_MAX_SEGS || seg_bounds == nullptr || group_size < 0) return SQ_ERR_INVALID_ARG;
+    int units = 0;
+    for (int s = 0; s < num_segs; ++s) {
+        int k = seg_bounds[s];
+        const int e = seg_bounds[s + 1];
+        if (e <= k) return SQ_ERR_INVALID_ARG;
+        while (k < e) {
+            int ue = e;
+            if (group_size > 0) {
+                const int ge = (k / group_size + 1) * group_size;
+                ue = ge < e ? ge : e;
+            }
+            ++units;
+            k = ue;
+        }
+    }
+    return units;
+}
+
+template <int KIND, bool DUAL>
+static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+    using C = Cfg<KIND, DUAL>;
+    static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
+    static bool attr_set[64] = {};
+    int dev = 0;
+    SQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        attr_set[dev] = true;
+    } else if (dev >= 64) {
+        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    }
+    const long long grid = p.total_tiles < kNumSMs ? p.total_tiles : kNumSMs;
+    seg_gemm_kernel<KIND, DUAL><<<static_cast<int>(grid), C::kThreads, C::kSmemBytes, st>>>(ma, man, mw, p);
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
+}
+
+int gemm(const sq_gemm_args* a, cudaStream_t st) {
+    SQ_REQUIRE(a != nullptr, SQ_ERR_INVALID_ARG, "sq_gemm: args is NULL");
+    SQ_REQUIRE(a->kind == SQ_GEMM_W8A8_I8 || a->kind == SQ_GEMM_W8A8_F8 || a->kind == SQ_GEMM_W4A8, SQ_ERR_INVALID_ARG,
+               "sq_gemm: unknown kind %d", a->kind);
+    SQ_REQUIRE(a->out_dtype == SQ_F32 || a->out_dtype == SQ_F16 || a->out_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
+               "sq_gemm: unknown out_dtype %d", a->out_dtype);
+    SQ_REQUIRE(a->batch >= 0 && a->M >= 0 && a->N >= 0 && a->K >= 0, SQ_ERR_INVALID_ARG, "sq_gemm: negative size");
+    if (a->batch == 0 || a->M == 0 || a->N == 0) return SQ_OK;
+    SQ_REQUIRE(a->xq_dev && a->wq_dev && a->sx_dev && a->sw_dev && a->y_dev, SQ_ERR_INVALID_ARG, "sq_gemm: NULL operand pointer");
+    const bool dual = a->xq_neg_dev != nullptr;
+    SQ_REQUIRE(!dual || a->sx_neg_dev, SQ_ERR_INVALID_ARG, "sq_gemm: DualScale needs sx_neg_dev");
+    SQ_REQUIRE(a->K > 0, SQ_ERR_INVALID_ARG, "sq_gemm: K must be positive");
+    SQ_REQUIRE(a->K % 32 == 0, SQ_ERR_ALIGNMENT, "sq_gemm: K (%lld) must be divisible by 32", static_cast<long long>(a->K));
+    SQ_REQUIRE(a->M < (1ll << 31) - BM && a->N < (1ll << 31) - BN && a->K < (1ll << 30) && a->batch < (1 << 20),
+               SQ_ERR_TOO_LARGE, "sq_gemm: problem dimension too large");
+    SQ_REQUIRE(a->num_segs >= 1 && a->num_segs <= SQ_MAX_SEGS, SQ_ERR_INVALID_ARG, "sq_gemm: num_segs %d outside [1, %d]",
+               a->num_segs, SQ_MAX_SEGS);
+    SQ_REQUIRE(a->seg_bounds[0] == 0 && a->seg_bounds[a->num_segs] == a->K, SQ_ERR_INVALID_ARG,
+               "sq_gemm: seg_bounds must run from 0 to K");
+    for (int s = 0; s < a->num_segs; ++s) {
+        SQ_REQUIRE(a->seg_bounds[s + 1] > a->seg_bounds[s], SQ_ERR_INVALID_ARG, "sq_gemm: seg_bounds not increasing at %d", s);
+        SQ_REQUIRE(a->seg_bounds[s + 1] % 32 == 0, SQ_ERR_ALIGNMENT, "sq_gemm: segment bound %d must be divisible by 32",
+                   a->seg_bounds[s + 1]);
+    }
+    SQ_REQUIRE(a->group_size >= 0 && a->group_size % 32 == 0, SQ_ERR_ALIGNMENT, "sq_gemm: group_size %d must be a multiple of 32",
+               a->group_size);
+    const bool w4 = a->kind == SQ_GEMM_W4A8;
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    SQ_REQUIRE(aligned16(a->xq_dev) && (!dual || aligned16(a->xq_neg_dev)) && aligned16(a->wq_dev), SQ_ERR_ALIGNMENT,
+               "sq_gemm: operand pointers must be 16-byte aligned");
+    SQ_REQUIRE(a->xq_row_stride % 16 == 0 && a->xq_batch_stride % 16 == 0 && a->wq_row_stride % 16 == 0 &&
+                   a->wq_batch_stride % 16 == 0,
+               SQ_ERR_ALIGNMENT, "sq_gemm: operand strides must be multiples of 16 bytes");
+    SQ_REQUIRE(a->xq_row_stride >= a->K && a->xq_batch_stride >= 0, SQ_ERR_INVALID_ARG, "sq_gemm: xq_row_stride smaller than K");
+
+    long long w_k = a->K;  // K extent of one weight matrix
+    long long w_batches = a->batch;
+    if (a->w_seg_as_batch) {
+        SQ_REQUIRE(a->batch == 1, SQ_ERR_INVALID_ARG, "sq_gemm: w_seg_as_batch needs batch == 1");
+        const int len = a->seg_bounds[1];
+        for (int s = 0; s < a->num_segs; ++s)
+            SQ_REQUIRE(a->seg_bounds[s + 1] - a->seg_bounds[s] == len, SQ_ERR_UNSUPPORTED,
+                       "sq_gemm: w_seg_as_batch needs equal segments (SegmentLinear.py:80-82)");
+        w_k = len;
+        w_batches = a->num_segs;
+    }
+    const long long w_row_bytes = w4 ? w_k / 2 : w_k;
+    SQ_REQUIRE(a->wq_row_stride >= w_row_bytes, SQ_ERR_INVALID_ARG, "sq_gemm: wq_row_stride smaller than a weight row");
+
+    const int units = gemm_num_units(a->num_segs, a->seg_bounds, a->group_size);
+    SQ_REQUIRE(units > 0, SQ_ERR_INVALID_ARG, "sq_gemm: bad segment description");
+
+    GemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K; p.batch = static_cast<int>(a->batch);
+    p.num_segs = a->num_segs;
+    for (int s = 0; s <= SQ_MAX_SEGS; ++s) p.seg_bounds[s] = s <= a->num_segs ? a->seg_bounds[s] : 0;
+    p.group_size = a->group_size;
+    p.w_seg_as_batch = a->w_seg_as_batch ? 1 : 0;
+    p.a_batched = a->xq_batch_stride != 0 ? 1 : 0;
+    p.sx = a->sx_dev; p.sx_neg = a->sx_neg_dev;
+    p.sx_bs = a->sx_batch_stride; p.sx_ss = a->sx_seg_stride; p.sx_rs = a->sx_row_stride;
+    p.sw = a->sw_dev; p.sw_is_bf16 = a->sw_is_bf16 ? 1 : 0;
+    p.sw_bs = a->sw_batch_stride; p.sw_ss = a->sw_seg_stride; p.sw_gs = a->sw_group_stride; p.sw_cs = a->sw_col_stride;
+    p.bias = a->bias_dev; p.bias_dtype = a->bias_dtype; p.bias_bs = a->bias_batch_stride;
+    p.y = a->y_dev; p.out_dtype = a->out_dtype; p.y_bs = a->y_batch_stride; p.y_rs = a->y_row_stride;
+    p.acc_dump = a->acc_dump_dev; p.units = units;
+    p.tiles_m = static_cast<int>((a->M + BM - 1) / BM);
+    p.tiles_n = static_cast<int>((a->N + BN - 1) / BN);
+    p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
+    if (a->bias_dev)
+        SQ_REQUIRE(a->bias_dtype == SQ_F32 || a->bias_dtype == SQ_F16 || a->bias_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
+                   "sq_gemm: unknown bias_dtype %d", a->bias_dtype);
+
+    CUtensorMap ma, man, mw;
+    const uint64_t a_batches = p.a_batched ? a->batch : 1;
+    const uint64_t a_bstride = p.a_batched ? a->xq_batch_stride : static_cast<uint64_t>(a->xq_row_stride) * a->M;
+    int rc = make_map(&ma, a->xq_dev, a->K, a->M, a_batches, a->xq_row_stride, a_bstride, BK, BM, true, "xq");
+    if (rc != SQ_OK) return rc;
+    man = ma;
+    if (dual) {
+        rc = make_map(&man, a->xq_neg_dev, a->K, a->M, a_batches, a->xq_row_stride, a_bstride, BK, BM, true, "xq_neg");
+        if (rc != SQ_OK) return rc;
+    }
+    const uint64_t w_bstride = (w_batches > 1 && a->wq_batch_stride != 0) ? a->wq_batch_stride
+                                                                         : static_cast<uint64_t>(a->wq_row_stride) * a->N;
+    const uint64_t w_nb = (w_batches > 1 && a->wq_batch_stride != 0) ? w_batches : 1;
+    SQ_REQUIRE(w_nb == static_cast<uint64_t>(w_batches) || !a->w_seg_as_batch, SQ_ERR_INVALID_ARG,
+               "sq_gemm: w_seg_as_batch needs a non-zero wq_batch_stride");
+    if (w_nb == 1 && w_batches > 1) {
+        // every problem shares one weight matrix: the kernel always asks for batch index b, so
+        // describe `batch` copies 0 bytes apart is not encodable; fold by pointing all at copy 0
+        SQ_REQUIRE(false, SQ_ERR_UNSUPPORTED, "sq_gemm: batched problems need their own weights (wq_batch_stride != 0)");
+    }
+    if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, BN, false, "wq(int4)");
+    else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, BN, true, "wq");
+    if (rc != SQ_OK) return rc;
+
+    if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch<SQ_GEMM_W8A8_I8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W8A8_I8, false>(ma, man, mw, p, st);
+    if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch<SQ_GEMM_W8A8_F8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W8A8_F8, false>(ma, man, mw, p, st);
+    return dual ? launch<SQ_GEMM_W4A8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W4A8, false>(ma, man, mw, p, st);
+}
+
+}  // namespace sq
