@@ -105,6 +105,10 @@ float sqo_e4m3_to_float(uint8_t b) {
     return (float)(sign ? -v : v);
 }
 
+void sqo_e4m3_encode(const float* x, uint8_t* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = sqo_e4m3_from_float(x[i]);
+}
+
 void sqo_e4m3_roundtrip(const float* x, float* out, int64_t n) {
     /* fake_e4m3fy CPU branch, segquant/src/fake_quant/quantizer_fp8.cpp:29-37 */
     for (int64_t i = 0; i < n; ++i) out[i] = sqo_e4m3_to_float(sqo_e4m3_from_float(x[i]));

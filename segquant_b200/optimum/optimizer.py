@@ -1,0 +1,232 @@
+"""Per-layer policy objects ("optimizers"): own the calibrators, freeze the scale tensors and
+dispatch a forward either to the native real-quant kernels or to the torch fake-quant math.
+
+API follows the reference's segquant/optimum/optimizer.py: BaseOptimizer.make_scale_tensor
+(:47-92) stacks per-segment scales into fp32 tensors `(scale_x, scale_w)` or
+`(pos_scale_x, neg_scale_x, scale_w)`; call_func (:94-123) is the single dispatch point;
+DefaultOptimizer (:166-293) quantises plainly.  Differences, all deliberate:
+
+* real-quant forwards go through ONE fused launch pair (ops.seg_linear) that sums K-segments in
+  fp32 inside the GEMM epilogue; the reference materialises S partial outputs and sums them in
+  torch (segquant/layers/SegmentLinear.py:238-240).  call_func keeps the reference's un-summed
+  contract for `forward(x, chunked=True)`.
+* `dynamic=True` activations use the fused absmax+quantise kernel; the reference calls a
+  `dynamic_calibrate` that does not exist (:96-100).
+* the fake path does not write into the caller's tensor (the reference does, :120-121).
+* unequal K-segments and group-wise weight scales are accepted.
+"""
+import torch
+
+from .. import ops
+from ..layers.segment_tensor_manager import segmented_matmul
+
+
+def _as_f32(v, device):
+    if isinstance(v, torch.Tensor):
+        return v.to(dtype=torch.float32, device=device)
+    return torch.tensor(v, dtype=torch.float32, device=device)
+
+
+class BaseOptimizer:
+    def __init__(self, seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                 real_quant=False, dual_scale=False, kernel_type=None):
+        self.seg_mode, self.chunks, self.chunksizes = seg_mode, chunks, chunksizes
+        self.weight_manager = weight_manager
+        self.input_calibrators, self.weight_calibrators = input_calibrators, weight_calibrators
+        self.real_quant, self.dual_scale, self.kernel_type = real_quant, dual_scale, kernel_type
+        self.packed = bool(real_quant and kernel_type and "Wint4" in kernel_type)
+        self.func_name = "gemm_dual_scaled_fn" if (real_quant and dual_scale) else "gemm_scaled_fn"
+        self.has_calibrated = False
+        self.scale_tensor = None
+        self._fused = None  # derived, device-resident arguments of the fused forward
+
+    # ---- scales ----------------------------------------------------------------------------
+    def _stack(self, calibrators, attr):
+        dev = self.weight_manager.device()
+        vals = [_as_f32(getattr(c, attr), dev) for c in calibrators]
+        if len(vals) == 1:
+            vals = vals * self.chunks
+        return torch.stack(vals)
+
+    def make_scale_tensor(self):
+        sw = self._stack(self.weight_calibrators, "scale")
+        if self.dual_scale:
+            self.scale_tensor = (self._stack(self.input_calibrators, "pos_scale"),
+                                 self._stack(self.input_calibrators, "neg_scale"), sw)
+        else:
+            self.scale_tensor = (self._stack(self.input_calibrators, "scale"), sw)
+        self._fused = None
+
+    def _weight_quantizer(self, i=0):
+        c = self.weight_calibrators[i]
+        return getattr(c, "quantizer", c)
+
+    def _input_quantizer(self, i=0):
+        c = self.input_calibrators[i]
+        return getattr(c, "quantizer", c)
+
+    # ---- reference-contract dispatch (un-summed segments, no bias) ------------------------------
+    def call_func(self, batch_input, batch_weight):
+        if self.real_quant:
+            if self._input_quantizer().dynamic:
+                raise RuntimeError("dynamic activation scales are served by the fused forward (chunked=False)")
+            fn = ops.real_quantized_gemm_scaled
+            if self.dual_scale:
+                pos, neg, sw = self.scale_tensor
+                return fn(self.kernel_type, batch_input, batch_weight, pos, sw, neg_scale_x=neg)
+            sx, sw = self.scale_tensor
+            return fn(self.kernel_type, batch_input, batch_weight, sx, sw)
+        qs = self.input_calibrators if len(self.input_calibrators) > 1 else self.input_calibrators * batch_input.shape[0]
+        fake = torch.stack([q.quantize(batch_input[i]) for i, q in enumerate(qs)])
+        return segmented_matmul(fake, batch_weight)
+
+    # ---- fused forward ---------------------------------------------------------------------------
+    def _build_fused(self):
+        wm = self.weight_manager
+        N, K = wm.out_features, wm.in_features
+        sw = self.scale_tensor[-1]
+        if not self._input_quantizer().dynamic and self.scale_tensor[0].numel() != self.chunks:
+            raise RuntimeError("static per-token activation scales are only served by forward(x, chunked=True)")
+        group = getattr(self._weight_quantizer(), "group_size", None) or 0
+        if self.seg_mode == "input":
+            bounds = wm.bounds
+            S = self.chunks
+            if group:
+                sw_t, strides = sw[0].contiguous(), (0, 0, 1, K // group)     # (N, G)
+            elif sw.numel() == S:
+                sw_t, strides = sw.reshape(S).contiguous(), (0, 1, 0, 0)      # one scalar per segment
+            else:
+                sw_t, strides = sw.reshape(S, N).contiguous(), (0, N, 0, 1)   # (S, N)
+            take = slice(None)
+        else:
+            bounds = [0, K]
+            S = self.chunks
+            if group:
+                sw_t, strides = sw.reshape(N, K // group).contiguous(), (0, 0, 1, K // group)
+            elif sw.numel() == S:
+                sw_t, strides = sw.reshape(S).repeat_interleave(N // S).contiguous(), (0, 0, 0, 1)
+            else:
+                sw_t, strides = sw.reshape(N).contiguous(), (0, 0, 0, 1)
+            take = slice(0, 1)   # one input calibrator, its scale repeated per chunk (:56-57)
+        if self.dual_scale:
+            sx, sxn = self.scale_tensor[0].reshape(-1)[take].contiguous(), self.scale_tensor[1].reshape(-1)[take].contiguous()
+        else:
+            sx, sxn = self.scale_tensor[0].reshape(-1)[take].contiguous(), None
+        wq = wm.weight_tensor
+        wq3 = wq.reshape(1, N, -1)
+        self._fused = dict(bounds=bounds, sx=sx, sx_neg=sxn, sw=sw_t, sw_strides=strides, group=group, wq=wq3, N=N)
+
+    def fused_forward(self, x, bias=None):
+        """Final (..., N) output of the real-quant layer: quantise + segmented GEMM + bias."""
+        if not self.real_quant:
+            raise RuntimeError("fused_forward is the real-quant path")
+        if self._fused is None:
+            self._build_fused()
+        f = self._fused
+        iq = self._input_quantizer()
+        return ops.seg_linear(self.kernel_type, x, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"], sx_neg=f["sx_neg"],
+                              dynamic=bool(iq.dynamic), group_size=f["group"], sw_strides=f["sw_strides"], bias=bias)
+
+    # ---- housekeeping ------------------------------------------------------------------------------
+    def _calibrate_weights(self, i_view, w_view):
+        for cal, w_chunk, x_chunk in zip(self.weight_calibrators, w_view, i_view):
+            cal.calibrate(w_chunk, input_data=x_chunk)
+
+    def process_step(self, err):
+        pass
+
+    def _move(self, device):
+        self.weight_manager = self.weight_manager.to(device)
+        self.input_calibrators = [c.to(device) for c in self.input_calibrators]
+        self.weight_calibrators = [c.to(device) for c in self.weight_calibrators]
+        if self.scale_tensor is not None:
+            self.scale_tensor = tuple(t.to(device) for t in self.scale_tensor)
+        self._fused = None
+
+    def to_cpu(self):
+        self._move("cpu")
+
+    def to_cuda(self, device):
+        self._move(device)
+
+
+class OptimizerRegistry:
+    _registry = {}
+
+    @classmethod
+    def register(cls, name):
+        def deco(obj):
+            cls._registry[name] = obj
+            return obj
+        return deco
+
+    @classmethod
+    def get(cls, name):
+        return cls._registry.get(name)
+
+    @classmethod
+    def create(cls, name, **kwargs):
+        factory = cls.get(name)
+        if factory is None:
+            raise ValueError(f"Optimizer '{name}' not found in registry.")
+        return factory(**kwargs)
+
+
+@OptimizerRegistry.register("default")
+class DefaultOptimizer(BaseOptimizer):
+    """Plain quantisation: K-segments share one weight quantiser and have one activation quantiser
+    each; N-segments share the activation quantiser and have one weight quantiser each."""
+
+    def __init__(self, seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                 real_quant=False, dual_scale=False, kernel_type=None, **kwargs):
+        assert len(input_calibrators) == 1 or len(weight_calibrators) == 1, \
+            "Either input_calibrators or weight_calibrators must have a length of 1."
+        super().__init__(seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                         real_quant, dual_scale, kernel_type)
+
+    def __repr__(self):
+        head = f"DefaultOptimizer(type={self.kernel_type}\n" if self.real_quant else "DefaultOptimizer(\n"
+        iq = ",\n    ".join(repr(c) for c in self.input_calibrators)
+        wq = ",\n    ".join(repr(c) for c in self.weight_calibrators)
+        return f"{head}    input_quantizers=[\n    {iq}\n  ],\n    weight_quantizers=[\n    {wq}\n  ]\n)"
+
+    def calibrate(self, input_manager):
+        for cal, chunk in zip(self.input_calibrators, input_manager.iter_list()):
+            cal.calibrate(chunk)
+        if self.seg_mode == "input":
+            self._calibrate_weights(input_manager.total_view(), self.weight_manager.total_view())
+        else:
+            self._calibrate_weights(input_manager.iter_list(), self.weight_manager.iter_list())
+
+    def finish_calibrate(self):
+        for i, cal in enumerate(self.input_calibrators):
+            cal.finish_calibrate()
+            self.input_calibrators[i] = cal.quantizer
+        wm = self.weight_manager
+        if self.seg_mode == "input":
+            assert len(self.weight_calibrators) == 1, "weight_calibrators length must be 1"
+            q = self.weight_calibrators[0].finish_calibrate(wm.total_view()[0])
+            self.weight_calibrators[0] = self.weight_calibrators[0].quantizer
+            if self.packed:
+                wm.weight_tensor = q.reshape(wm.out_features, wm.in_features // 2)
+                wm.packed = True
+            else:
+                wm.weight_tensor = q
+        else:
+            parts = []
+            for i, (cal, chunk) in enumerate(zip(self.weight_calibrators, wm.iter_list())):
+                parts.append(cal.finish_calibrate(chunk))
+                self.weight_calibrators[i] = cal.quantizer
+            wm.replace_with_segments_layout(torch.stack(parts, dim=0), packed=self.packed)
+        self.has_calibrated = True
+        self.make_scale_tensor()
+
+    def forward(self, input_manager):
+        """Un-summed per-segment outputs (S, ..., N or N/S), the reference's `chunked` form."""
+        if not input_manager.uniform and self.seg_mode == "input":
+            if self.real_quant:
+                raise NotImplementedError("chunked outputs need equal segments; use forward(x) (fused)")
+            outs = [q.quantize(xs) @ w.transpose(-1, -2) for q, xs, w in
+                    zip(self.input_calibrators, input_manager.iter_list(), self.weight_manager.iter_list())]
+            return torch.stack(outs)
+        return self.call_func(input_manager.iter_view(), self.weight_manager.iter_view())

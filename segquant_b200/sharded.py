@@ -1,0 +1,79 @@
+"""Column-sharded SegmentLinear: output features split over the ranks of a torch.distributed
+process group (one process per GPU), activations replicated, one all-gather of output slices.
+
+The reference has no distributed code at all; this is the multi-GPU form of its layer asked for by
+the large-N GEMM sweep.  Rank r owns rows [r*N/g, (r+1)*N/g) of the weight (with their scales and
+bias), quantises its own copy of x (cheaper than broadcasting the quantised bytes), runs the fused
+layer forward on its slice and the slices are exchanged with NCCL `all_gather_into_tensor` over
+NVLink.  The exchange moves (g-1)/g * M*N*2 bytes in and out of every GPU, which at B200 tensor
+rates costs more than the GEMM itself for every K <= 12288; `forward` therefore reports nothing
+by itself -- bench.py times the GEMM phase and the whole step separately.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_total, world, rank):
+    """[begin, end) of the output columns rank `rank` owns; requires world | n_total so that all
+    slices have one size and the gather is a single dense buffer."""
+    if n_total % world:
+        raise ValueError(f"N={n_total} is not divisible by world size {world}")
+    per = n_total // world
+    return rank * per, (rank + 1) * per
+
+
+def assemble(gathered):
+    """(world, M, N/world) rank-major gather buffer -> (M, N) with rank r's columns at
+    [r*N/world, (r+1)*N/world)."""
+    world, m, per = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, world * per)
+
+
+def all_gather_slices(local, group=None):
+    """All-gather equally shaped [M, N/world] slices into a (world, M, N/world) buffer."""
+    world = dist.get_world_size(group)
+    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    local = local.contiguous()
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, local, group=group)
+    else:
+        dist.all_gather(list(out.unbind(0)), local, group=group)
+    return out
+
+
+class ColumnShardedSegLinear:
+    """Holds this rank's slice as an ordinary SegmentLinear (real-quant)."""
+
+    def __init__(self, local_layer, rank, world, n_total, group=None):
+        self.layer, self.rank, self.world, self.n_total, self.group = local_layer, rank, world, n_total, group
+
+    @classmethod
+    def from_full(cls, x_calib, weight, bias, rank, world, kernel_type="Wint8Aint8", dual_scale=False, seg_mode="input",
+                  chunks=1, chunksizes=None, weight_axis=1, group_size=None, group=None):
+        from .layers.SegmentLinear import SegmentLinear
+        n_total, k = weight.shape
+        lo, hi = shard_range(n_total, world, rank)
+        w_type, a_type = kernel_type[1:].split("A")
+        w_args = {"real_quant": True, "axis": weight_axis}
+        if group_size:
+            w_args["group_size"] = group_size
+        layer = SegmentLinear(k, hi - lo, bias=bias is not None, seg_mode=seg_mode, chunks=chunks, chunksizes=chunksizes,
+                              custom_weight_tensor=weight[lo:hi].contiguous(),
+                              custom_bias_tensor=None if bias is None else bias[lo:hi].contiguous(),
+                              input_quant_type=a_type, weight_quant_type=w_type,
+                              input_quant_args={"real_quant": True, "axis": None, "dual_scale": dual_scale},
+                              weight_quant_args=w_args, device=weight.device)
+        layer.calibrate(x_calib)
+        layer.finish_calibrate()
+        return cls(layer, rank, world, n_total, group)
+
+    def local_forward(self, x):
+        return self.layer(x)
+
+    def forward(self, x):
+        y = self.local_forward(x)
+        lead = y.shape[:-1]
+        gathered = all_gather_slices(y.reshape(-1, y.shape[-1]), self.group)
+        return assemble(gathered).reshape(*lead, self.n_total)
+
+    __call__ = forward

@@ -1,0 +1,185 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE's own Python code.
+
+    python tests/golden/make_golden.py [/root/reference]
+
+The reference (OptiSys-ZJU/segquant) is imported from its read-only checkout; nothing of it is
+copied.  `import segquant` would JIT-build its CUDA/CUTLASS extensions, so the package module is
+pre-registered with only its __path__, and the four real-quant loaders are replaced by stubs
+without GEMM functions -- SegmentLinear then takes its fake-quant branch
+(segquant/layers/SegmentLinear.py:105-113), which is the reference's CPU path.  The fp8 round trip
+uses the reference's own fake_e4m3fy C++ built into oracle/_ref/ (oracle/build_ref.py).
+
+Each fixture is an .npz with the seeded inputs, the scales the reference's calibrators produced and
+the reference's outputs.  tests/test_oracle_golden.py checks the oracle against them on CPU;
+tests/test_gpu_parity.py checks the CUDA path against them on the GPU.
+"""
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, REPO)
+
+
+def import_reference(root):
+    from oracle.build_ref import load_prebuilt
+    fp8_ext = load_prebuilt()
+    if fp8_ext is None:
+        raise SystemExit("oracle/_ref is not built: run `python oracle/build_ref.py` first")
+    sys.path.insert(0, root)
+    pkg = types.ModuleType("segquant")
+    pkg.__path__ = [os.path.join(root, "segquant")]
+    sys.modules["segquant"] = pkg
+    import segquant.utils.extension as ext
+
+    class _NoKernels:
+        pass
+
+    ext.load_fake_quant_fp8_ext = lambda verbose=False, required=False: fp8_ext
+    ext.load_real_quant_fp8_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wfpe4m3Afpe4m3",))
+    ext.load_real_quant_int8_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wint8Aint8",))
+    ext.load_real_quant_int4_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wint4Aint4",))
+    ext.load_real_quant_mix_ext = lambda verbose=False, required=False: (_NoKernels(), tuple(ext.supported_type))
+    import segquant.quantizers.quantizer as q
+    q.load_fake_quant_fp8_ext = ext.load_fake_quant_fp8_ext
+    from segquant.layers.SegmentLinear import SegmentLinear
+    return SegmentLinear, q
+
+
+def t2n(t):
+    if isinstance(t, torch.Tensor):
+        return t.detach().float().cpu().numpy()
+    return np.float32(t)
+
+
+def gen_input_seg_int8(SegmentLinear, seed=0, M=96, K=256, N=64, S=4):
+    """BASELINE config-1 recipe at toy size: K-segmented W8A8 INT8, per-segment activation scales,
+    per-output-channel weight scales."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    factors = [0.5, 1.0, 4.0, 16.0]
+    seg = K // S
+    for s in range(S):
+        x[:, s * seg:(s + 1) * seg] *= factors[s % 4]
+    perm = torch.randperm(K, generator=g)[: max(1, int(0.02 * K))]
+    x[:, perm] *= 20.0
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    lin = SegmentLinear(K, N, bias=True, seg_mode="input", chunks=S, custom_weight_tensor=w.clone(),
+                        custom_bias_tensor=b.clone(), input_quant_type="int8", weight_quant_type="int8",
+                        input_quant_args={"real_quant": False, "axis": None},
+                        weight_quant_args={"real_quant": False, "axis": 1},
+                        opt_type="default", opt_kwargs={}, calib_type="amax", calib_kwargs={}, device="cpu")
+    lin.calibrate(x.clone())
+    lin.finish_calibrate()
+    y = lin(x.clone())
+    sx, sw = lin.optimizer.scale_tensor
+    return dict(x=t2n(x), w=t2n(w), b=t2n(b), y=t2n(y), sx=t2n(sx), sw=t2n(sw),
+                w_fake=t2n(lin.optimizer.weight_manager.weight_tensor), bounds=np.arange(S + 1, dtype=np.int32) * seg)
+
+
+def gen_dual_fp8(SegmentLinear, seed=1, M=96, K=384, N=48):
+    """BASELINE config-2 recipe at toy size: DualScale FP8 after GELU, per-output-channel weights."""
+    g = torch.Generator().manual_seed(seed)
+    z = torch.randn(M, K, generator=g)
+    x = torch.nn.functional.gelu(z)
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    lin = SegmentLinear(K, N, bias=True, seg_mode="weight", chunks=1, custom_weight_tensor=w.clone(),
+                        custom_bias_tensor=b.clone(), input_quant_type="fpe4m3", weight_quant_type="fpe4m3",
+                        input_quant_args={"real_quant": False, "axis": None, "dual_scale": True},
+                        weight_quant_args={"real_quant": False, "axis": 1},
+                        opt_type="default", opt_kwargs={}, calib_type="amax", calib_kwargs={}, device="cpu")
+    lin.calibrate(x.clone())
+    lin.finish_calibrate()
+    y = lin(x.clone())
+    sp, sn, sw = lin.optimizer.scale_tensor
+    return dict(x=t2n(x), w=t2n(w), b=t2n(b), y=t2n(y), sx_pos=t2n(sp), sx_neg=t2n(sn), sw=t2n(sw),
+                w_fake=t2n(lin.optimizer.weight_manager.weight_tensor), bounds=np.array([0, K], dtype=np.int32))
+
+
+def gen_weight_seg_dual_int8(SegmentLinear, seed=3, M=4, K=128, N=192, S=6):
+    """The adaLN pattern: SiLU -> Linear -> chunk(6): N-segmented weights, DualScale int8 activations."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.nn.functional.silu(torch.randn(M, K, generator=g))
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    lin = SegmentLinear(K, N, bias=True, seg_mode="weight", chunks=S, custom_weight_tensor=w.clone(),
+                        custom_bias_tensor=b.clone(), input_quant_type="int8", weight_quant_type="int8",
+                        input_quant_args={"real_quant": False, "axis": None, "dual_scale": True},
+                        weight_quant_args={"real_quant": False, "axis": None},
+                        opt_type="default", opt_kwargs={}, calib_type="amax", calib_kwargs={}, device="cpu")
+    lin.calibrate(x.clone())
+    lin.finish_calibrate()
+    y = lin(x.clone())
+    sp, sn, sw = lin.optimizer.scale_tensor
+    return dict(x=t2n(x), w=t2n(w), b=t2n(b), y=t2n(y), sx_pos=t2n(sp), sx_neg=t2n(sn), sw=t2n(sw),
+                w_fake=t2n(lin.optimizer.weight_manager.weight_tensor), chunks=np.int32(S))
+
+
+def gen_quantizer_vectors(q, seed=4):
+    """Scale definitions and fake-quant outputs straight from the reference's quantizer classes."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    x = torch.randn(32, 64, generator=g) * 3
+    x[0, 0] = 0.0
+    iq = q.IntQuantizer(num_bits=8, axis=None)
+    iq.calibrate(x)
+    out["int8_x"] = t2n(x); out["int8_scale"] = t2n(iq.scale); out["int8_fake"] = t2n(iq.fake_quantize(x))
+    iqa = q.IntQuantizer(num_bits=8, axis=1)
+    iqa.calibrate(x)
+    out["int8_axis1_scale"] = t2n(iqa.scale); out["int8_axis1_fake"] = t2n(iqa.fake_quantize(x))
+    xs = torch.nn.functional.silu(torch.randn(32, 64, generator=g) * 2)
+    iqd = q.IntQuantizer(num_bits=8, axis=None, dual_scale=True)
+    iqd.calibrate(xs)
+    out["dual_x"] = t2n(xs); out["dual_int8_pos"] = t2n(iqd.pos_scale); out["dual_int8_neg"] = t2n(iqd.neg_scale)
+    out["dual_int8_fake"] = t2n(iqd.fake_quantize(xs))
+    fq = q.FloatQuantizer(axis=None)
+    fq.calibrate(x)
+    out["fp8_scale"] = t2n(fq.scale); out["fp8_fake"] = t2n(fq.fake_quantize(x))
+    fqd = q.FloatQuantizer(axis=None, dual_scale=True)
+    fqd.calibrate(xs)
+    out["dual_fp8_pos"] = t2n(fqd.pos_scale); out["dual_fp8_neg"] = t2n(fqd.neg_scale)
+    out["dual_fp8_fake"] = t2n(fqd.fake_quantize(xs))
+    # int4 group-wise weights: IntQuantizer(num_bits=4, axis=-1) on W.view(N, K/g, g)
+    w = torch.randn(24, 256, generator=g) * 0.02
+    i4 = q.IntQuantizer(num_bits=4, axis=-1)
+    wg = w.view(24, 2, 128)
+    i4.calibrate(wg)
+    out["int4_w"] = t2n(w); out["int4_group_scale"] = t2n(i4.scale); out["int4_group_fake"] = t2n(i4.fake_quantize(wg).view(24, 256))
+    # dynamic per-token int8: IntQuantizer(axis=-1, dynamic=True).quantize
+    dq = q.IntQuantizer(num_bits=8, axis=-1, dynamic=True)
+    out["dyn_fake"] = t2n(dq.quantize(x)); out["dyn_scale"] = t2n(dq.scale)
+    xb = x.to(torch.bfloat16)
+    dqb = q.IntQuantizer(num_bits=8, axis=-1, dynamic=True)
+    dqb.quantize(xb)
+    out["dyn_scale_bf16"] = t2n(dqb.scale)
+    # fp8 round trip on a grid of values (the reference's compiled fake_e4m3fy)
+    grid = torch.cat([torch.linspace(-500, 500, 4001), torch.logspace(-12, 3, 600), -torch.logspace(-12, 3, 600)]).float()
+    out["e4m3_grid"] = t2n(grid)
+    out["e4m3_roundtrip"] = t2n(q.load_fake_quant_fp8_ext().fake_e4m3fy(grid.contiguous()))
+    return out
+
+
+def main():
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    torch.set_num_threads(1)  # deterministic reductions
+    SegmentLinear, q = import_reference(root)
+    fixtures = {
+        "input_seg_int8": gen_input_seg_int8(SegmentLinear),
+        "dual_fp8": gen_dual_fp8(SegmentLinear),
+        "weight_seg_dual_int8": gen_weight_seg_dual_int8(SegmentLinear),
+        "quantizers": gen_quantizer_vectors(q),
+    }
+    for name, d in fixtures.items():
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **d)
+        print(f"wrote {path} ({os.path.getsize(path) / 1024:.1f} KB): {sorted(d)}")
+
+
+if __name__ == "__main__":
+    main()
