@@ -67,7 +67,7 @@ uint8_t sqo_e4m3_from_float(float f) {
     uint32_t bits;
     memcpy(&bits, &f, 4);
     const uint8_t sign = (uint8_t)((bits >> 24) & 0x80u);
-    if (isnan(f)) return (uint8_t)(sign | 0x7F);
+    if (isnan(f)) return 0x7F; /* the hardware conversion yields the positive NaN code for every NaN */
     double a = fabs((double)f);
     if (a >= 448.0) return (uint8_t)(sign | 0x7E); /* saturate (also +-inf) */
     if (a == 0.0) return sign;

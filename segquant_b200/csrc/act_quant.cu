@@ -118,8 +118,15 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
 
 // Dynamic per-token scales: one warp per (row, segment).  Pass 1 reduces |x| (or the positive and
 // negative extremes) with warp shuffles, pass 2 re-reads the row segment (at most 24 KB, an L1/L2
-// hit) and quantises.  The scale is rounded to the dtype of x because the reference computes
-// qmax / amax on a tensor of that dtype (segquant/quantizers/quantizer.py:209-217, :187-203).
+// hit) and quantises.  The reference computes `qmax / amax` on a tensor of x's dtype
+// (segquant/quantizers/quantizer.py:209-217, :187-203), and torch evaluates scalar / tensor as
+// tensor.reciprocal() * scalar: two roundings to that dtype, reproduced here.
+template <typename T>
+__device__ __forceinline__ float scale_like_torch(float qmax, float amax) {
+    const float r = to_float<T>(from_float<T>(__frcp_rn(amax)));
+    return to_float<T>(from_float<T>(r * qmax));
+}
+
 template <typename T, int OUT, bool DUAL>
 __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_constant__ ActQuantParams p) {
     const int lane = threadIdx.x & 31;
@@ -161,9 +168,9 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             if constexpr (DUAL) nmax = fmaxf(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
         }
-        const float sc = to_float<T>(from_float<T>(kQmax / fmaxf(amax, kEps)));
+        const float sc = scale_like_torch<T>(kQmax, fmaxf(amax, kEps));
         float scn = 0.0f;
-        if constexpr (DUAL) scn = to_float<T>(from_float<T>(kQminAbs / fmaxf(nmax, kEps)));
+        if constexpr (DUAL) scn = scale_like_torch<T>(kQminAbs, fmaxf(nmax, kEps));
         if (lane == 0) {
             p.sx_out[(b * p.num_segs + s) * p.M + r] = sc;
             if constexpr (DUAL) p.sx_neg_out[(b * p.num_segs + s) * p.M + r] = scn;
@@ -187,6 +194,8 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
 
 static int validate(const sq_act_quant_args* a, bool dynamic) {
     SQ_REQUIRE(a != nullptr, SQ_ERR_INVALID_ARG, "sq_quantize_act: args is NULL");
+    SQ_REQUIRE(a->batch >= 0 && a->M >= 0 && a->K >= 0, SQ_ERR_INVALID_ARG, "sq_quantize_act: negative size");
+    if (a->batch * a->M * a->K == 0) return SQ_OK;  // nothing to do: pointers may be NULL
     SQ_REQUIRE(a->x_dev && a->xq_dev, SQ_ERR_INVALID_ARG, "sq_quantize_act: x_dev / xq_dev is NULL");
     SQ_REQUIRE(dynamic || a->sx_dev, SQ_ERR_INVALID_ARG, "sq_quantize_act: sx_dev is NULL");
     SQ_REQUIRE(a->batch >= 0 && a->M >= 0 && a->K >= 0, SQ_ERR_INVALID_ARG, "sq_quantize_act: negative size");

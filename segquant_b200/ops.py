@@ -77,6 +77,8 @@ def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=Fal
     dual = sx_neg is not None
     xq = out if out is not None else torch.empty((B, M, K), dtype=torch.uint8, device=x.device)
     xqn = (out_neg if out_neg is not None else torch.empty((B, M, K), dtype=torch.uint8, device=x.device)) if dual else None
+    if x.numel() == 0:
+        return xq, xqn
     a = L.ActQuantArgs()
     a.x_dev = x.data_ptr()
     a.x_dtype = _dt(x)
