@@ -107,14 +107,17 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// Bounded wait: gives up after ~2 s (or as soon as another role has raised the abort flag).
-__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    const unsigned long long t0 = global_timer_ns();
-    for (uint32_t it = 0;; ++it) {
+// Bounded wait: gives up after ~4e9 SM cycles (about 2 s), or as soon as another role has raised the
+// abort flag.  The timeout uses the SM-local cycle counter: reading %globaltimer costs microseconds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u) {
+        if ((it & 1023u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > 2000000000ull) {
+            if (clock64() - t0 > 4000000000ll) {
                 atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
                 *abort_flag = 1;
                 __threadfence_block();
@@ -122,12 +125,6 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
             }
         }
     }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-#pragma unroll 1
-    for (int it = 0; it < 64; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, code);
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -194,18 +191,13 @@ template <uint32_t N>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
-// 128-byte swizzle (what TMA SWIZZLE_128B writes): 8-row groups are 1024 bytes apart (SBO), the
-// leading-dimension offset is unused for swizzled K-major layouts, version 1 = Blackwell,
-// layout type 2 = SWIZZLE_128B.  `addr` is the shared address of element (row 0, k 0 of this MMA).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
-    d |= static_cast<uint64_t>(1) << 16;            // LBO (ignored)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;    // SBO
-    d |= static_cast<uint64_t>(1) << 46;            // descriptor version
-    d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
-    return d;
-}
+// 128-byte swizzle (what TMA SWIZZLE_128B writes).  Low word: start address >> 4 (14 bits) and the
+// leading-dimension offset (unused for swizzled K-major layouts, set to 1).  High word: 8-row groups
+// are 1024 bytes apart (SBO = 64), descriptor version 1 = Blackwell (bit 46), layout type 2 =
+// SWIZZLE_128B (bits 61-63).  Stepping K by one MMA (32 bytes) adds 2 to the low word.
+constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint64_t smem_desc(uint32_t lo) { return (static_cast<uint64_t>(kSmemDescHi) << 32) | lo; }
 
 // Instruction descriptor: dense, no negate, both operands K-major, D = 128 x 256.
 template <int KIND>
@@ -353,10 +345,12 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (warp < 4) {
         // ------------------------------------------------------------------ producer / MMA warps
+        // Each role's whole warp walks the (warp-uniform) loops and polls the barriers; lane 0 issues.
         reg_dec<kW4 ? 40 : 56>();
-        if (warp == 0 && lane == 0) {
+        if (warp == 0) {
             // ===== TMA producer =====
-            uint32_t it = 0;  // running stage counter
+            int st = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
                 const int b = static_cast<int>(tile / tiles_per_batch);
@@ -366,25 +360,28 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int ab = p.a_batched ? b : 0;
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    for (int k = k_beg; k < k_end; k += BK, ++it) {
-                        const int st = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1u;
+                    const int wb = p.w_seg_as_batch ? s : b;
+                    const int wk_off = p.w_seg_as_batch ? k_beg : 0;
+                    for (int k = k_beg; k < k_end; k += BK) {
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
-                        const uint32_t full = smem_u32(&bar_full[st]);
-                        mbar_arrive_expect_tx(full, C::kTxBytes);
-                        tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
-                        if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
-                        const int wk = p.w_seg_as_batch ? (k - k_beg) : k;
-                        const int wb = p.w_seg_as_batch ? s : b;
-                        if (kW4) tma_load_3d(stage_bp(st), &map_w, wk >> 1, n0, wb, full);
-                        else tma_load_3d(stage_b(st), &map_w, wk, n0, wb, full);
+                        if (lane == 0) {
+                            const uint32_t full = smem_u32(&bar_full[st]);
+                            mbar_arrive_expect_tx(full, C::kTxBytes);
+                            tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
+                            if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
+                            if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
+                            else tma_load_3d(stage_b(st), &map_w, k - wk_off, n0, wb, full);
+                        }
+                        __syncwarp();
+                        if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
                 }
             }
-        } else if (warp == 1 && lane == 0) {
+        } else if (warp == 1) {
             // ===== MMA issuer =====
             constexpr uint32_t idesc = make_idesc<KIND>();
-            uint32_t it = 0;   // stage counter
+            int st = 0;
+            uint32_t ph = 0;
             uint32_t au = 0;   // accumulation-unit counter (selects the TMEM buffer)
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
@@ -393,41 +390,59 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     int u_end = k_beg;  // forces "new unit" at the first step of the segment
                     uint32_t accumulate = 0;
                     uint32_t d_pos = 0, d_neg = 0;
-                    for (int kb = k_beg; ok && kb < k_end; kb += BK, ++it) {
-                        const int st = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1u;
+                    for (int kb = k_beg; ok && kb < k_end; kb += BK) {
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
                         if (kW4) {
                             if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
                         }
                         tc_fence_after();
+                        const uint32_t a_lo = smem_desc_lo(stage_a(st));
+                        const uint32_t an_lo = smem_desc_lo(stage_an(st));
+                        const uint32_t b_lo = smem_desc_lo(stage_b(st));
                         const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
-                        for (int kk = 0; kk < kmax; kk += UMMA_K) {
-                            const int k = kb + kk;
-                            if (k == u_end) {
-                                // unit boundary: hand the finished buffer to the epilogue, take the next one
-                                if (k != k_beg) {
-                                    umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));
+                        if (kb != u_end && kb + kmax <= u_end) {
+                            // the whole stage lies inside the current unit: no checks between the MMAs
+                            if (lane == 0) {
+#pragma unroll
+                                for (int i = 0; i < BK / UMMA_K; ++i) {
+                                    if (i * UMMA_K < kmax) {
+                                        const uint64_t db = smem_desc(b_lo + 2 * i);
+                                        umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
+                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
+                                    }
                                 }
-                                const uint32_t buf = DUAL ? 0u : (au & 1u);
-                                const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
-                                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
-                                tc_fence_after();
-                                d_pos = tmem_base + buf * BN;
-                                d_neg = tmem_base + BN;
-                                accumulate = 0;
-                                u_end = unit_end(p, s, k);
-                                ++au;
                             }
-                            const uint64_t db = make_smem_desc(stage_b(st) + kk);
-                            umma<KIND>(d_pos, make_smem_desc(stage_a(st) + kk), db, idesc, accumulate);
-                            if (DUAL) umma<KIND>(d_neg, make_smem_desc(stage_an(st) + kk), db, idesc, accumulate);
-                            accumulate = 1;
+                        } else {
+                            for (int kk = 0; kk < kmax; kk += UMMA_K) {
+                                const int k = kb + kk;
+                                if (k == u_end) {
+                                    // unit boundary: hand the finished buffer to the epilogue, take the next one
+                                    if (k != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));
+                                    const uint32_t buf = DUAL ? 0u : (au & 1u);
+                                    const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
+                                    if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                                    tc_fence_after();
+                                    d_pos = tmem_base + buf * BN;
+                                    d_neg = tmem_base + BN;
+                                    accumulate = 0;
+                                    u_end = unit_end(p, s, k);
+                                    ++au;
+                                }
+                                if (lane == 0) {
+                                    const uint64_t db = smem_desc(b_lo + (kk >> 4));
+                                    umma<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
+                                    if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
+                                }
+                                accumulate = 1;
+                            }
+                            if (!ok) break;
                         }
-                        if (!ok) break;
-                        umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
+                        if (lane == 0) umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
+                        __syncwarp();
+                        if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
-                    if (ok) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));  // last unit of the segment
+                    if (ok && lane == 0) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));  // last unit of the segment
+                    __syncwarp();
                 }
             }
         }
