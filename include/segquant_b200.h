@@ -208,6 +208,28 @@ int sq_gemm_num_units(int32_t num_segs, const int32_t* seg_bounds, int32_t group
  */
 int sq_seg_linear(const sq_act_quant_args* q, const sq_gemm_args* g, sq_stream_t stream);
 
+/* ---- fused layer forward without any device allocation -------------------------------------------
+ * No counterpart in the reference (its host pipeline allocates scratch tensors on every call).
+ *
+ * Same computation as sq_seg_linear, for callers that cannot supply the scratch buffer because they
+ * are not allowed to allocate device memory at all -- e.g. a plugin inside a serving process that
+ * froze its device-memory budget at start-up, or a latency-critical loop barred from the allocator.
+ * The quantised activations go to a fixed array of SQ_STATIC_SCRATCH_BYTES that is part of the
+ * library image (each GPU that loads the library holds it until the process exits); q->xq_dev /
+ * q->xq_neg_dev are ignored.  DualScale is selected by q->sx_neg_dev != NULL and needs twice the
+ * space: batch*M*K (x2) rounded up to 256 must fit, otherwise SQ_ERR_TOO_LARGE is returned and
+ * nothing is launched.  The call itself allocates nothing (no cudaMalloc / cudaFree, no allocating
+ * library routine).
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call before starting any stream capture.
+ * All calls share the one array, and it keeps whatever the last call left there: two calls whose GPU
+ * work can overlap (different streams, or different host threads) race on it and must be ordered by
+ * the caller.  Nothing in it needs to be cleared between calls.
+ */
+#define SQ_STATIC_SCRATCH_BYTES (64u * 1024u * 1024u)
+int sq_seg_linear_static(const sq_act_quant_args* q, const sq_gemm_args* g, sq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

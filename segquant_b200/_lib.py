@@ -7,6 +7,7 @@ import ctypes
 import os
 
 SQ_MAX_SEGS = 64
+SQ_STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
 SQ_OK = 0
 SQ_ERR_INVALID_ARG = -1
@@ -127,6 +128,8 @@ def load():
     lib.sq_gemm_num_units.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]
     lib.sq_seg_linear.restype = ctypes.c_int
     lib.sq_seg_linear.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.POINTER(GemmArgs), ctypes.c_void_p]
+    lib.sq_seg_linear_static.restype = ctypes.c_int
+    lib.sq_seg_linear_static.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.POINTER(GemmArgs), ctypes.c_void_p]
     _LIB = lib
     return lib
 

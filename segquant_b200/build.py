@@ -15,7 +15,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsegquant_b200.so")
-SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu"]
+SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu", "static_scratch.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "segquant_b200.h")]
 
 NVCC_FLAGS = [
