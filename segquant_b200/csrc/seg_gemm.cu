@@ -28,12 +28,14 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace sq {
 
 constexpr int BM = 128;        // tile rows (TMEM lanes)
-constexpr int BN = 256;        // tile columns (TMEM columns per buffer)
+constexpr int BN = 256;        // widest tile (TMEM columns per buffer); the width in use is GemmParams::bn
 constexpr int BK = 128;        // K elements per pipeline stage (= one 128-byte swizzle row)
 constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
 constexpr int kTmemCols = 512;
@@ -74,6 +76,8 @@ struct GemmParams {
     int units;
     int tiles_m, tiles_n;
     long long total_tiles;
+    int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
+    int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -199,7 +203,7 @@ constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ uint64_t smem_desc(uint32_t lo) { return (static_cast<uint64_t>(kSmemDescHi) << 32) | lo; }
 
-// Instruction descriptor: dense, no negate, both operands K-major, D = 128 x 256.
+// Instruction descriptor: dense, no negate, both operands K-major, D = 128 x bn.
 template <int KIND>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
     uint32_t d = 0;
@@ -212,8 +216,7 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
         d |= 1u << 7;   // A = signed 8-bit
         d |= 1u << 10;  // B = signed 8-bit
     }
-    d |= static_cast<uint32_t>(BN >> 3) << 17;
-    d |= static_cast<uint32_t>(BM >> 4) << 24;
+    d |= static_cast<uint32_t>(BM >> 4) << 24;   // the N field (bits 17-22) is added at run time: bn >> 3
     return d;
 }
 
@@ -356,7 +359,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int b = static_cast<int>(tile / tiles_per_batch);
                 const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
                 const int m0 = (rem / p.tiles_n) * BM;
-                const int n0 = (rem % p.tiles_n) * BN;
+                const int n0 = (rem % p.tiles_n) * p.bn;
                 const int ab = p.a_batched ? b : 0;
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
@@ -366,7 +369,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
                         if (lane == 0) {
                             const uint32_t full = smem_u32(&bar_full[st]);
-                            mbar_arrive_expect_tx(full, C::kTxBytes);
+                            mbar_arrive_expect_tx(full, kABytes * (DUAL ? 2 : 1) + static_cast<uint32_t>(p.bn) * (kW4 ? BK / 2 : BK));
                             tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
                             if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
                             if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
@@ -379,10 +382,12 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         } else if (warp == 1) {
             // ===== MMA issuer =====
-            constexpr uint32_t idesc = make_idesc<KIND>();
+            const uint32_t idesc = make_idesc<KIND>() | (static_cast<uint32_t>(p.bn >> 3) << 17);
+            const bool one_buf = DUAL && !p.dual_db;   // DualScale with wide tiles: pos / neg fill all of TMEM
             int st = 0;
             uint32_t ph = 0;
-            uint32_t au = 0;   // accumulation-unit counter (selects the TMEM buffer)
+            uint32_t au = 0;       // accumulation-unit counter (selects the TMEM buffer)
+            uint32_t cur_buf = 0;  // buffer of the unit being accumulated
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
                 for (int s = 0; ok && s < p.num_segs; ++s) {
@@ -417,13 +422,14 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 const int k = kb + kk;
                                 if (k == u_end) {
                                     // unit boundary: hand the finished buffer to the epilogue, take the next one
-                                    if (k != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));
-                                    const uint32_t buf = DUAL ? 0u : (au & 1u);
-                                    const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
+                                    if (k != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
+                                    const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
                                     if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
                                     tc_fence_after();
+                                    cur_buf = buf;
                                     d_pos = tmem_base + buf * BN;
-                                    d_neg = tmem_base + BN;
+                                    d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
                                     accumulate = 0;
                                     u_end = unit_end(p, s, k);
                                     ++au;
@@ -441,7 +447,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         __syncwarp();
                         if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
-                    if (ok && lane == 0) umma_commit(smem_u32(&bar_tmem_full[DUAL ? 0 : ((au - 1) & 1u)]));  // last unit of the segment
+                    if (ok && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));  // last unit of the segment
                     __syncwarp();
                 }
             }
@@ -453,13 +459,16 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;                      // TMEM lane quarter of this warp
         const int h = (warp - 4) >> 2;               // column half
         const bool per_token = p.sx_rs != 0;
+        const bool one_buf = DUAL && !p.dual_db;
+        const int hcols = p.bn >> 1;                 // columns per warpgroup: 64, 96 or 128
+        const int nch = hcols >> 4;                  // 16-column chunks per thread
         uint32_t au = 0;
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
             const int b = static_cast<int>(tile / tiles_per_batch);
             const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
             const int m0 = (rem / p.tiles_n) * BM;
-            const int n0 = (rem % p.tiles_n) * BN;
+            const int n0 = (rem % p.tiles_n) * p.bn;
             const long long m = m0 + q * 32 + lane;
             const bool row_ok = m < p.M;
 
@@ -478,7 +487,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     {
                         const long long n = n0 + epi_tid;
                         float r = 0.0f, rn = 0.0f;
-                        if (n < p.N) {
+                        if (n < p.N && epi_tid < p.bn) {
                             const float swv = load_sw(p, b * p.sw_bs + s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
                             const float sxv = per_token ? 1.0f : __ldg(p.sx + b * p.sx_bs + s * p.sx_ss);
                             r = 1.0f / (sxv * swv);
@@ -500,21 +509,22 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         rxm = 1.0f / __ldg(p.sx + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
                         if (DUAL) rxnm = 1.0f / __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
                     }
-                    const uint32_t buf = DUAL ? 0u : (au & 1u);
-                    const uint32_t tph = DUAL ? (au & 1u) : ((au >> 1) & 1u);
+                    const uint32_t buf = one_buf ? 0u : (au & 1u);
+                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
                     if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * 128;
-                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + BN + h * 128;
-                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * 128;
-                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * 128;
+                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
+                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (p.dual_db ? buf * BN + 128 : BN) + h * hcols;
+                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * hcols;
+                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * hcols;
                     int32_t* dump = nullptr;
                     if (p.acc_dump != nullptr && row_ok) {
                         const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
-                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * 128;
+                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * hcols;
                     }
 #pragma unroll
                     for (int ch = 0; ch < 8; ++ch) {
+                        if (ch >= nch) break;
                         uint32_t v[16];
                         tmem_ld_x16(t_pos + ch * 16, v);
                         tmem_ld_wait();
@@ -528,7 +538,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (dump != nullptr) {
 #pragma unroll 1
                             for (int j = 0; j < 16; ++j)
-                                if (n0 + h * 128 + ch * 16 + j < p.N)
+                                if (n0 + h * hcols + ch * 16 + j < p.N)
                                     dump[ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
                         }
                         if (DUAL) {
@@ -544,7 +554,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (dump != nullptr) {
 #pragma unroll 1
                                 for (int j = 0; j < 16; ++j)
-                                    if (n0 + h * 128 + ch * 16 + j < p.N)
+                                    if (n0 + h * hcols + ch * 16 + j < p.N)
                                         dump[p.M * p.N + ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
                             }
                         }
@@ -558,9 +568,9 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
             if (!ok) break;
-            // ---- bias, cast, store (one row of 128 consecutive columns per thread)
+            // ---- bias, cast, store (one row of up to 128 consecutive columns per thread)
             if (row_ok) {
-                const long long ncol0 = n0 + h * 128;
+                const long long ncol0 = n0 + h * hcols;
                 const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
                 uint8_t* yrow = static_cast<uint8_t*>(p.y) + (b * p.y_bs + m * p.y_rs + ncol0) * esz;
                 const bool vec_ok = (reinterpret_cast<uintptr_t>(yrow) & 15u) == 0;
@@ -569,7 +579,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const long long nc = ncol0 + ch * 16;
                     int valid = static_cast<int>(p.N - nc);
                     valid = valid > 16 ? 16 : valid;
-                    if (valid > 0) {
+                    if (valid > 0 && ch < nch) {
                         float o[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
@@ -602,10 +612,11 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
                         const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
                         uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
-                        // staging tile: 256 rows x 64 packed bytes; 16-byte chunk c = (row, quarter)
+                        // staging tile: bn rows x 64 packed bytes; 16-byte chunk c = (row, quarter)
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int c = ct + i * 128;
+                            if (c >= p.bn * 4) break;
                             const int row = c >> 2, qd = c & 3;
                             const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
                             const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
@@ -690,6 +701,28 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
                static_cast<int>(r), (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch,
                (unsigned long long)row_stride, (unsigned long long)batch_stride);
     return SQ_OK;
+}
+
+// Tile width against wave quantisation: the persistent grid runs ceil(tiles / 148) rounds, a round
+// costs about (bn + fixed) per tile; narrow tiles re-read more operands, which the fixed term also
+// stands for.  SEGQUANT_B200_BN=128|192|256 forces a width (tuning aid).
+static int pick_tile_width(long long row_tiles, long long N, bool dual) {
+    if (const char* env = getenv("SEGQUANT_B200_BN")) {
+        const int v = atoi(env);
+        if (v == 128 || v == 192 || v == 256) return v;
+    }
+    const int widths[3] = {256, 192, 128};
+    int best = 256;
+    double best_cost = 1e300;
+    for (int w : widths) {
+        const long long tiles = row_tiles * ((N + w - 1) / w);
+        const long long rounds = (tiles + kNumSMs - 1) / kNumSMs;
+        double per_tile = w + 40.0;
+        if (dual && w > 128) per_tile += 0.08 * w;  // epilogue of a wide DualScale tile is not overlapped
+        const double cost = static_cast<double>(rounds) * per_tile;
+        if (cost < best_cost * 0.97) { best_cost = cost; best = w; }
+    }
+    return best;
 }
 
 int gemm_num_units(int num_segs, const int* seg_bounds, int group_size) {
@@ -798,7 +831,9 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.y = a->y_dev; p.out_dtype = a->out_dtype; p.y_bs = a->y_batch_stride; p.y_rs = a->y_row_stride;
     p.acc_dump = a->acc_dump_dev; p.units = units;
     p.tiles_m = static_cast<int>((a->M + BM - 1) / BM);
-    p.tiles_n = static_cast<int>((a->N + BN - 1) / BN);
+    p.bn = pick_tile_width(static_cast<long long>(p.tiles_m) * a->batch, a->N, dual);
+    p.dual_db = (dual && p.bn <= 128) ? 1 : 0;
+    p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
     if (a->bias_dev)
         SQ_REQUIRE(a->bias_dtype == SQ_F32 || a->bias_dtype == SQ_F16 || a->bias_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
@@ -824,8 +859,8 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
         // describe `batch` copies 0 bytes apart is not encodable; fold by pointing all at copy 0
         SQ_REQUIRE(false, SQ_ERR_UNSUPPORTED, "sq_gemm: batched problems need their own weights (wq_batch_stride != 0)");
     }
-    if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, BN, false, "wq(int4)");
-    else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, BN, true, "wq");
+    if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, p.bn, false, "wq(int4)");
+    else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, p.bn, true, "wq");
     if (rc != SQ_OK) return rc;
 
     if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch<SQ_GEMM_W8A8_I8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W8A8_I8, false>(ma, man, mw, p, st);
