@@ -189,6 +189,8 @@ def run_ours(args):
     def step(i, ev=None):
         r = i % ROTATE
         f = fused[r]
+        if ev is not None:
+            ev[2].record()
         ops.quantize_act(xs[r], f["bounds"], f["sx"], f["sx_neg"], a_kind, out=xq[r], out_neg=xqn[r])
         if ev is not None:
             ev[0].record()
@@ -211,7 +213,7 @@ def run_ours(args):
         time.sleep(0.25)
     barrier()
     launches0 = ops.launch_count
-    gemm_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    gemm_events = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(3)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -220,12 +222,14 @@ def run_ours(args):
     barrier()
     launches = ops.launch_count - launches0
     ms_total = e0.elapsed_time(e1)
-    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events) / args.steps
-    t = torch.tensor([ms_total, gemm_ms], dtype=torch.float64, device=dev)
+    gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events) / args.steps
+    quant_ms = sum(c.elapsed_time(a) for a, _, c in gemm_events) / args.steps
+    t = torch.tensor([ms_total, gemm_ms, quant_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = t[0].item() / args.steps
     gemm_ms = t[1].item()
+    quant_ms = t[2].item()
 
     # ---- end to end through the public layer API with host buffers
     host_x = [x.cpu().pin_memory() for x in xs]
@@ -302,6 +306,9 @@ def run_ours(args):
             "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": 2.0 * M * N * K * world / e2e_ms / 1e9, "unit": "TOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
+            "kernels": {"act_quant_ms": quant_ms, "act_quant_gbs": M * K * 4 / quant_ms / 1e6,
+                        "act_quant_note": "algorithmic bytes M*K*(2 in + 2 out) per launch / mean CUDA-event time",
+                        "seg_gemm_ms": gemm_ms},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
         }
         if sharded:

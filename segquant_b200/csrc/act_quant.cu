@@ -5,8 +5,8 @@
 // of segquant/src/real_quant/quantizer.cuh:159-206 (4 scalar elements per thread, a div/mod per
 // element) and the `.contiguous()` segment copy in segquant/optimum/optimizer.py:105.
 //
-// Work split: one warp walks one row; lane l takes the 16-element chunks l, l+32, ... so every
-// store instruction of a warp writes 512 contiguous bytes.
+// Work split: one warp walks one row, one 128-bit load per lane and step, eight loads in flight per
+// lane; the dynamic per-token kernel gives one warp to a (row, segment).
 #include "common.cuh"
 
 namespace sq {
@@ -52,65 +52,151 @@ __device__ __forceinline__ uint4 pack16(const float (&v)[16]) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// DualScale: element >= 0 -> positive tensor (other side gets quantise(0) = byte 0), else the
-// negative tensor (quantizer.cuh:178-206).  The byte of a quantised +0.0f is 0 in both formats.
+// DualScale (dynamic kernel): element >= 0 -> positive tensor, else the negative tensor
+// (quantizer.cuh:178-206); the side an element does not belong to gets quantise(+0) = byte 0.
 template <int OUT>
 __device__ __forceinline__ void pack16_dual(const float (&x)[16], float sp, float sn, uint4& outp, uint4& outn) {
-    uint32_t wp[4] = {0, 0, 0, 0}, wn[4] = {0, 0, 0, 0};
+    float vp[16], vn[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const bool pos = x[i] >= 0.0f;
-        const float scaled = x[i] * (pos ? sp : sn);
-        const uint32_t q = (OUT == SQ_Q_INT8) ? quant_int8(scaled) : quant_e4m3(scaled);
-        const uint32_t sh = (i & 3) * 8;
-        wp[i >> 2] |= (pos ? q : 0u) << sh;
-        wn[i >> 2] |= (pos ? 0u : q) << sh;
+        vp[i] = pos ? x[i] * sp : 0.0f;
+        vn[i] = pos ? 0.0f : x[i] * sn;
     }
-    outp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-    outn = make_uint4(wn[0], wn[1], wn[2], wn[3]);
+    outp = pack16<OUT>(vp);
+    outn = pack16<OUT>(vn);
+}
+
+// ---- static-scale kernel ---------------------------------------------------------------------
+// Work unit = one 128-bit load = E elements (4 fp32 or 8 half/bf16).  One warp walks one row; lane l
+// takes units l, l+32, ... so every load and store instruction of a warp is fully coalesced, and U
+// independent loads per lane are issued before any of them is consumed.
+
+// int8 bytes of four already scaled values: clamp, then round to nearest even by adding 1.5 * 2^23
+// (the integer lands in the low mantissa bits; same result as rintf, without a float->int convert).
+__device__ __forceinline__ uint32_t quant_int8x4(float a, float b, float c, float d) {
+    constexpr float kMagic = 12582912.0f;
+    const uint32_t ia = __float_as_uint(fminf(fmaxf(a, -128.0f), 127.0f) + kMagic);
+    const uint32_t ib = __float_as_uint(fminf(fmaxf(b, -128.0f), 127.0f) + kMagic);
+    const uint32_t ic = __float_as_uint(fminf(fmaxf(c, -128.0f), 127.0f) + kMagic);
+    const uint32_t id = __float_as_uint(fminf(fmaxf(d, -128.0f), 127.0f) + kMagic);
+    return __byte_perm(__byte_perm(ia, ib, 0x0040), __byte_perm(ic, id, 0x0040), 0x5410);
+}
+
+template <int OUT>
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d) {
+    if constexpr (OUT == SQ_Q_INT8) return quant_int8x4(a, b, c, d);
+    else return quant_e4m3x2(a, b) | (quant_e4m3x2(c, d) << 16);
+}
+
+template <typename T>
+struct Unit;   // one 128-bit load, kept as raw words until it is consumed (4 registers per load in flight)
+template <>
+struct Unit<float> {
+    static constexpr int E = 4;
+    __device__ static __forceinline__ void unpack(const uint4& t, float (&v)[4]) {
+        v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y); v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+    }
+};
+template <>
+struct Unit<__half> {
+    static constexpr int E = 8;
+    __device__ static __forceinline__ void unpack(const uint4& t, float (&v)[8]) {
+        const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+    }
+};
+template <>
+struct Unit<__nv_bfloat16> {
+    static constexpr int E = 8;
+    __device__ static __forceinline__ void unpack(const uint4& t, float (&v)[8]) {
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+    }
+};
+
+template <int OUT, bool DUAL, int E>
+__device__ __forceinline__ void quant_store(const float (&x)[E], float sp, float sn, uint8_t* q, uint8_t* qn) {
+    uint32_t wp[E / 4], wn[E / 4];
+    if constexpr (!DUAL) {
+#pragma unroll
+        for (int i = 0; i < E / 4; ++i) wp[i] = quant4<OUT>(x[4 * i] * sp, x[4 * i + 1] * sp, x[4 * i + 2] * sp, x[4 * i + 3] * sp);
+    } else {
+        float vp[E], vn[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const bool pos = x[i] >= 0.0f;
+            vp[i] = pos ? x[i] * sp : 0.0f;
+            vn[i] = pos ? 0.0f : x[i] * sn;
+        }
+#pragma unroll
+        for (int i = 0; i < E / 4; ++i) {
+            wp[i] = quant4<OUT>(vp[4 * i], vp[4 * i + 1], vp[4 * i + 2], vp[4 * i + 3]);
+            wn[i] = quant4<OUT>(vn[4 * i], vn[4 * i + 1], vn[4 * i + 2], vn[4 * i + 3]);
+        }
+    }
+    if constexpr (E == 8) {
+        *reinterpret_cast<uint2*>(q) = make_uint2(wp[0], wp[1]);
+        if constexpr (DUAL) *reinterpret_cast<uint2*>(qn) = make_uint2(wn[0], wn[1]);
+    } else {
+        *reinterpret_cast<uint32_t*>(q) = wp[0];
+        if constexpr (DUAL) *reinterpret_cast<uint32_t*>(qn) = wn[0];
+    }
 }
 
 template <typename T, int OUT, bool DUAL, bool SMOOTH>
-__global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
+__global__ void __launch_bounds__(256, 4) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
+    constexpr int E = Unit<T>::E;
+    constexpr int U = 8;
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const long long rows = p.batch * p.M;
-    const int kch = static_cast<int>(p.K >> 4);
+    const int units = static_cast<int>(p.K / E);
     const T* __restrict__ x = static_cast<const T*>(p.x);
 
     for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < rows;
          row += static_cast<long long>(gridDim.x) * warps_per_cta) {
-        const long long b = row / p.M;
-        const long long r = row - b * p.M;
+        long long b = 0, r = row;
+        if (p.batch > 1) { b = row / p.M; r = row - b * p.M; }
         const T* xr = x + b * p.x_batch_stride + r * p.x_row_stride;
         const float* sxr = p.sx + b * p.sx_batch_stride + r * p.sx_row_stride;
         const float* sxnr = DUAL ? p.sx_neg + b * p.sx_batch_stride + r * p.sx_row_stride : nullptr;
         uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
 
-#pragma unroll 2
-        for (int c = lane; c < kch; c += 32) {
-            const int k = c << 4;
-            float v[16];
-            load16<T>(xr + k, v);
-            if constexpr (SMOOTH) {
-                float sm[16];
-                load16<float>(p.smooth + k, sm);
+        // segment cursor: this lane's k only grows, so the segment index only moves forward
+        int s = 0;
+        int next_bound = p.seg_bounds[1];
+        float sc = __ldg(sxr);
+        float scn = DUAL ? __ldg(sxnr) : 0.0f;
+
+        for (int u0 = lane; u0 < units; u0 += 32 * U) {
+            uint4 raw[U];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = v[i] / sm[i];
+            for (int j = 0; j < U; ++j) {
+                const int u = u0 + 32 * j;
+                if (u < units) raw[j] = __ldg(reinterpret_cast<const uint4*>(xr + u * E));
             }
-            const int s = find_segment(p, k);
-            const float sc = __ldg(sxr + s * p.sx_seg_stride);
-            if constexpr (!DUAL) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] *= sc;
-                *reinterpret_cast<uint4*>(qr + k) = pack16<OUT>(v);
-            } else {
-                const float scn = __ldg(sxnr + s * p.sx_seg_stride);
-                uint4 op, on;
-                pack16_dual<OUT>(v, sc, scn, op, on);
-                *reinterpret_cast<uint4*>(qr + k) = op;
-                *reinterpret_cast<uint4*>(qnr + k) = on;
+            for (int j = 0; j < U; ++j) {
+                const int u = u0 + 32 * j;
+                if (u >= units) break;
+                const int k = u * E;
+                float v[E];
+                Unit<T>::unpack(raw[j], v);
+                while (k >= next_bound) {
+                    ++s;
+                    next_bound = p.seg_bounds[s + 1];
+                    sc = __ldg(sxr + s * p.sx_seg_stride);
+                    if constexpr (DUAL) scn = __ldg(sxnr + s * p.sx_seg_stride);
+                }
+                if constexpr (SMOOTH) {
+#pragma unroll
+                    for (int i = 0; i < E; ++i) v[i] = v[i] / __ldg(p.smooth + k + i);
+                }
+                quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);
             }
         }
     }
