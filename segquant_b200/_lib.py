@@ -93,7 +93,8 @@ _LIB = None
 
 
 def lib_path():
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsegquant_b200.so")
+    """In-tree library, or the file named by SEGQUANT_B200_LIB (e.g. an instrumented build)."""
+    return os.environ.get("SEGQUANT_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsegquant_b200.so")
 
 
 def load():

@@ -41,15 +41,20 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False, ptxas_verbose=False):
-    """Compile every CUDA source for sm_100a and link the shared library in-tree."""
-    if not force and not needs_build():
+def build(force=False, verbose=False, ptxas_verbose=False, extra_flags=(), out=None):
+    """Compile every CUDA source for sm_100a and link the shared library in-tree.
+
+    extra_flags / out: build a variant (e.g. ["-DSQ_TRACE"]) into another file without touching the
+    product library."""
+    variant = out is not None
+    target = out or LIB_PATH
+    if not variant and not force and not needs_build():
         return LIB_PATH
     objs = []
     procs = []
     for s in SOURCES:
-        obj = os.path.join(CSRC, s.replace(".cu", ".o"))
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_verbose else []) + [
+        obj = os.path.join(CSRC, s.replace(".cu", ".variant.o" if variant else ".o"))
+        cmd = [_nvcc()] + NVCC_FLAGS + list(extra_flags) + (["-Xptxas", "-v"] if ptxas_verbose else []) + [
             "-c", os.path.join(CSRC, s), "-o", obj]
         if verbose:
             print(" ".join(cmd), flush=True)
@@ -66,11 +71,11 @@ def build(force=False, verbose=False, ptxas_verbose=False):
     if failed:
         raise RuntimeError("segquant_b200: CUDA compilation failed")
     link = [_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-            "-o", LIB_PATH] + objs
+            "-o", target] + objs
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("segquant_b200: link failed:\n" + r.stdout)
-    return LIB_PATH
+    return target
 
 
 if __name__ == "__main__":

@@ -44,6 +44,7 @@ constexpr int kEpiThreads = 256;
 constexpr uint32_t kABytes = BM * BK;          // 16 KB
 constexpr uint32_t kBBytes = BN * BK;          // 32 KB
 constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
+constexpr uint32_t kStoreStageBytes = 8 * 2048;  // output staging for TMA stores: 2 KB per epilogue warp
 
 // status-word codes (low byte = which wait, rest = block index)
 enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitEpi = 7 };
@@ -51,6 +52,20 @@ enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTm
 // Written (first writer wins) when a bounded wait gives up: (block index << 8) | WaitCode.
 // One copy per device that loads this library; read and cleared by read_device_status().
 __device__ unsigned long long g_wait_status = 0ull;
+
+// Timeline instrumentation, compiled in only with -DSQ_TRACE (never in the product library):
+// clock64() stamps of block 0's producer (role 0), MMA issuer (role 1) and first epilogue thread (role 2).
+#ifdef SQ_TRACE
+__device__ long long g_trace[3 * 4096];
+#define SQ_STAMP(role, idx) do { if (blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
+#else
+#define SQ_STAMP(role, idx) do { } while (0)
+#endif
+#ifdef SQ_TRACE_FINE
+#define SQ_FINE(slot) do { if (lane == 0 && blockIdx.x == 0 && trace_mma < 500) g_trace[2 * 4096 + 8 * trace_mma + (slot)] = clock64(); } while (0)
+#else
+#define SQ_FINE(slot) do { } while (0)
+#endif
 
 struct GemmParams {
     long long M, N, K;
@@ -76,6 +91,7 @@ struct GemmParams {
     int units;
     int tiles_m, tiles_n;
     long long total_tiles;
+    int y_tma;    // output goes through TMA stores (y base / strides are 16-byte aligned)
     int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
 };
@@ -232,7 +248,7 @@ struct Cfg {
     static constexpr uint32_t kTxBytes = kABytes * (DUAL ? 2 : 1) + (kW4 ? kBPackedBytes : kBBytes);
     // dynamic shared memory: 1 KB alignment slack + stages + scale tables (2 parities x 2 sides x BN floats)
     static constexpr uint32_t kTabBytes = 2 * 2 * BN * sizeof(float);
-    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + 256;
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
 };
 
 struct UnitCursor {
@@ -287,13 +303,97 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, long lon
     return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + idx));
 }
 
+// TMA store of a [rows x 16 columns] box from shared memory; out-of-range rows / columns are clipped.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+
+// Bias, cast and store of one thread's output row segment (up to 128 columns held in acc[]).
+// Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
+// chunk; the LSU stays free for the MMA / producer warps, every DRAM sector is written whole);
+// otherwise each thread writes its row directly.  `stage` is this warp's 2 KB staging area.
+__device__ __forceinline__ void store_output(const GemmParams& p, const CUtensorMap* map_y, const float (&acc)[128], int nch,
+                                             long long b, long long m, int m_warp, bool row_ok, long long ncol0,
+                                             uint8_t* stage, int lane) {
+    const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
+    if (p.y_tma) {
+        if (m_warp >= p.M) return;                           // nothing of this warp's 32 rows exists (warp-uniform)
+        const uint32_t stage_u32 = smem_u32(stage);
+        const uint32_t buf_bytes = 32u * 16u * esz;          // 1 KB (16-bit) or 2 KB (fp32)
+        const bool two_bufs = esz == 2;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+            const long long nc = ncol0 + ch * 16;
+            if (ch >= nch || nc >= p.N) break;
+            float o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
+            if (p.bias != nullptr) {
+                const long long bo = b * p.bias_bs + nc;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (nc + j < p.N) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
+            }
+            const uint32_t off = (two_bufs && (ch & 1)) ? buf_bytes : 0u;
+            // the buffer about to be overwritten must have been read by its previous TMA store
+            if (lane == 0) {
+                if (two_bufs) bulk_wait_read<1>();
+                else bulk_wait_read<0>();
+            }
+            __syncwarp();
+            uint8_t* dst = stage + off + lane * 16 * esz;
+            if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(dst), o, 16, true);
+            else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(dst), o, 16, true);
+            else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(dst), o, 16, true);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(map_y, stage_u32 + off, static_cast<int>(nc) * esz, m_warp, static_cast<int>(b));   // the map is byte-typed
+                bulk_commit();
+            }
+        }
+        return;
+    }
+    if (!row_ok) return;
+    uint8_t* yrow = static_cast<uint8_t*>(p.y) + (b * p.y_bs + m * p.y_rs + ncol0) * esz;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(yrow) & 15u) == 0;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+        const long long nc = ncol0 + ch * 16;
+        int valid = static_cast<int>(p.N - nc);
+        valid = valid > 16 ? 16 : valid;
+        if (valid > 0 && ch < nch) {
+            float o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
+            if (p.bias != nullptr) {
+                const long long bo = b * p.bias_bs + nc;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < valid) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
+            }
+            if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
+            else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
+            else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
 template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(Cfg<KIND, DUAL>::kThreads, 1)
 seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
-                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ GemmParams p) {
+                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+                const __grid_constant__ GemmParams p) {
     using C = Cfg<KIND, DUAL>;
     constexpr int kStages = C::kStages;
     constexpr bool kW4 = C::kW4;
@@ -352,6 +452,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         reg_dec<kW4 ? 40 : 56>();
         if (warp == 0) {
             // ===== TMA producer =====
+            int trace_it = 0; (void)trace_it;
             int st = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -368,6 +469,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int k = k_beg; k < k_end; k += BK) {
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
                         if (lane == 0) {
+                            SQ_STAMP(0, 2 * trace_it);
                             const uint32_t full = smem_u32(&bar_full[st]);
                             mbar_arrive_expect_tx(full, kABytes * (DUAL ? 2 : 1) + static_cast<uint32_t>(p.bn) * (kW4 ? BK / 2 : BK));
                             tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
@@ -375,6 +477,8 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
                             else tma_load_3d(stage_b(st), &map_w, k - wk_off, n0, wb, full);
                         }
+                        if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
+                        ++trace_it;
                         __syncwarp();
                         if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
@@ -388,6 +492,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t ph = 0;
             uint32_t au = 0;       // accumulation-unit counter (selects the TMEM buffer)
             uint32_t cur_buf = 0;  // buffer of the unit being accumulated
+            int trace_mma = 0; (void)trace_mma;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
                 for (int s = 0; ok && s < p.num_segs; ++s) {
@@ -396,11 +501,26 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     uint32_t accumulate = 0;
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BK) {
+                        SQ_FINE(0);
+#ifdef SQ_VAR_LANE0_POLL
+                        {   // experiment: only lane 0 polls, the others meet it at the warp barrier
+                            int got = 1;
+                            if (lane == 0) got = mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull) ? 1 : 0;
+                            got = __shfl_sync(0xffffffffu, got, 0);
+                            if (!got) { ok = false; break; }
+                        }
+#else
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
+#endif
                         if (kW4) {
                             if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
                         }
+                        SQ_FINE(1);
+#ifndef SQ_VAR_NOFENCE
                         tc_fence_after();
+#endif
+                        SQ_FINE(2);
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
                         const uint32_t a_lo = smem_desc_lo(stage_a(st));
                         const uint32_t an_lo = smem_desc_lo(stage_an(st));
                         const uint32_t b_lo = smem_desc_lo(stage_b(st));
@@ -414,6 +534,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                         const uint64_t db = smem_desc(b_lo + 2 * i);
                                         umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
                                         if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
+                                        SQ_FINE(3 + i);
                                     }
                                 }
                             }
@@ -443,7 +564,11 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             }
                             if (!ok) break;
                         }
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 1);
                         if (lane == 0) umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 2);
+                        SQ_FINE(7);
+                        ++trace_mma;
                         __syncwarp();
                         if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
@@ -513,6 +638,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
                     if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
                     tc_fence_after();
+                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
                     const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
                     const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (p.dual_db ? buf * BN + 128 : BN) + h * hcols;
                     const float* rt_pos = rtab + (par * 2 + 0) * BN + h * hcols;
@@ -524,16 +650,26 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
 #pragma unroll
                     for (int ch = 0; ch < 8; ++ch) {
+#ifdef SQ_VAR_EPI_EMPTY
+                        break;   // experiment: epilogue does nothing but the barrier protocol
+#endif
                         if (ch >= nch) break;
                         uint32_t v[16];
                         tmem_ld_x16(t_pos + ch * 16, v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
+#if defined(SQ_VAR_EPI_NOMATH)
+                            acc[ch * 16 + j] = __uint_as_float(v[j]);   // experiment: no convert / scale
+#elif defined(SQ_VAR_EPI_NOLDS)
+                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
+                            acc[ch * 16 + j] = fmaf(f, rxm, acc[ch * 16 + j]);   // experiment: no scale-table reads
+#else
                             const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
                             float r = rt_pos[ch * 16 + j];
                             if (per_token) r *= rxm;
                             acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
+#endif
                         }
                         if (dump != nullptr) {
 #pragma unroll 1
@@ -563,39 +699,19 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
                     ++au;
                     k = ke;
                 }
             }
             if (!ok) break;
-            // ---- bias, cast, store (one row of up to 128 consecutive columns per thread)
-            if (row_ok) {
-                const long long ncol0 = n0 + h * hcols;
-                const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
-                uint8_t* yrow = static_cast<uint8_t*>(p.y) + (b * p.y_bs + m * p.y_rs + ncol0) * esz;
-                const bool vec_ok = (reinterpret_cast<uintptr_t>(yrow) & 15u) == 0;
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const long long nc = ncol0 + ch * 16;
-                    int valid = static_cast<int>(p.N - nc);
-                    valid = valid > 16 ? 16 : valid;
-                    if (valid > 0 && ch < nch) {
-                        float o[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
-                        if (p.bias != nullptr) {
-                            const long long bo = b * p.bias_bs + nc;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (j < valid) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
-                        }
-                        if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
-                        else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
-                        else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
-                    }
-                }
-            }
+            // ---- bias, cast, store
+#if !defined(SQ_VAR_EPI_EMPTY) && !defined(SQ_VAR_EPI_NOSTORE)
+            store_output(p, &map_y, acc, nch, b, m, m0 + q * 32, row_ok, n0 + h * hcols,
+                         smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048, lane);
+#endif
         }
+        if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
     } else {
         // ------------------------------------------------------------------ int4 -> int8 expansion warps (W4A8)
         if constexpr (kW4) {
@@ -659,6 +775,15 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
+#ifdef SQ_TRACE
+extern "C" int sq_trace_read(long long* out, int n) {
+    if (n > 3 * 4096) n = 3 * 4096;
+    if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n) != cudaSuccess) return SQ_ERR_CUDA;
+    return n;
+}
+#endif
+
 long long read_device_status() {
     unsigned long long v = 0, zero = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
@@ -666,6 +791,8 @@ long long read_device_status() {
     if (v != 0 && cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(zero)) != cudaSuccess) return SQ_ERR_CUDA;
     return static_cast<long long>(v);
 }
+
+#include "seg_gemm_2cta.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // Host side
@@ -703,24 +830,39 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
     return SQ_OK;
 }
 
-// Tile width against wave quantisation: the persistent grid runs ceil(tiles / 148) rounds, a round
-// costs about (bn + fixed) per tile; narrow tiles re-read more operands, which the fixed term also
-// stands for.  SEGQUANT_B200_BN=128|192|256 forces a width (tuning aid).
-static int pick_tile_width(long long row_tiles, long long N, bool dual) {
+// Schedule choice against wave quantisation.  The persistent grid runs ceil(tiles / slots) rounds
+// (148 CTAs, or 74 CTA pairs each covering twice the rows); a round costs about (bn + fixed) per
+// tile divided by the efficiency of the mode (a single CTA is limited by shared-memory bandwidth,
+// see seg_gemm_2cta.cuh).  Narrow tiles re-read more operands, which the fixed term also stands for.
+// SEGQUANT_B200_BN=128|192|256 and SEGQUANT_B200_CTA2=0|1 force a choice (tuning aids).
+struct Schedule {
+    int bn;
+    bool two_cta;
+};
+static Schedule pick_schedule(long long M, long long N, long long batch, bool dual) {
+    int force_bn = 0, force_cta2 = -1;
     if (const char* env = getenv("SEGQUANT_B200_BN")) {
         const int v = atoi(env);
-        if (v == 128 || v == 192 || v == 256) return v;
+        if (v == 128 || v == 192 || v == 256) force_bn = v;
     }
+    if (const char* env = getenv("SEGQUANT_B200_CTA2")) force_cta2 = atoi(env) ? 1 : 0;
     const int widths[3] = {256, 192, 128};
-    int best = 256;
+    Schedule best{256, false};
     double best_cost = 1e300;
-    for (int w : widths) {
-        const long long tiles = row_tiles * ((N + w - 1) / w);
-        const long long rounds = (tiles + kNumSMs - 1) / kNumSMs;
-        double per_tile = w + 40.0;
-        if (dual && w > 128) per_tile += 0.08 * w;  // epilogue of a wide DualScale tile is not overlapped
-        const double cost = static_cast<double>(rounds) * per_tile;
-        if (cost < best_cost * 0.97) { best_cost = cost; best = w; }
+    for (int mode = 0; mode < 2; ++mode) {
+        if (force_cta2 >= 0 && mode != force_cta2) continue;
+        const long long rows = mode ? BM2 : BM;
+        const long long slots = mode ? kNumSMs / 2 : kNumSMs;
+        const double eff = mode ? 0.69 : 0.67;   // measured: the pair only wins on very large problems so far
+        for (int w : widths) {
+            if (force_bn && w != force_bn) continue;
+            const long long tiles = batch * ((M + rows - 1) / rows) * ((N + w - 1) / w);
+            const long long rounds = (tiles + slots - 1) / slots;
+            double per_tile = (w + 40.0) / eff;
+            if (dual && w > 128) per_tile += 0.08 * w;  // epilogue of a wide DualScale tile is not overlapped
+            const double cost = static_cast<double>(rounds) * per_tile;
+            if (cost < best_cost * 0.97) { best_cost = cost; best = Schedule{w, mode == 1}; }
+        }
     }
     return best;
 }
@@ -746,7 +888,7 @@ int gemm_num_units(int num_segs, const int* seg_bounds, int group_size) {
 }
 
 template <int KIND, bool DUAL>
-static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
     using C = Cfg<KIND, DUAL>;
     static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
     static bool attr_set[64] = {};
@@ -759,7 +901,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorM
         SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     }
     const long long grid = p.total_tiles < kNumSMs ? p.total_tiles : kNumSMs;
-    seg_gemm_kernel<KIND, DUAL><<<static_cast<int>(grid), C::kThreads, C::kSmemBytes, st>>>(ma, man, mw, p);
+    seg_gemm_kernel<KIND, DUAL><<<static_cast<int>(grid), C::kThreads, C::kSmemBytes, st>>>(ma, man, mw, my, p);
     SQ_CUDA_OK(cudaGetLastError());
     return SQ_OK;
 }
@@ -830,8 +972,10 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.bias = a->bias_dev; p.bias_dtype = a->bias_dtype; p.bias_bs = a->bias_batch_stride;
     p.y = a->y_dev; p.out_dtype = a->out_dtype; p.y_bs = a->y_batch_stride; p.y_rs = a->y_row_stride;
     p.acc_dump = a->acc_dump_dev; p.units = units;
-    p.tiles_m = static_cast<int>((a->M + BM - 1) / BM);
-    p.bn = pick_tile_width(static_cast<long long>(p.tiles_m) * a->batch, a->N, dual);
+    const Schedule sched = pick_schedule(a->M, a->N, a->batch, dual);
+    const int tile_rows = sched.two_cta ? BM2 : BM;
+    p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
+    p.bn = sched.bn;
     p.dual_db = (dual && p.bn <= 128) ? 1 : 0;
     p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
@@ -859,13 +1003,34 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
         // describe `batch` copies 0 bytes apart is not encodable; fold by pointing all at copy 0
         SQ_REQUIRE(false, SQ_ERR_UNSUPPORTED, "sq_gemm: batched problems need their own weights (wq_batch_stride != 0)");
     }
-    if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, p.bn, false, "wq(int4)");
-    else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, p.bn, true, "wq");
+    // output: TMA stores need a 16-byte aligned base and strides; anything else is written by the threads
+    CUtensorMap my = ma;
+    {
+        const long long esz = a->out_dtype == SQ_F32 ? 4 : 2;
+        const bool aligned = (reinterpret_cast<uintptr_t>(a->y_dev) & 15u) == 0 && (a->y_row_stride * esz) % 16 == 0 &&
+                             a->y_row_stride >= a->N && (a->batch == 1 || ((a->y_batch_stride * esz) % 16 == 0 && a->y_batch_stride > 0));
+        p.y_tma = 0;
+        if (aligned) {
+            const uint64_t y_bstride = a->batch > 1 ? a->y_batch_stride * esz : static_cast<uint64_t>(a->y_row_stride) * esz * a->M;
+            rc = make_map(&my, a->y_dev, a->N * esz, a->M, a->batch, a->y_row_stride * esz, y_bstride, 16 * esz, 32, false, "y");
+            if (rc != SQ_OK) return rc;
+            p.y_tma = 1;
+        }
+    }
+    // B tile rows staged per CTA: the whole tile, or half of it in a CTA pair
+    const uint32_t w_box_rows = sched.two_cta ? p.bn / 2 : p.bn;
+    if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, w_box_rows, false, "wq(int4)");
+    else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, w_box_rows, true, "wq");
     if (rc != SQ_OK) return rc;
 
-    if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch<SQ_GEMM_W8A8_I8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W8A8_I8, false>(ma, man, mw, p, st);
-    if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch<SQ_GEMM_W8A8_F8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W8A8_F8, false>(ma, man, mw, p, st);
-    return dual ? launch<SQ_GEMM_W4A8, true>(ma, man, mw, p, st) : launch<SQ_GEMM_W4A8, false>(ma, man, mw, p, st);
+    if (sched.two_cta) {
+        if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch_2cta<SQ_GEMM_W8A8_I8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W8A8_I8, false>(ma, man, mw, my, p, st);
+        if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch_2cta<SQ_GEMM_W8A8_F8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W8A8_F8, false>(ma, man, mw, my, p, st);
+        return dual ? launch_2cta<SQ_GEMM_W4A8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W4A8, false>(ma, man, mw, my, p, st);
+    }
+    if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch<SQ_GEMM_W8A8_I8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W8A8_I8, false>(ma, man, mw, my, p, st);
+    if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch<SQ_GEMM_W8A8_F8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W8A8_F8, false>(ma, man, mw, my, p, st);
+    return dual ? launch<SQ_GEMM_W4A8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W4A8, false>(ma, man, mw, my, p, st);
 }
 
 }  // namespace sq

@@ -1,0 +1,551 @@
+// Two-CTA (cta_group::2) variant of the segmented GEMM: a cluster of two CTAs on neighbouring SMs
+// computes one 256 x bn tile.  Included by seg_gemm.cu (inside namespace sq, after the helpers).
+//
+// Why: with one CTA per tile every SM reads a whole B tile from shared memory for each MMA and
+// fills it by TMA; operand reads plus fills need ~190 bytes/clk of shared-memory bandwidth at full
+// tensor rate.  In a pair each CTA stages and reads only HALF of the B tile (bn/2 rows) next to its
+// own 128 rows of A, one tcgen05.mma.cta_group::2 instruction drives both tensor cores, and the
+// requirement drops to ~128 bytes/clk.
+//
+// Differences from the one-CTA kernel:
+//   * CTA r of the pair owns rows [m0 + 128 r, +128) of the tile and B rows [n0 + r bn/2, +bn/2).
+//   * TMA loads carry .cta_group::2 and signal the LEADER's (rank 0) "full" barrier; only the leader
+//     arms it, with the byte count of both CTAs.  No multicast is used anywhere.
+//   * Only the leader's warp 1 issues MMAs.  tcgen05.commit is issued twice, once on the local and
+//     once on the peer's barrier, so both CTAs see "stage empty" and "accumulator full".
+//   * Epilogue warps of both CTAs drain their own tensor memory and arrive (cluster scope) on the
+//     leader's "accumulator empty" barrier (count 16); W4A8 expansion warps of both CTAs arrive on
+//     the leader's "converted" barrier (count 8), their packed bytes land on a CTA-local barrier.
+//   * The cluster is synchronised after barrier initialisation and before exit.
+// All waits stay bounded exactly as in the one-CTA kernel.
+#pragma once
+
+constexpr int BM2 = 256;  // tile rows of a CTA pair
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+// Bounded wait with cluster-scope acquire (pairs with arrivals made by the other CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((it & 1023u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 4000000000ll) {
+                atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d_2sm(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// one arrival on the barrier at `cluster_addr` (own or peer CTA) once all MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_2sm(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void umma_2sm(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == SQ_GEMM_W8A8_F8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+template <int KIND, bool DUAL>
+struct Cfg2 {
+    static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
+    static constexpr uint32_t kBHalfBytes = 128 * BK;        // up to 128 rows of B per CTA
+    static constexpr uint32_t kBpHalfBytes = 128 * BK / 2;   // packed int4 staging
+    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBHalfBytes + (kW4 ? kBpHalfBytes : 0);
+    static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kThreads = kW4 ? 512 : 384;
+    static constexpr uint32_t kTabBytes = 2 * 2 * BN * sizeof(float);
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
+};
+
+template <int KIND, bool DUAL>
+__global__ void __launch_bounds__(Cfg2<KIND, DUAL>::kThreads, 1)
+seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
+                 const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+                const __grid_constant__ GemmParams p) {
+    using C = Cfg2<KIND, DUAL>;
+    constexpr int kStages = C::kStages;
+    constexpr bool kW4 = C::kW4;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_epi;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [2][2][BN]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();      // 0 = leader
+    const uint32_t peer = rank ^ 1u;
+    const int hb = p.bn >> 1;                     // B rows / accumulator-column share of one CTA
+
+    auto stage_a = [&](int st) { return smem_base + st * C::kStageBytes; };
+    auto stage_an = [&](int st) { return smem_base + st * C::kStageBytes + kABytes; };
+    auto stage_b = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1); };
+    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + C::kBHalfBytes; };
+
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&bar_full[i]), 1);
+            mbar_init(smem_u32(&bar_empty[i]), 1);
+            mbar_init(smem_u32(&bar_cvt[i]), 8);
+            mbar_init(smem_u32(&bar_bp[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bar_tmem_full[i]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[i]), 2 * (kEpiThreads / 32));
+        }
+        mbar_init(smem_u32(&bar_epi), kEpiThreads / 32);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_a);
+        if (DUAL) prefetch_tmap(&map_an);
+        prefetch_tmap(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc_2sm(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish_2sm();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers exist before anything can signal them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;   // tiles_m counts 256-row tiles here
+    const long long first_tile = cluster_id_x();
+    const long long tile_step = cluster_count_x();
+
+    if (warp < 4) {
+        reg_dec<kW4 ? 40 : 56>();
+        if (warp == 0) {
+            // ===== TMA producer (both CTAs) =====
+            int trace_it = 0; (void)trace_it;
+            int st = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            const uint32_t tx_leader = 2u * kABytes * (DUAL ? 2 : 1) + (kW4 ? 0u : static_cast<uint32_t>(p.bn) * BK);
+            for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+                const int b = static_cast<int>(tile / tiles_per_batch);
+                const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+                const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
+                const int n0 = (rem % p.tiles_n) * p.bn + static_cast<int>(rank) * hb;
+                const int ab = p.a_batched ? b : 0;
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    const int wb = p.w_seg_as_batch ? s : b;
+                    const int wk_off = p.w_seg_as_batch ? k_beg : 0;
+                    for (int k = k_beg; k < k_end; k += BK) {
+                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
+                        if (lane == 0) {
+                            SQ_STAMP(0, 2 * trace_it);
+                            const uint32_t full_leader = map_to_rank(smem_u32(&bar_full[st]), 0);
+                            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[st]), tx_leader);
+                            tma_load_3d_2sm(stage_a(st), &map_a, k, m0, ab, full_leader);
+                            if (DUAL) tma_load_3d_2sm(stage_an(st), &map_an, k, m0, ab, full_leader);
+                            if (kW4) {
+                                const uint32_t bp = smem_u32(&bar_bp[st]);
+                                mbar_arrive_expect_tx(bp, static_cast<uint32_t>(hb) * (BK / 2));
+                                tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, bp);
+                            } else {
+                                tma_load_3d_2sm(stage_b(st), &map_w, k - wk_off, n0, wb, full_leader);
+                            }
+                        }
+                        if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
+                        ++trace_it;
+                        __syncwarp();
+                        if (++st == kStages) { st = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        } else if (warp == 1 && rank == 0) {
+            // ===== MMA issuer (leader CTA only) =====
+            const uint32_t idesc = (make_idesc<KIND>() & ~(0x1Fu << 24)) | (static_cast<uint32_t>(BM2 >> 4) << 24) |
+                                   (static_cast<uint32_t>(p.bn >> 3) << 17);
+            const bool one_buf = DUAL && !p.dual_db;
+            int st = 0;
+            uint32_t ph = 0;
+            uint32_t au = 0;
+            uint32_t cur_buf = 0;
+            int trace_mma = 0; (void)trace_mma;
+            bool ok = true;
+            for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    int u_end = k_beg;
+                    uint32_t accumulate = 0;
+                    uint32_t d_pos = 0, d_neg = 0;
+                    for (int kb = k_beg; ok && kb < k_end; kb += BK) {
+#ifdef SQ_VAR_LANE0_POLL
+                        {   // experiment: only lane 0 polls, the others meet it at the warp barrier
+                            int got = 1;
+                            if (lane == 0) got = mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull) ? 1 : 0;
+                            got = __shfl_sync(0xffffffffu, got, 0);
+                            if (!got) { ok = false; break; }
+                        }
+#else
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
+#endif
+                        if (kW4) {
+                            if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
+                        }
+#ifndef SQ_VAR_NOFENCE
+                        tc_fence_after();
+#endif
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
+                        const uint32_t a_lo = smem_desc_lo(stage_a(st));
+                        const uint32_t an_lo = smem_desc_lo(stage_an(st));
+                        const uint32_t b_lo = smem_desc_lo(stage_b(st));
+                        const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
+                        if (kb != u_end && kb + kmax <= u_end) {
+                            if (lane == 0) {
+#pragma unroll
+                                for (int i = 0; i < BK / UMMA_K; ++i) {
+                                    if (i * UMMA_K < kmax) {
+                                        const uint64_t db = smem_desc(b_lo + 2 * i);
+                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
+                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
+                                    }
+                                }
+                            }
+                        } else {
+                            for (int kk = 0; kk < kmax; kk += UMMA_K) {
+                                const int k = kb + kk;
+                                if (k == u_end) {
+                                    if (k != k_beg && lane == 0) {
+                                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+                                    }
+                                    const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                                    if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                                    tc_fence_after();
+                                    cur_buf = buf;
+                                    d_pos = tmem_base + buf * BN;
+                                    d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                                    accumulate = 0;
+                                    u_end = unit_end(p, s, k);
+                                    ++au;
+                                }
+                                if (lane == 0) {
+                                    const uint64_t db = smem_desc(b_lo + (kk >> 4));
+                                    umma_2sm<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
+                                    if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
+                                }
+                                accumulate = 1;
+                            }
+                            if (!ok) break;
+                        }
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 1);
+                        if (lane == 0) {   // stage free in both CTAs once these MMAs have read it
+                            umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 0));
+                            umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 1));
+                        }
+                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 2);
+                        ++trace_mma;
+                        __syncwarp();
+                        if (++st == kStages) { st = 0; ph ^= 1u; }
+                    }
+                    if (ok && lane == 0) {
+                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // ===== epilogue (both CTAs): same as the one-CTA kernel on this CTA's 128 rows =====
+        reg_inc<kW4 ? 192 : 216>();
+        const int epi_tid = threadIdx.x - 128;
+        const int q = warp & 3;
+        const int h = (warp - 4) >> 2;
+        const bool per_token = p.sx_rs != 0;
+        const bool one_buf = DUAL && !p.dual_db;
+        const int hcols = p.bn >> 1;
+        const int nch = hcols >> 4;
+        uint32_t au = 0;
+        bool ok = true;
+        for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+            const int b = static_cast<int>(tile / tiles_per_batch);
+            const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+            const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
+            const int n0 = (rem % p.tiles_n) * p.bn;
+            const long long m = m0 + q * 32 + lane;
+            const bool row_ok = m < p.M;
+
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+
+            int unit_in_tile = 0;
+            for (int s = 0; ok && s < p.num_segs; ++s) {
+                const int k_end = p.seg_bounds[s + 1];
+                for (int k = p.seg_bounds[s]; ok && k < k_end; ++unit_in_tile) {
+                    const int ke = unit_end(p, s, k);
+                    const int g = p.group_size > 0 ? k / p.group_size : 0;
+                    const uint32_t par = au & 1u;
+                    {
+                        const long long n = n0 + epi_tid;
+                        float r = 0.0f, rn = 0.0f;
+                        if (n < p.N && epi_tid < p.bn) {
+                            const float swv = load_sw(p, b * p.sw_bs + s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
+                            const float sxv = per_token ? 1.0f : __ldg(p.sx + b * p.sx_bs + s * p.sx_ss);
+                            r = 1.0f / (sxv * swv);
+                            if (DUAL) {
+                                const float sxn = per_token ? 1.0f : __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss);
+                                rn = 1.0f / (sxn * swv);
+                            }
+                            if (kW4) { r *= 0.0625f; rn *= 0.0625f; }
+                        }
+                        rtab[(par * 2 + 0) * BN + epi_tid] = r;
+                        rtab[(par * 2 + 1) * BN + epi_tid] = rn;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
+                    if (!mbar_wait(smem_u32(&bar_epi), par, abort_flag, kWaitEpi)) { ok = false; break; }
+                    float rxm = 1.0f, rxnm = 1.0f;
+                    if (per_token && row_ok) {
+                        rxm = 1.0f / __ldg(p.sx + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
+                        if (DUAL) rxnm = 1.0f / __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
+                    }
+                    const uint32_t buf = one_buf ? 0u : (au & 1u);
+                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                    if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
+                    tc_fence_after();
+                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
+                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
+                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (p.dual_db ? buf * BN + 128 : BN) + h * hcols;
+                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * hcols;
+                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * hcols;
+                    int32_t* dump = nullptr;
+                    if (p.acc_dump != nullptr && row_ok) {
+                        const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
+                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * hcols;
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        if (ch >= nch) break;
+                        uint32_t v[16];
+                        tmem_ld_x16(t_pos + ch * 16, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
+                            float r = rt_pos[ch * 16 + j];
+                            if (per_token) r *= rxm;
+                            acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
+                        }
+                        if (dump != nullptr) {
+#pragma unroll 1
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + h * hcols + ch * 16 + j < p.N)
+                                    dump[ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
+                        }
+                        if (DUAL) {
+                            tmem_ld_x16(t_neg + ch * 16, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
+                                float r = rt_neg[ch * 16 + j];
+                                if (per_token) r *= rxnm;
+                                acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
+                            }
+                            if (dump != nullptr) {
+#pragma unroll 1
+                                for (int j = 0; j < 16; ++j)
+                                    if (n0 + h * hcols + ch * 16 + j < p.N)
+                                        dump[p.M * p.N + ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bar_tmem_empty[buf]), 0));
+                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
+                    ++au;
+                    k = ke;
+                }
+            }
+            if (!ok) break;
+            store_output(p, &map_y, acc, nch, b, m, m0 + q * 32, row_ok, n0 + h * hcols,
+                         smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048, lane);
+        }
+        if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
+    } else {
+        // ===== int4 -> int8 expansion of this CTA's half of the weight tile (W4A8, both CTAs) =====
+        if constexpr (kW4) {
+            reg_dec<80>();
+            const int ct = threadIdx.x - 384;
+            int st = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+                for (int s = 0; ok && s < p.num_segs; ++s) {
+                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                    for (int kb = k_beg; kb < k_end; kb += BK) {
+                        if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
+                        uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int c = ct + i * 128;
+                            if (c >= hb * 4) break;
+                            const int row = c >> 2, qd = c & 3;
+                            const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
+                            const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
+                            uint32_t out[8];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t lo = (in[j] << 4) & 0xF0F0F0F0u;
+                                const uint32_t hi = in[j] & 0xF0F0F0F0u;
+                                out[2 * j] = __byte_perm(lo, hi, 0x5140);
+                                out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                            }
+                            uint8_t* drow = dst + row * 128;
+                            const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
+                            *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+                            *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bar_cvt[st]), 0));
+                        if (++st == kStages) { st = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: nobody leaves while the peer may still signal this CTA's barriers
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_2sm(tmem_base, kTmemCols);
+    }
+    (void)peer;
+}
+
+// Launch on as many CTA pairs as can be resident.  Returns SQ_ERR_UNSUPPORTED if the device cannot
+// host a pair of this kernel (the caller then uses the one-CTA kernel).
+template <int KIND, bool DUAL>
+static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+    using C = Cfg2<KIND, DUAL>;
+    static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
+    static int max_clusters[64] = {};
+    int dev = 0;
+    SQ_CUDA_OK(cudaGetDevice(&dev));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (dev >= 64 || max_clusters[dev] == 0) {
+        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm2_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        cfg.gridDim = dim3(kNumSMs, 1, 1);
+        int n = 0;
+        SQ_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, seg_gemm2_kernel<KIND, DUAL>, &cfg));
+        if (n < 1) {
+            set_error("sq_gemm: no CTA pair of the two-CTA kernel fits on this device");
+            return SQ_ERR_UNSUPPORTED;
+        }
+        if (dev < 64) max_clusters[dev] = n;
+        else max_clusters[0] = n;
+    }
+    const int resident = dev < 64 ? max_clusters[dev] : max_clusters[0];
+    const long long clusters = p.total_tiles < resident ? p.total_tiles : resident;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+    SQ_CUDA_OK(cudaLaunchKernelEx(&cfg, seg_gemm2_kernel<KIND, DUAL>, ma, man, mw, my, p));
+    return SQ_OK;
+}

@@ -1,0 +1,189 @@
+"""Synthetic SD3.5-medium-like MMDiT denoise step built from real-quantized SegmentLinear layers.
+
+Architecture (random-init weights ~ N(0, 0.02), no checkpoint): 24 joint blocks, hidden 1536,
+24 heads of 64, MLP ratio 4, 4096 image tokens + 333 text tokens.  The block structure follows the
+reference's vendored SD3 transformer: JointTransformerBlock (backend/torch/layers/attention.py:476-679),
+AdaLayerNormZero (backend/torch/layers/normalization.py:322-380: SiLU -> Linear(H, 6H) -> chunk(6)),
+AdaLayerNormContinuous (:271-317), the embedders of backend/torch/layers/embeddings.py:973-1071, and the
+output head of backend/torch/modules/transformer_sd3.py:90-156.
+
+Every nn.Linear is a W8A8 INT8 SegmentLinear with the segmentation the reference's pattern detector
+would give it (segquant/pattern_detector.py:239-358):
+  * adaLN modulation linears: N-segmented into their 6 (or 2) output chunks, DualScale input (after SiLU);
+  * ff.net[2] (after GELU-tanh) and the second embedder linears (after SiLU): DualScale input;
+  * attention output projections: S = 1 by default, or 24 K-segments of 64 (`out_proj_segments=24`,
+    the reshape_to_linear pattern: heads x head_dim);
+  * everything else: S = 1.
+Attention (torch SDPA) and the norms stay bf16.  Scales are calibrated once from one forward of the
+float model on the given inputs (AMax), then every layer runs the fused quantise + tcgen05 GEMM path.
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .layers.SegmentLinear import SegmentLinear
+
+
+class QLinear:
+    """A float linear that becomes a real-quantized SegmentLinear after one calibration forward."""
+
+    def __init__(self, in_f, out_f, gen, device, dtype, seg_mode="weight", chunks=1, dual=False, bias=True, act="int8", wq="int8"):
+        self.in_f, self.out_f, self.seg_mode, self.chunks, self.dual = in_f, out_f, seg_mode, chunks, dual
+        self.act, self.wq = act, wq
+        self.w = (torch.randn(out_f, in_f, generator=gen, dtype=torch.float32) * 0.02).to(dtype).to(device)
+        self.b = (torch.randn(out_f, generator=gen, dtype=torch.float32) * 0.01).to(dtype).to(device) if bias else None
+        self.layer = None
+        self.device = device
+
+    def calibrate_forward(self, x):
+        self.layer = SegmentLinear(
+            self.in_f, self.out_f, bias=self.b is not None, seg_mode=self.seg_mode, chunks=self.chunks,
+            custom_weight_tensor=self.w, custom_bias_tensor=self.b, input_quant_type=self.act, weight_quant_type=self.wq,
+            input_quant_args={"real_quant": True, "axis": None, "dual_scale": self.dual},
+            weight_quant_args={"real_quant": True, "axis": 1}, device=self.device)
+        self.layer.calibrate(x)
+        return F.linear(x, self.w, self.b)
+
+    def finish(self):
+        self.layer.finish_calibrate()
+        self.w = None   # the float weight is no longer needed
+
+    def __call__(self, x):
+        return self.layer(x)
+
+
+def _layer_norm(x):
+    return F.layer_norm(x, (x.shape[-1],), eps=1e-6)
+
+
+def _timestep_embedding(t, dim=256):
+    half = dim // 2
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
+    args = t.float()[:, None] * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class JointBlock:
+    def __init__(self, hidden, heads, gen, device, dtype, last, out_proj_segments):
+        self.heads, self.last = heads, last
+        mk = lambda i, o, **kw: QLinear(i, o, gen, device, dtype, **kw)  # noqa: E731
+        self.norm1 = mk(hidden, 6 * hidden, chunks=6, dual=True)
+        self.norm1_context = mk(hidden, (2 if last else 6) * hidden, chunks=2 if last else 6, dual=True)
+        self.to_q, self.to_k, self.to_v = mk(hidden, hidden), mk(hidden, hidden), mk(hidden, hidden)
+        self.add_q, self.add_k, self.add_v = mk(hidden, hidden), mk(hidden, hidden), mk(hidden, hidden)
+        seg = dict(seg_mode="input", chunks=out_proj_segments) if out_proj_segments > 1 else {}
+        self.to_out = mk(hidden, hidden, **seg)
+        self.ff0, self.ff2 = mk(hidden, 4 * hidden), mk(4 * hidden, hidden, dual=True)
+        if not last:
+            self.to_add_out = mk(hidden, hidden, **seg)
+            self.ffc0, self.ffc2 = mk(hidden, 4 * hidden), mk(4 * hidden, hidden, dual=True)
+
+    def linears(self):
+        names = ["norm1", "norm1_context", "to_q", "to_k", "to_v", "add_q", "add_k", "add_v", "to_out", "ff0", "ff2"]
+        if not self.last:
+            names += ["to_add_out", "ffc0", "ffc2"]
+        return [getattr(self, n) for n in names]
+
+    def forward(self, img, txt, c_act, call):
+        """c_act = SiLU(conditioning) [B, H]; call(layer, x) runs either the calibration or the quantized linear."""
+        B, Ti, H = img.shape
+        Tt = txt.shape[1]
+        m = call(self.norm1, c_act).unsqueeze(1).chunk(6, dim=-1)            # shift, scale, gate (msa), shift, scale, gate (mlp)
+        n_img = _layer_norm(img) * (1 + m[1]) + m[0]
+        mc = call(self.norm1_context, c_act).unsqueeze(1).chunk(2 if self.last else 6, dim=-1)
+        n_txt = _layer_norm(txt) * (1 + mc[1]) + mc[0]
+
+        def heads(t):
+            return t.view(B, -1, self.heads, H // self.heads).transpose(1, 2)
+
+        q = torch.cat([heads(call(self.to_q, n_img)), heads(call(self.add_q, n_txt))], dim=2)
+        k = torch.cat([heads(call(self.to_k, n_img)), heads(call(self.add_k, n_txt))], dim=2)
+        v = torch.cat([heads(call(self.to_v, n_img)), heads(call(self.add_v, n_txt))], dim=2)
+        a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, Ti + Tt, H)
+        a_img, a_txt = a[:, :Ti], a[:, Ti:]
+
+        img = img + m[2] * call(self.to_out, a_img)
+        n2 = _layer_norm(img) * (1 + m[4]) + m[3]
+        img = img + m[5] * call(self.ff2, F.gelu(call(self.ff0, n2), approximate="tanh"))
+        if not self.last:
+            txt = txt + mc[2] * call(self.to_add_out, a_txt.contiguous())
+            n2c = _layer_norm(txt) * (1 + mc[4]) + mc[3]
+            txt = txt + mc[5] * call(self.ffc2, F.gelu(call(self.ffc0, n2c), approximate="tanh"))
+        return img, txt
+
+
+class SyntheticMMDiT:
+    def __init__(self, device, blocks=24, hidden=1536, heads=24, img_tokens=4096, txt_tokens=333, seed=0,
+                 dtype=torch.bfloat16, out_proj_segments=1):
+        gen = torch.Generator().manual_seed(seed)
+        self.device, self.dtype, self.hidden = device, dtype, hidden
+        self.img_tokens, self.txt_tokens = img_tokens, txt_tokens
+        mk = lambda i, o, **kw: QLinear(i, o, gen, device, dtype, **kw)  # noqa: E731
+        self.context_embedder = mk(4096, hidden)
+        self.t_lin1, self.t_lin2 = mk(256, hidden), mk(hidden, hidden, dual=True)
+        self.p_lin1, self.p_lin2 = mk(2048, hidden), mk(hidden, hidden, dual=True)
+        self.blocks = [JointBlock(hidden, heads, gen, device, dtype, last=(i == blocks - 1), out_proj_segments=out_proj_segments)
+                       for i in range(blocks)]
+        self.norm_out = mk(hidden, 2 * hidden, chunks=2, dual=True)
+        self.proj_out = mk(hidden, 64)
+        self.calibrated = False
+
+    def linears(self):
+        out = [self.context_embedder, self.t_lin1, self.t_lin2, self.p_lin1, self.p_lin2]
+        for b in self.blocks:
+            out += b.linears()
+        return out + [self.norm_out, self.proj_out]
+
+    def _forward(self, latents, text, pooled, timestep, call):
+        """latents [B, Ti, H] (already patch-embedded: the patch embedder is a Conv2d, never quantised),
+        text [B, Tt, 4096], pooled [B, 2048], timestep [B]."""
+        temb = call(self.t_lin2, F.silu(call(self.t_lin1, _timestep_embedding(timestep).to(self.dtype))))
+        pemb = call(self.p_lin2, F.silu(call(self.p_lin1, pooled)))
+        c_act = F.silu(temb + pemb)
+        txt = call(self.context_embedder, text)
+        img = latents
+        for blk in self.blocks:
+            img, txt = blk.forward(img, txt, c_act, call)
+        mod = call(self.norm_out, c_act).unsqueeze(1).chunk(2, dim=-1)       # scale, shift
+        img = _layer_norm(img) * (1 + mod[0]) + mod[1]
+        return call(self.proj_out, img)
+
+    def calibrate(self, latents, text, pooled, timestep):
+        """One forward of the float model; every linear records its input range and is then quantized."""
+        with torch.no_grad():
+            y = self._forward(latents, text, pooled, timestep, lambda layer, x: layer.calibrate_forward(x))
+            for lin in self.linears():
+                lin.finish()
+        self.calibrated = True
+        return y
+
+    def __call__(self, latents, text, pooled, timestep):
+        if not self.calibrated:
+            raise RuntimeError("call calibrate() once before running the quantized model")
+        with torch.no_grad():
+            return self._forward(latents, text, pooled, timestep, lambda layer, x: layer(x))
+
+    def linear_ops(self, batch):
+        """Useful operations 2*M*N*K of one step, summed over every quantized linear."""
+        total = 0
+        small = {id(l) for l in (self.t_lin1, self.t_lin2, self.p_lin1, self.p_lin2, self.norm_out)}
+        txt_side = {id(self.context_embedder)}
+        for blk in self.blocks:
+            small |= {id(blk.norm1), id(blk.norm1_context)}
+            txt_side |= {id(l) for l in (blk.add_q, blk.add_k, blk.add_v)}
+            if not blk.last:
+                txt_side |= {id(l) for l in (blk.to_add_out, blk.ffc0, blk.ffc2)}
+        for lin in self.linears():
+            rows = batch if id(lin) in small else batch * (self.txt_tokens if id(lin) in txt_side else self.img_tokens)
+            total += 2 * rows * lin.in_f * lin.out_f
+        return total
+
+
+def synthetic_inputs(batch, device, dtype=torch.bfloat16, img_tokens=4096, txt_tokens=333, hidden=1536, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    latents = torch.randn(batch, img_tokens, hidden, generator=g).to(dtype).to(device)
+    text = torch.randn(batch, txt_tokens, 4096, generator=g).to(dtype).to(device)
+    pooled = torch.randn(batch, 2048, generator=g).to(dtype).to(device)
+    timestep = torch.full((batch,), 500.0, device=device)
+    return latents, text, pooled, timestep

@@ -61,11 +61,12 @@ def uniform_bounds(K, segments):
 # activation quantise
 # ---------------------------------------------------------------------------------------------
 def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=False, smooth=None,
-                 out=None, out_neg=None, out_layout="same"):
+                 out=None, out_neg=None, shared_scales=False):
     """x: (B, M, K) view (any batch / row stride, K contiguous) or (M, K).
 
-    sx: (B*S,) or (B*S*M,) float32 in (batch, segment[, row]) order.  Returns (xq, xq_neg) uint8
-    tensors of shape (B, M, K) (contiguous).  `bounds` cuts K into the S segments."""
+    sx: (B*S,) or (B*S*M,) float32 in (batch, segment[, row]) order, or (S,) used by every batch
+    when shared_scales is set.  Returns (xq, xq_neg) uint8 tensors of shape (B, M, K) (contiguous).
+    `bounds` cuts K into the S segments."""
     global launch_count
     _need_cuda(x, sx, sx_neg)
     if x.dim() == 2:
@@ -93,6 +94,8 @@ def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=Fal
         a.sx_batch_stride, a.sx_seg_stride, a.sx_row_stride = S * M, M, 1
     else:
         a.sx_batch_stride, a.sx_seg_stride, a.sx_row_stride = S, 1, 0
+    if shared_scales:
+        a.sx_batch_stride = 0
     a.smooth_dev = smooth.data_ptr() if smooth is not None else None
     a.xq_dev = xq.data_ptr()
     a.xq_neg_dev = xqn.data_ptr() if dual else None
@@ -264,9 +267,19 @@ def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=Fa
     segments in fp32 registers, adds the bias and casts.  Returns [.., N] in x.dtype."""
     kind, a_kind, _ = KERNELS[kernel_type]
     lead = x.shape[:-1]
-    x2 = x.reshape(-1, x.shape[-1])
+    K = x.shape[-1]
     out_dtype = out_dtype or x.dtype
     dual = sx_neg is not None
+    if x.dim() == 3 and x.stride(-1) == 1 and not x.is_contiguous() and not dynamic:
+        # a strided (B, M, K) view (e.g. a token slice of a joint sequence): the quantise kernel reads it
+        # in place and writes contiguous bytes, so no copy of x is made
+        xq, xqn = quantize_act(x, bounds, sx, sx_neg, a_kind, smooth=smooth, shared_scales=True)
+        rows = xq.shape[0] * xq.shape[1]
+        y = gemm(kind, xq.view(1, rows, K), wq, N, bounds, sx, sw, xq_neg=None if xqn is None else xqn.view(1, rows, K),
+                 sx_neg=sx_neg, group_size=group_size, sw_strides=sw_strides, bias=bias, out_dtype=out_dtype,
+                 w_seg_as_batch=w_seg_as_batch)
+        return y.reshape(*lead, N)
+    x2 = x.reshape(-1, K)
     if dynamic:
         xq, xqn, sxd, sxnd = quantize_act_dynamic(x2, bounds, a_kind, dual=dual)
         y = gemm(kind, xq.unsqueeze(0), wq, N, bounds, sxd, sw, xq_neg=xqn, sx_neg=sxnd, per_token=True,
