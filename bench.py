@@ -318,15 +318,192 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------
+# other BASELINE workloads (not the default line): synthetic MMDiT denoise step, GEMM sweep
+# ---------------------------------------------------------------------------------------------
+def _dist_setup():
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, world, rank, dev
+
+
+def run_mmdit(args):
+    """config[3]: 24-block SD3.5-medium-like MMDiT, every linear W8A8 INT8 SegLinear, attention / norms bf16.
+    Batch 2 on one GPU; batch 16 split over 2 / 4 / 8 GPUs (replicas, no collective inside the step)."""
+    from segquant_b200 import ops
+    from segquant_b200.mmdit import SyntheticMMDiT, synthetic_inputs
+    dist, world, rank, dev = _dist_setup()
+    batch = 2 if world == 1 else 16 // world
+    model = SyntheticMMDiT(dev, out_proj_segments=args.out_proj_segments)
+    inputs = synthetic_inputs(batch, dev, seed=100 + rank)
+    model.calibrate(*inputs)
+    torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        y = model(*inputs)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    l0 = ops.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = model(*inputs)
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = ops.launch_count - l0
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    # end to end: host latents in, host noise prediction out
+    host_in = [x.cpu().pin_memory() for x in inputs]
+    host_out = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e2.record()
+    for _ in range(max(2, args.steps // 4)):
+        dev_in = [x.to(dev, non_blocking=True) for x in host_in]
+        host_out.copy_(model(*dev_in), non_blocking=True)
+    e3.record()
+    torch.cuda.synchronize()
+    t2 = torch.tensor([e2.elapsed_time(e3) / max(2, args.steps // 4)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    status = ops.device_status()
+    if rank == 0:
+        lin_ops = model.linear_ops(batch)
+        tokens = model.img_tokens + model.txt_tokens
+        attn_flops = 24 * batch * 4 * tokens * tokens * model.hidden
+        line = {
+            "metric": "mmdit_denoise_step_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8 linears, bf16 attention", "data": "synthetic",
+            "config": {"workload": f"config[3]: synthetic MMDiT, 24 joint blocks, hidden 1536, 4096+333 tokens, batch {batch} per GPU "
+                                   f"({batch * world} total), attention output projections with {args.out_proj_segments} K-segment(s)",
+                       "parallelism": f"dp{world} replicas"},
+            "linear_tops": lin_ops / ms / 1e9, "linear_ops_per_step": lin_ops, "attention_flops_per_step": attn_flops,
+            "e2e": {"value": t2.item(), "unit": "ms", "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
+                    "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
+            "gpu_launches": launches, "clocks": clocks, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+SWEEP_NK = [(1536, 1536), (6144, 1536), (1536, 6144), (9216, 3072), (12288, 3072), (3072, 12288), (1280, 5120)]
+
+
+def run_sweep(args):
+    """config[4]: M x (N, K) x {INT8, FP8, W4A8 g=128} x segments {1,2,4,8}; each point column-sharded over the
+    ranks with an NCCL all-gather of the output slices.  Prints one JSON line holding every point."""
+    from segquant_b200 import _lib as L
+    from segquant_b200 import ops
+    from segquant_b200.sharded import all_gather_slices, shard_range
+    dist, world, rank, dev = _dist_setup()
+    g = torch.Generator().manual_seed(5)
+    points = []
+    modes = [("int8", "Wint8Aint8", L.SQ_Q_INT8, 0), ("fp8", "Wfpe4m3Afpe4m3", L.SQ_Q_E4M3, 0), ("w4a8", "Wint4Aint8", L.SQ_Q_INT4, 128)]
+    Ms = [int(m) for m in args.sweep_m.split(",")]
+    for (N, K) in SWEEP_NK:
+        if N % world:
+            continue
+        lo, hi = shard_range(N, world, rank)
+        n_loc = hi - lo
+        w = (torch.randn(n_loc, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        for name, ktype, wkind, group in modes:
+            qmax = {L.SQ_Q_INT8: 127.0, L.SQ_Q_E4M3: 448.0, L.SQ_Q_INT4: 7.0}[wkind]
+            if group:
+                sw = (qmax / w.float().view(n_loc, K // group, group).abs().amax(-1)).contiguous()
+                wq = torch.empty(n_loc * K // 2, dtype=torch.uint8, device=dev)
+                ops.quantize_weight(w, wq, sw, wkind, group_size=group)
+                wq3, strides = wq.view(1, n_loc, K // 2), (0, 0, 1, K // group)
+            else:
+                sw = (qmax / w.float().abs().amax(-1)).contiguous()
+                wq = torch.empty((n_loc, K), dtype=torch.uint8, device=dev)
+                ops.quantize_weight(w, wq, sw, wkind)
+                wq3, strides = wq.view(1, n_loc, K), (0, 0, 0, 1)
+            for M in Ms:
+                for S in (1, 2, 4, 8):
+                    if K % (S * 32):
+                        continue
+                    bounds = ops.uniform_bounds(K, S)
+                    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+                    scale = torch.exp(torch.empty(S).uniform_(-1.386, 3.466, generator=g))   # log-uniform in [0.25, 32]
+                    for s_ in range(S):
+                        x[:, bounds[s_]:bounds[s_ + 1]] *= scale[s_].to(torch.bfloat16)
+                    x = x.to(dev)
+                    aq = 448.0 if name == "fp8" else 127.0
+                    sx = torch.stack([aq / x[:, bounds[s_]:bounds[s_ + 1]].float().abs().max() for s_ in range(S)]).contiguous()
+
+                    def fwd():
+                        return ops.seg_linear(ktype, x, wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides)
+
+                    for _ in range(3):
+                        y = fwd()
+                    torch.cuda.synchronize()
+                    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                    it = args.sweep_iters
+                    e[0].record()
+                    for _ in range(it):
+                        y = fwd()
+                    e[1].record()
+                    for _ in range(it):
+                        y = fwd()
+                        if world > 1:
+                            all_gather_slices(y)
+                    e[2].record()
+                    torch.cuda.synchronize()
+                    t = torch.tensor([e[0].elapsed_time(e[1]) / it, e[1].elapsed_time(e[2]) / it], dtype=torch.float64, device=dev)
+                    if world > 1:
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    ms_c, ms_t = t.tolist()
+                    points.append({"mode": name, "M": M, "N": N, "K": K, "S": S, "layer_ms": ms_c, "layer_tops": 2.0 * M * N * K / ms_c / 1e9,
+                                   "with_allgather_ms": ms_t if world > 1 else None})
+    status = ops.device_status()
+    if rank == 0:
+        best = {m: max((p["layer_tops"] for p in points if p["mode"] == m), default=0.0) for m in ("int8", "fp8", "w4a8")}
+        print(json.dumps({"metric": "seglinear_gemm_tops_sweep", "unit": "TOPS", "n_gpus": world, "higher_is_better": True,
+                          "scaling": "strong", "data": "synthetic", "value": max(best.values()), "best_tops": best,
+                          "config": {"workload": "config[4]: GEMM sweep, layer = activation quantise + GEMM + epilogue, bf16 in/out, "
+                                                 "N column-sharded over the ranks", "iters": args.sweep_iters},
+                          "device_status": status, "points": points}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep"],
+                    help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep)")
+    ap.add_argument("--out-proj-segments", type=int, default=1, help="mmdit: K-segments of the attention output projections (1 or 24)")
+    ap.add_argument("--sweep-m", default="256,1024,4096,16384")
+    ap.add_argument("--sweep-iters", type=int, default=10)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "mmdit":
+        run_mmdit(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
     else:
         run_ours(args)
 

@@ -839,7 +839,7 @@ struct Schedule {
     int bn;
     bool two_cta;
 };
-static Schedule pick_schedule(long long M, long long N, long long batch, bool dual) {
+static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind) {
     int force_bn = 0, force_cta2 = -1;
     if (const char* env = getenv("SEGQUANT_B200_BN")) {
         const int v = atoi(env);
@@ -851,9 +851,12 @@ static Schedule pick_schedule(long long M, long long N, long long batch, bool du
     double best_cost = 1e300;
     for (int mode = 0; mode < 2; ++mode) {
         if (force_cta2 >= 0 && mode != force_cta2) continue;
+        // measured on B200: the CTA pair (256-byte K stages) wins for 8-bit weights once K is long enough to
+        // amortise its longer prologue; int4 expansion and short K run faster on single CTAs
+        if (force_cta2 < 0 && mode == 1 && (kind == SQ_GEMM_W4A8 || K < 2048)) continue;
         const long long rows = mode ? BM2 : BM;
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;
-        const double eff = mode ? 0.69 : 0.67;   // measured: the pair only wins on very large problems so far
+        const double eff = mode ? 0.76 : 0.67;
         for (int w : widths) {
             if (force_bn && w != force_bn) continue;
             const long long tiles = batch * ((M + rows - 1) / rows) * ((N + w - 1) / w);
@@ -972,7 +975,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.bias = a->bias_dev; p.bias_dtype = a->bias_dtype; p.bias_bs = a->bias_batch_stride;
     p.y = a->y_dev; p.out_dtype = a->out_dtype; p.y_bs = a->y_batch_stride; p.y_rs = a->y_row_stride;
     p.acc_dump = a->acc_dump_dev; p.units = units;
-    const Schedule sched = pick_schedule(a->M, a->N, a->batch, dual);
+    const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind);
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
     p.bn = sched.bn;

@@ -116,12 +116,14 @@ __device__ __forceinline__ void umma_2sm(uint32_t tmem_d, uint64_t desc_a, uint6
     }
 }
 
-template <int KIND, bool DUAL>
+// KSUB = 128-byte K sub-tiles per pipeline stage: with 2 a stage carries 8 MMAs, which halves the
+// per-MMA share of the barrier wait / commit cost of the issuing thread.
+template <int KIND, bool DUAL, int KSUB>
 struct Cfg2 {
     static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
-    static constexpr uint32_t kBHalfBytes = 128 * BK;        // up to 128 rows of B per CTA
-    static constexpr uint32_t kBpHalfBytes = 128 * BK / 2;   // packed int4 staging
-    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBHalfBytes + (kW4 ? kBpHalfBytes : 0);
+    static constexpr uint32_t kBHalfBytes = 128 * BK;        // up to 128 rows of B per CTA and sub-tile
+    static constexpr uint32_t kBpHalfBytes = 128 * BK / 2;   // packed int4 staging per sub-tile
+    static constexpr uint32_t kStageBytes = KSUB * (kABytes * (DUAL ? 2 : 1) + kBHalfBytes + (kW4 ? kBpHalfBytes : 0));
     static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kThreads = kW4 ? 512 : 384;
@@ -129,14 +131,15 @@ struct Cfg2 {
     static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
 };
 
-template <int KIND, bool DUAL>
-__global__ void __launch_bounds__(Cfg2<KIND, DUAL>::kThreads, 1)
+template <int KIND, bool DUAL, int KSUB>
+__global__ void __launch_bounds__(Cfg2<KIND, DUAL, KSUB>::kThreads, 1)
 seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
                  const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                 const __grid_constant__ GemmParams p) {
-    using C = Cfg2<KIND, DUAL>;
+    using C = Cfg2<KIND, DUAL, KSUB>;
     constexpr int kStages = C::kStages;
     constexpr bool kW4 = C::kW4;
+    constexpr int BKS = BK * KSUB;   // K covered by one stage
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_epi;
@@ -154,10 +157,13 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t peer = rank ^ 1u;
     const int hb = p.bn >> 1;                     // B rows / accumulator-column share of one CTA
 
-    auto stage_a = [&](int st) { return smem_base + st * C::kStageBytes; };
-    auto stage_an = [&](int st) { return smem_base + st * C::kStageBytes + kABytes; };
-    auto stage_b = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1); };
-    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + C::kBHalfBytes; };
+    // stage layout: A[KSUB] | A_neg[KSUB] | B[KSUB] | B_packed[KSUB]
+    auto stage_a = [&](int st, int j) { return smem_base + st * C::kStageBytes + j * kABytes; };
+    auto stage_an = [&](int st, int j) { return smem_base + st * C::kStageBytes + (KSUB + j) * kABytes; };
+    auto stage_b = [&](int st, int j) { return smem_base + st * C::kStageBytes + KSUB * kABytes * (DUAL ? 2 : 1) + j * C::kBHalfBytes; };
+    auto stage_bp = [&](int st, int j) {
+        return smem_base + st * C::kStageBytes + KSUB * (kABytes * (DUAL ? 2 : 1) + C::kBHalfBytes) + j * C::kBpHalfBytes;
+    };
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
@@ -201,7 +207,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int st = 0;
             uint32_t ph = 0;
             bool ok = true;
-            const uint32_t tx_leader = 2u * kABytes * (DUAL ? 2 : 1) + (kW4 ? 0u : static_cast<uint32_t>(p.bn) * BK);
+            const uint32_t tx_sub = 2u * kABytes * (DUAL ? 2 : 1) + (kW4 ? 0u : static_cast<uint32_t>(p.bn) * BK);   // both CTAs, one sub-tile
             for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
                 const int b = static_cast<int>(tile / tiles_per_batch);
                 const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
@@ -212,20 +218,24 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
                     const int wb = p.w_seg_as_batch ? s : b;
                     const int wk_off = p.w_seg_as_batch ? k_beg : 0;
-                    for (int k = k_beg; k < k_end; k += BK) {
+                    for (int k = k_beg; k < k_end; k += BKS) {
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
                         if (lane == 0) {
                             SQ_STAMP(0, 2 * trace_it);
+                            const int left = k_end - k;
+                            const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;   // sub-tiles that hold data
                             const uint32_t full_leader = map_to_rank(smem_u32(&bar_full[st]), 0);
-                            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[st]), tx_leader);
-                            tma_load_3d_2sm(stage_a(st), &map_a, k, m0, ab, full_leader);
-                            if (DUAL) tma_load_3d_2sm(stage_an(st), &map_an, k, m0, ab, full_leader);
-                            if (kW4) {
-                                const uint32_t bp = smem_u32(&bar_bp[st]);
-                                mbar_arrive_expect_tx(bp, static_cast<uint32_t>(hb) * (BK / 2));
-                                tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, bp);
-                            } else {
-                                tma_load_3d_2sm(stage_b(st), &map_w, k - wk_off, n0, wb, full_leader);
+                            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[st]), tx_sub * nsub);
+                            const uint32_t bp = smem_u32(&bar_bp[st]);
+                            if (kW4) mbar_arrive_expect_tx(bp, static_cast<uint32_t>(hb) * (BK / 2) * nsub);
+#pragma unroll
+                            for (int j = 0; j < KSUB; ++j) {
+                                if (j >= nsub) break;
+                                const int kj = k + j * BK;
+                                tma_load_3d_2sm(stage_a(st, j), &map_a, kj, m0, ab, full_leader);
+                                if (DUAL) tma_load_3d_2sm(stage_an(st, j), &map_an, kj, m0, ab, full_leader);
+                                if (kW4) tma_load_3d(stage_bp(st, j), &map_w, (kj - wk_off) >> 1, n0, wb, bp);
+                                else tma_load_3d_2sm(stage_b(st, j), &map_w, kj - wk_off, n0, wb, full_leader);
                             }
                         }
                         if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
@@ -252,7 +262,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     int u_end = k_beg;
                     uint32_t accumulate = 0;
                     uint32_t d_pos = 0, d_neg = 0;
-                    for (int kb = k_beg; ok && kb < k_end; kb += BK) {
+                    for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
 #ifdef SQ_VAR_LANE0_POLL
                         {   // experiment: only lane 0 polls, the others meet it at the warp barrier
                             int got = 1;
@@ -270,18 +280,22 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         tc_fence_after();
 #endif
                         if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
-                        const uint32_t a_lo = smem_desc_lo(stage_a(st));
-                        const uint32_t an_lo = smem_desc_lo(stage_an(st));
-                        const uint32_t b_lo = smem_desc_lo(stage_b(st));
-                        const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
+                        // sub-tile j of an operand starts (tile bytes >> 4) descriptor units after sub-tile j-1
+                        const uint32_t a_lo = smem_desc_lo(stage_a(st, 0));
+                        const uint32_t an_lo = smem_desc_lo(stage_an(st, 0));
+                        const uint32_t b_lo = smem_desc_lo(stage_b(st, 0));
+                        const int kmax = (k_end - kb) < BKS ? (k_end - kb) : BKS;
                         if (kb != u_end && kb + kmax <= u_end) {
                             if (lane == 0) {
 #pragma unroll
-                                for (int i = 0; i < BK / UMMA_K; ++i) {
+                                for (int i = 0; i < BKS / UMMA_K; ++i) {
                                     if (i * UMMA_K < kmax) {
-                                        const uint64_t db = smem_desc(b_lo + 2 * i);
-                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
-                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
+                                        constexpr int kPerSub = BK / UMMA_K;
+                                        const uint32_t ao = (i / kPerSub) * (kABytes >> 4) + 2 * (i % kPerSub);
+                                        const uint32_t bo = (i / kPerSub) * (C::kBHalfBytes >> 4) + 2 * (i % kPerSub);
+                                        const uint64_t db = smem_desc(b_lo + bo);
+                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + ao), db, idesc, 1u);
+                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + ao), db, idesc, 1u);
                                     }
                                 }
                             }
@@ -305,9 +319,10 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     ++au;
                                 }
                                 if (lane == 0) {
-                                    const uint64_t db = smem_desc(b_lo + (kk >> 4));
-                                    umma_2sm<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
-                                    if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
+                                    const uint32_t sub = static_cast<uint32_t>(kk) / BK, within = (static_cast<uint32_t>(kk) % BK) >> 4;
+                                    const uint64_t db = smem_desc(b_lo + sub * (C::kBHalfBytes >> 4) + within);
+                                    umma_2sm<KIND>(d_pos, smem_desc(a_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
+                                    if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
                                 }
                                 accumulate = 1;
                             }
@@ -461,10 +476,13 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    for (int kb = k_beg; kb < k_end; kb += BK) {
+                    for (int kb = k_beg; kb < k_end; kb += BKS) {
                         if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
-                        const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
-                        uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
+                        const int left = k_end - kb;
+                        const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;
+                        for (int jsub = 0; jsub < nsub; ++jsub) {
+                        const uint8_t* src = smem_gen + (stage_bp(st, jsub) - smem_base);
+                        uint8_t* dst = smem_gen + (stage_b(st, jsub) - smem_base);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int c = ct + i * 128;
@@ -484,6 +502,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
                             *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
                             *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+                        }
                         }
                         fence_proxy_async_smem();
                         __syncwarp();
@@ -513,9 +532,9 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 // Launch on as many CTA pairs as can be resident.  Returns SQ_ERR_UNSUPPORTED if the device cannot
 // host a pair of this kernel (the caller then uses the one-CTA kernel).
-template <int KIND, bool DUAL>
-static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
-    using C = Cfg2<KIND, DUAL>;
+template <int KIND, bool DUAL, int KSUB>
+static int launch_2cta_k(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+    using C = Cfg2<KIND, DUAL, KSUB>;
     static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
     static int max_clusters[64] = {};
     int dev = 0;
@@ -532,10 +551,10 @@ static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUte
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (dev >= 64 || max_clusters[dev] == 0) {
-        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm2_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm2_kernel<KIND, DUAL, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         cfg.gridDim = dim3(kNumSMs, 1, 1);
         int n = 0;
-        SQ_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, seg_gemm2_kernel<KIND, DUAL>, &cfg));
+        SQ_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, seg_gemm2_kernel<KIND, DUAL, KSUB>, &cfg));
         if (n < 1) {
             set_error("sq_gemm: no CTA pair of the two-CTA kernel fits on this device");
             return SQ_ERR_UNSUPPORTED;
@@ -546,6 +565,19 @@ static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUte
     const int resident = dev < 64 ? max_clusters[dev] : max_clusters[0];
     const long long clusters = p.total_tiles < resident ? p.total_tiles : resident;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-    SQ_CUDA_OK(cudaLaunchKernelEx(&cfg, seg_gemm2_kernel<KIND, DUAL>, ma, man, mw, my, p));
+    SQ_CUDA_OK(cudaLaunchKernelEx(&cfg, seg_gemm2_kernel<KIND, DUAL, KSUB>, ma, man, mw, my, p));
     return SQ_OK;
+}
+
+// 256-byte K stages wherever two of them fit in shared memory (all but W4A8 + DualScale).
+// SEGQUANT_B200_KSUB=1 forces 128-byte stages (tuning aid).
+template <int KIND, bool DUAL>
+static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+    constexpr bool can2 = Cfg2<KIND, DUAL, 2>::kStagesRaw >= 2;
+    bool want2 = can2;
+    if (const char* env = getenv("SEGQUANT_B200_KSUB")) want2 = can2 && atoi(env) != 1;
+    if constexpr (can2) {
+        if (want2) return launch_2cta_k<KIND, DUAL, 2>(ma, man, mw, my, p, st);
+    }
+    return launch_2cta_k<KIND, DUAL, 1>(ma, man, mw, my, p, st);
 }
