@@ -339,13 +339,16 @@ def run_mmdit(args):
     """config[3]: 24-block SD3.5-medium-like MMDiT, every linear W8A8 INT8 SegLinear, attention / norms bf16.
     Batch 2 on one GPU; batch 16 split over 2 / 4 / 8 GPUs (replicas, no collective inside the step)."""
     from segquant_b200 import ops
-    from segquant_b200.mmdit import SyntheticMMDiT, synthetic_inputs
+    from segquant_b200.mmdit import GraphedStep, SyntheticMMDiT, synthetic_inputs
     dist, world, rank, dev = _dist_setup()
     batch = 2 if world == 1 else 16 // world
     model = SyntheticMMDiT(dev, out_proj_segments=args.out_proj_segments)
     inputs = synthetic_inputs(batch, dev, seed=100 + rank)
     model.calibrate(*inputs)
     torch.cuda.synchronize()
+    eager = model
+    if not args.no_graph:
+        model = GraphedStep(eager, *inputs)
     for _ in range(max(args.warmup, 3)):
         y = model(*inputs)
     if world > 1:
@@ -385,16 +388,16 @@ def run_mmdit(args):
     clocks = sampler.stop() if rank == 0 else None
     status = ops.device_status()
     if rank == 0:
-        lin_ops = model.linear_ops(batch)
-        tokens = model.img_tokens + model.txt_tokens
-        attn_flops = 24 * batch * 4 * tokens * tokens * model.hidden
+        lin_ops = eager.linear_ops(batch)
+        tokens = eager.img_tokens + eager.txt_tokens
+        attn_flops = 24 * batch * 4 * tokens * tokens * eager.hidden
         line = {
             "metric": "mmdit_denoise_step_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
             "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8 linears, bf16 attention", "data": "synthetic",
             "config": {"workload": f"config[3]: synthetic MMDiT, 24 joint blocks, hidden 1536, 4096+333 tokens, batch {batch} per GPU "
                                    f"({batch * world} total), attention output projections with {args.out_proj_segments} K-segment(s)",
-                       "parallelism": f"dp{world} replicas"},
+                       "launch": "eager" if args.no_graph else "one CUDA graph per step", "parallelism": f"dp{world} replicas"},
             "linear_tops": lin_ops / ms / 1e9, "linear_ops_per_step": lin_ops, "attention_flops_per_step": attn_flops,
             "e2e": {"value": t2.item(), "unit": "ms", "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
                     "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
@@ -495,6 +498,7 @@ def main():
     ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep"],
                     help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep)")
     ap.add_argument("--out-proj-segments", type=int, default=1, help="mmdit: K-segments of the attention output projections (1 or 24)")
+    ap.add_argument("--no-graph", action="store_true", help="mmdit: launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384")
     ap.add_argument("--sweep-iters", type=int, default=10)
     args = ap.parse_args()

@@ -174,7 +174,7 @@ typedef struct sq_gemm_args {
     const void* xq_neg_dev;    /* NULL unless DualScale */
     int64_t xq_batch_stride, xq_row_stride;      /* bytes; batch stride 0 = shared by all b */
     const void* wq_dev;
-    int64_t wq_batch_stride, wq_row_stride;      /* bytes */
+    int64_t wq_batch_stride, wq_row_stride;      /* bytes; batch stride 0 = one weight matrix shared by all b */
     int32_t w_seg_as_batch;
     int32_t num_segs;
     int32_t seg_bounds[SQ_MAX_SEGS + 1];

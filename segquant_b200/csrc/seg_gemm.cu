@@ -75,6 +75,7 @@ struct GemmParams {
     int group_size;
     int w_seg_as_batch;
     int a_batched;
+    int w_batched;   // 0: every problem of the batch uses the same weight matrix
     const float* sx;
     const float* sx_neg;
     long long sx_bs, sx_ss, sx_rs;
@@ -464,7 +465,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int ab = p.a_batched ? b : 0;
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    const int wb = p.w_seg_as_batch ? s : b;
+                    const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
                     const int wk_off = p.w_seg_as_batch ? k_beg : 0;
                     for (int k = k_beg; k < k_end; k += BK) {
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
@@ -1001,11 +1002,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     const uint64_t w_nb = (w_batches > 1 && a->wq_batch_stride != 0) ? w_batches : 1;
     SQ_REQUIRE(w_nb == static_cast<uint64_t>(w_batches) || !a->w_seg_as_batch, SQ_ERR_INVALID_ARG,
                "sq_gemm: w_seg_as_batch needs a non-zero wq_batch_stride");
-    if (w_nb == 1 && w_batches > 1) {
-        // every problem shares one weight matrix: the kernel always asks for batch index b, so
-        // describe `batch` copies 0 bytes apart is not encodable; fold by pointing all at copy 0
-        SQ_REQUIRE(false, SQ_ERR_UNSUPPORTED, "sq_gemm: batched problems need their own weights (wq_batch_stride != 0)");
-    }
+    p.w_batched = (w_nb > 1 && !a->w_seg_as_batch) ? 1 : 0;   // wq_batch_stride == 0: one weight matrix for all problems
     // output: TMA stores need a 16-byte aligned base and strides; anything else is written by the threads
     CUtensorMap my = ma;
     {

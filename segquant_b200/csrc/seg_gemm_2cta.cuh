@@ -216,7 +216,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int ab = p.a_batched ? b : 0;
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    const int wb = p.w_seg_as_batch ? s : b;
+                    const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
                     const int wk_off = p.w_seg_as_batch ? k_beg : 0;
                     for (int k = k_beg; k < k_end; k += BKS) {
                         if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }

@@ -156,10 +156,13 @@ class SegmentLinear(nn.Module):
             self.bias_data = self.bias_data.to(device)
 
     # ---- forward ---------------------------------------------------------------------------------------
-    def forward(self, x, chunked=False):
+    def forward(self, x, chunked=False, out=None):
+        """out (real-quant path only): a (B, M, N) view to write into, e.g. a slice of a larger buffer."""
         opt = self.optimizer
         if opt.real_quant and not chunked:
-            return opt.fused_forward(x, self.bias_data if self.bias else None)
+            return opt.fused_forward(x, self.bias_data if self.bias else None, out=out)
+        if out is not None:
+            raise ValueError("out= is served by the fused real-quant forward only")
         parts = opt.forward(self._inputs(x))
         if chunked:
             return parts

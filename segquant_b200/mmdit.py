@@ -49,8 +49,8 @@ class QLinear:
         self.layer.finish_calibrate()
         self.w = None   # the float weight is no longer needed
 
-    def __call__(self, x):
-        return self.layer(x)
+    def __call__(self, x, out=None):
+        return self.layer(x, out=out)
 
 
 def _layer_norm(x):
@@ -86,30 +86,34 @@ class JointBlock:
         return [getattr(self, n) for n in names]
 
     def forward(self, img, txt, c_act, call):
-        """c_act = SiLU(conditioning) [B, H]; call(layer, x) runs either the calibration or the quantized linear."""
+        """c_act = SiLU(conditioning) [B, H]; call(layer, x, out=None) runs either the calibration or the quantized
+        linear, writing into `out` when given."""
         B, Ti, H = img.shape
         Tt = txt.shape[1]
         m = call(self.norm1, c_act).unsqueeze(1).chunk(6, dim=-1)            # shift, scale, gate (msa), shift, scale, gate (mlp)
-        n_img = _layer_norm(img) * (1 + m[1]) + m[0]
+        n_img = torch.addcmul(m[0], _layer_norm(img), 1 + m[1])
         mc = call(self.norm1_context, c_act).unsqueeze(1).chunk(2 if self.last else 6, dim=-1)
-        n_txt = _layer_norm(txt) * (1 + mc[1]) + mc[0]
+        n_txt = torch.addcmul(mc[0], _layer_norm(txt), 1 + mc[1])
+
+        # the six projections write straight into their token range of one joint buffer per q / k / v
+        qkv = torch.empty((3, B, Ti + Tt, H), dtype=img.dtype, device=img.device)
+        for j, (li, lt) in enumerate(((self.to_q, self.add_q), (self.to_k, self.add_k), (self.to_v, self.add_v))):
+            call(li, n_img, qkv[j, :, :Ti])
+            call(lt, n_txt, qkv[j, :, Ti:])
 
         def heads(t):
-            return t.view(B, -1, self.heads, H // self.heads).transpose(1, 2)
+            return t.view(B, Ti + Tt, self.heads, H // self.heads).transpose(1, 2)
 
-        q = torch.cat([heads(call(self.to_q, n_img)), heads(call(self.add_q, n_txt))], dim=2)
-        k = torch.cat([heads(call(self.to_k, n_img)), heads(call(self.add_k, n_txt))], dim=2)
-        v = torch.cat([heads(call(self.to_v, n_img)), heads(call(self.add_v, n_txt))], dim=2)
-        a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, Ti + Tt, H)
+        a = F.scaled_dot_product_attention(heads(qkv[0]), heads(qkv[1]), heads(qkv[2])).transpose(1, 2).reshape(B, Ti + Tt, H)
         a_img, a_txt = a[:, :Ti], a[:, Ti:]
 
-        img = img + m[2] * call(self.to_out, a_img)
-        n2 = _layer_norm(img) * (1 + m[4]) + m[3]
-        img = img + m[5] * call(self.ff2, F.gelu(call(self.ff0, n2), approximate="tanh"))
+        img = torch.addcmul(img, m[2], call(self.to_out, a_img))
+        n2 = torch.addcmul(m[3], _layer_norm(img), 1 + m[4])
+        img = torch.addcmul(img, m[5], call(self.ff2, F.gelu(call(self.ff0, n2), approximate="tanh")))
         if not self.last:
-            txt = txt + mc[2] * call(self.to_add_out, a_txt.contiguous())
-            n2c = _layer_norm(txt) * (1 + mc[4]) + mc[3]
-            txt = txt + mc[5] * call(self.ffc2, F.gelu(call(self.ffc0, n2c), approximate="tanh"))
+            txt = torch.addcmul(txt, mc[2], call(self.to_add_out, a_txt))
+            n2c = torch.addcmul(mc[3], _layer_norm(txt), 1 + mc[4])
+            txt = torch.addcmul(txt, mc[5], call(self.ffc2, F.gelu(call(self.ffc0, n2c), approximate="tanh")))
         return img, txt
 
 
@@ -146,13 +150,19 @@ class SyntheticMMDiT:
         for blk in self.blocks:
             img, txt = blk.forward(img, txt, c_act, call)
         mod = call(self.norm_out, c_act).unsqueeze(1).chunk(2, dim=-1)       # scale, shift
-        img = _layer_norm(img) * (1 + mod[0]) + mod[1]
+        img = torch.addcmul(mod[1], _layer_norm(img), 1 + mod[0])
         return call(self.proj_out, img)
 
     def calibrate(self, latents, text, pooled, timestep):
         """One forward of the float model; every linear records its input range and is then quantized."""
         with torch.no_grad():
-            y = self._forward(latents, text, pooled, timestep, lambda layer, x: layer.calibrate_forward(x))
+            def calib(layer, x, out=None):
+                y = layer.calibrate_forward(x)
+                if out is not None:
+                    out.copy_(y)
+                    return out
+                return y
+            y = self._forward(latents, text, pooled, timestep, calib)
             for lin in self.linears():
                 lin.finish()
         self.calibrated = True
@@ -162,7 +172,7 @@ class SyntheticMMDiT:
         if not self.calibrated:
             raise RuntimeError("call calibrate() once before running the quantized model")
         with torch.no_grad():
-            return self._forward(latents, text, pooled, timestep, lambda layer, x: layer(x))
+            return self._forward(latents, text, pooled, timestep, lambda layer, x, out=None: layer(x, out=out))
 
     def linear_ops(self, batch):
         """Useful operations 2*M*N*K of one step, summed over every quantized linear."""
@@ -178,6 +188,32 @@ class SyntheticMMDiT:
             rows = batch if id(lin) in small else batch * (self.txt_tokens if id(lin) in txt_side else self.img_tokens)
             total += 2 * rows * lin.in_f * lin.out_f
         return total
+
+
+class GraphedStep:
+    """The quantized denoise step captured once into a CUDA graph and replayed: a step is ~2000 small
+    launches (two per linear plus the bf16 glue), so launch overhead dominates when they are issued one by
+    one from Python.  Inputs are copied into static buffers; the output tensor is reused by every replay."""
+
+    def __init__(self, model, latents, text, pooled, timestep, warmup=2):
+        self.static_in = [t.clone() for t in (latents, text, pooled, timestep)]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):            # first calls build per-layer caches and set kernel attributes
+                model(*self.static_in)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_out = model(*self.static_in)
+
+    def __call__(self, latents=None, text=None, pooled=None, timestep=None):
+        for dst, src in zip(self.static_in, (latents, text, pooled, timestep)):
+            if src is not None and src is not dst:
+                dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        return self.static_out
 
 
 def synthetic_inputs(batch, device, dtype=torch.bfloat16, img_tokens=4096, txt_tokens=333, hidden=1536, seed=0):

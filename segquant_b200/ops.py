@@ -261,7 +261,7 @@ def device_status():
 # fused layer forward
 # ---------------------------------------------------------------------------------------------
 def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=False, group_size=0,
-               sw_strides=(0, 0, 0, 1), bias=None, smooth=None, w_seg_as_batch=False, out_dtype=None):
+               sw_strides=(0, 0, 0, 1), bias=None, smooth=None, w_seg_as_batch=False, out_dtype=None, out=None):
     """SegmentLinear.forward on the real-quant path in two launches: quantise x [.., K] with the
     per-K-segment (or DualScale, or dynamic per-token) scales, then one GEMM that sums the
     segments in fp32 registers, adds the bias and casts.  Returns [.., N] in x.dtype."""
@@ -270,6 +270,15 @@ def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=Fa
     K = x.shape[-1]
     out_dtype = out_dtype or x.dtype
     dual = sx_neg is not None
+    if out is not None:
+        # write straight into a caller-provided (B, M, N) view (any batch / row stride, N contiguous), e.g. a slice of
+        # a joint token buffer: one problem per batch entry, all sharing the weight matrix
+        if dynamic or x.dim() != 3 or out.dim() != 3 or out.stride(-1) != 1 or out.shape[:2] != x.shape[:2] or out.shape[2] != N:
+            raise ValueError("out= needs a static-scale (B, M, K) input and a (B, M, N) output view with a contiguous last dim")
+        xq, xqn = quantize_act(x if x.stride(-1) == 1 else x.contiguous(), bounds, sx, sx_neg, a_kind, smooth=smooth, shared_scales=True)
+        gemm(kind, xq, wq, N, bounds, sx, sw, xq_neg=xqn, sx_neg=sx_neg, group_size=group_size, sw_strides=sw_strides, bias=bias,
+             out_dtype=out.dtype, out=out, y_strides=(out.stride(0), out.stride(1)), sx_batch_stride=0, w_seg_as_batch=w_seg_as_batch)
+        return out
     if x.dim() == 3 and x.stride(-1) == 1 and not x.is_contiguous() and not dynamic:
         # a strided (B, M, K) view (e.g. a token slice of a joint sequence): the quantise kernel reads it
         # in place and writes contiguous bytes, so no copy of x is made
