@@ -45,6 +45,8 @@ constexpr uint32_t kABytes = BM * BK;          // 16 KB
 constexpr uint32_t kBBytes = BN * BK;          // 32 KB
 constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
 constexpr uint32_t kStoreStageBytes = 8 * 2048;  // output staging for TMA stores: 2 KB per epilogue warp
+constexpr int kTabSlots = 4;                     // per-unit scale tables in flight (the epilogue needs 3)
+constexpr uint32_t kTabBytesAll = kTabSlots * 2 * BN * sizeof(float);   // [slot][pos, neg][BN]
 
 // status-word codes (low byte = which wait, rest = block index)
 enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitEpi = 7 };
@@ -60,6 +62,13 @@ __device__ long long g_trace[3 * 4096];
 #define SQ_STAMP(role, idx) do { if (blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
 #else
 #define SQ_STAMP(role, idx) do { } while (0)
+#endif
+#ifdef SQ_TRACE_EPI   // eight stamps per accumulation unit of block 0's first epilogue thread, in role 0's slots
+#undef SQ_STAMP
+#define SQ_STAMP(role, idx) do { if ((role) != 0 && blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
+#define SQ_EPI(slot) do { if (threadIdx.x == 128 && blockIdx.x == 0 && au < 500) g_trace[8 * au + (slot)] = clock64(); } while (0)
+#else
+#define SQ_EPI(slot) do { } while (0)
 #endif
 #ifdef SQ_TRACE_FINE
 #define SQ_FINE(slot) do { if (lane == 0 && blockIdx.x == 0 && trace_mma < 500) g_trace[2 * 4096 + 8 * trace_mma + (slot)] = clock64(); } while (0)
@@ -107,6 +116,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -247,8 +259,8 @@ struct Cfg {
     static constexpr int kStages = (192 * 1024) / kStageBytes;
     static constexpr int kThreads = kW4 ? 512 : 384;
     static constexpr uint32_t kTxBytes = kABytes * (DUAL ? 2 : 1) + (kW4 ? kBPackedBytes : kBBytes);
-    // dynamic shared memory: 1 KB alignment slack + stages + scale tables (2 parities x 2 sides x BN floats)
-    static constexpr uint32_t kTabBytes = 2 * 2 * BN * sizeof(float);
+    // dynamic shared memory: 1 KB alignment slack + stages + scale tables + output staging
+    static constexpr uint32_t kTabBytes = kTabBytesAll;
     static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
 };
 
@@ -387,6 +399,8 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
     }
 }
 
+#include "seg_gemm_epilogue.cuh"
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
@@ -407,7 +421,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [2][2][BN]
+    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [kTabSlots][2][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -580,143 +594,23 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ epilogue warps
-        reg_inc<kW4 ? 192 : 216>();
-        const int epi_tid = threadIdx.x - 128;       // 0..255
-        const int q = warp & 3;                      // TMEM lane quarter of this warp
-        const int h = (warp - 4) >> 2;               // column half
-        const bool per_token = p.sx_rs != 0;
-        const bool one_buf = DUAL && !p.dual_db;
-        const int hcols = p.bn >> 1;                 // columns per warpgroup: 64, 96 or 128
-        const int nch = hcols >> 4;                  // 16-column chunks per thread
+        reg_inc<kW4 ? 200 : 224>();
         uint32_t au = 0;
-        bool ok = true;
-        for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
             const int b = static_cast<int>(tile / tiles_per_batch);
             const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
             const int m0 = (rem / p.tiles_n) * BM;
             const int n0 = (rem % p.tiles_n) * p.bn;
-            const long long m = m0 + q * 32 + lane;
-            const bool row_ok = m < p.M;
-
-            float acc[128];
-#pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-
-            int unit_in_tile = 0;
-            for (int s = 0; ok && s < p.num_segs; ++s) {
-                const int k_end = p.seg_bounds[s + 1];
-                for (int k = p.seg_bounds[s]; ok && k < k_end; ++unit_in_tile) {
-                    const int ke = unit_end(p, s, k);
-                    const int g = p.group_size > 0 ? k / p.group_size : 0;
-                    const uint32_t par = au & 1u;
-                    // ---- per-column reciprocal scale table for this unit
-                    {
-                        const long long n = n0 + epi_tid;
-                        float r = 0.0f, rn = 0.0f;
-                        if (n < p.N && epi_tid < p.bn) {
-                            const float swv = load_sw(p, b * p.sw_bs + s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
-                            const float sxv = per_token ? 1.0f : __ldg(p.sx + b * p.sx_bs + s * p.sx_ss);
-                            r = 1.0f / (sxv * swv);
-                            if (DUAL) {
-                                const float sxn = per_token ? 1.0f : __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss);
-                                rn = 1.0f / (sxn * swv);
-                            }
-                            if (kW4) { r *= 0.0625f; rn *= 0.0625f; }  // int4 weights are expanded as 16*w
-                        }
-                        rtab[(par * 2 + 0) * BN + epi_tid] = r;
-                        rtab[(par * 2 + 1) * BN + epi_tid] = rn;
-                    }
-                    // all 8 epilogue warps have written their table entries (bounded, unlike bar.sync)
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
-                    if (!mbar_wait(smem_u32(&bar_epi), par, abort_flag, kWaitEpi)) { ok = false; break; }
-                    float rxm = 1.0f, rxnm = 1.0f;
-                    if (per_token && row_ok) {
-                        rxm = 1.0f / __ldg(p.sx + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
-                        if (DUAL) rxnm = 1.0f / __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
-                    }
-                    const uint32_t buf = one_buf ? 0u : (au & 1u);
-                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                    if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
-                    tc_fence_after();
-                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
-                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
-                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (p.dual_db ? buf * BN + 128 : BN) + h * hcols;
-                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * hcols;
-                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * hcols;
-                    int32_t* dump = nullptr;
-                    if (p.acc_dump != nullptr && row_ok) {
-                        const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
-                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * hcols;
-                    }
-#pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-#ifdef SQ_VAR_EPI_EMPTY
-                        break;   // experiment: epilogue does nothing but the barrier protocol
-#endif
-                        if (ch >= nch) break;
-                        uint32_t v[16];
-                        tmem_ld_x16(t_pos + ch * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-#if defined(SQ_VAR_EPI_NOMATH)
-                            acc[ch * 16 + j] = __uint_as_float(v[j]);   // experiment: no convert / scale
-#elif defined(SQ_VAR_EPI_NOLDS)
-                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
-                            acc[ch * 16 + j] = fmaf(f, rxm, acc[ch * 16 + j]);   // experiment: no scale-table reads
-#else
-                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
-                            float r = rt_pos[ch * 16 + j];
-                            if (per_token) r *= rxm;
-                            acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
-#endif
-                        }
-                        if (dump != nullptr) {
-#pragma unroll 1
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + h * hcols + ch * 16 + j < p.N)
-                                    dump[ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
-                        }
-                        if (DUAL) {
-                            tmem_ld_x16(t_neg + ch * 16, v);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
-                                float r = rt_neg[ch * 16 + j];
-                                if (per_token) r *= rxnm;
-                                acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
-                            }
-                            if (dump != nullptr) {
-#pragma unroll 1
-                                for (int j = 0; j < 16; ++j)
-                                    if (n0 + h * hcols + ch * 16 + j < p.N)
-                                        dump[p.M * p.N + ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
-                            }
-                        }
-                    }
-                    // buffer drained: give it back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
-                    ++au;
-                    k = ke;
-                }
-            }
-            if (!ok) break;
-            // ---- bias, cast, store
-#if !defined(SQ_VAR_EPI_EMPTY) && !defined(SQ_VAR_EPI_NOSTORE)
-            store_output(p, &map_y, acc, nch, b, m, m0 + q * 32, row_ok, n0 + h * hcols,
-                         smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048, lane);
-#endif
+            if (!epilogue_tile<KIND, DUAL, false>(p, &map_y, tmem_base, rtab, smem_u32(&bar_tmem_full[0]), smem_u32(&bar_tmem_empty[0]),
+                                                  smem_u32(&bar_epi), abort_flag, au, b, m0, n0, warp, lane,
+                                                  smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048))
+                break;
         }
         if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
     } else {
         // ------------------------------------------------------------------ int4 -> int8 expansion warps (W4A8)
         if constexpr (kW4) {
-            reg_dec<80>();
+            reg_dec<72>();
             const int ct = threadIdx.x - 384;  // 0..127
             uint32_t it = 0;
             bool ok = true;

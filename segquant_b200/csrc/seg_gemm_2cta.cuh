@@ -47,9 +47,6 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
 __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -127,7 +124,7 @@ struct Cfg2 {
     static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kThreads = kW4 ? 512 : 384;
-    static constexpr uint32_t kTabBytes = 2 * 2 * BN * sizeof(float);
+    static constexpr uint32_t kTabBytes = kTabBytesAll;
     static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
 };
 
@@ -149,7 +146,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [2][2][BN]
+    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [kTabSlots][2][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -348,127 +345,24 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp < 12) {
         // ===== epilogue (both CTAs): same as the one-CTA kernel on this CTA's 128 rows =====
-        reg_inc<kW4 ? 192 : 216>();
-        const int epi_tid = threadIdx.x - 128;
-        const int q = warp & 3;
-        const int h = (warp - 4) >> 2;
-        const bool per_token = p.sx_rs != 0;
-        const bool one_buf = DUAL && !p.dual_db;
-        const int hcols = p.bn >> 1;
-        const int nch = hcols >> 4;
+        reg_inc<kW4 ? 200 : 224>();
         uint32_t au = 0;
-        bool ok = true;
-        for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+        const uint32_t empty_leader = map_to_rank(smem_u32(&bar_tmem_empty[0]), 0);
+        for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
             const int b = static_cast<int>(tile / tiles_per_batch);
             const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
             const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
             const int n0 = (rem % p.tiles_n) * p.bn;
-            const long long m = m0 + q * 32 + lane;
-            const bool row_ok = m < p.M;
-
-            float acc[128];
-#pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-
-            int unit_in_tile = 0;
-            for (int s = 0; ok && s < p.num_segs; ++s) {
-                const int k_end = p.seg_bounds[s + 1];
-                for (int k = p.seg_bounds[s]; ok && k < k_end; ++unit_in_tile) {
-                    const int ke = unit_end(p, s, k);
-                    const int g = p.group_size > 0 ? k / p.group_size : 0;
-                    const uint32_t par = au & 1u;
-                    {
-                        const long long n = n0 + epi_tid;
-                        float r = 0.0f, rn = 0.0f;
-                        if (n < p.N && epi_tid < p.bn) {
-                            const float swv = load_sw(p, b * p.sw_bs + s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
-                            const float sxv = per_token ? 1.0f : __ldg(p.sx + b * p.sx_bs + s * p.sx_ss);
-                            r = 1.0f / (sxv * swv);
-                            if (DUAL) {
-                                const float sxn = per_token ? 1.0f : __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss);
-                                rn = 1.0f / (sxn * swv);
-                            }
-                            if (kW4) { r *= 0.0625f; rn *= 0.0625f; }
-                        }
-                        rtab[(par * 2 + 0) * BN + epi_tid] = r;
-                        rtab[(par * 2 + 1) * BN + epi_tid] = rn;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
-                    if (!mbar_wait(smem_u32(&bar_epi), par, abort_flag, kWaitEpi)) { ok = false; break; }
-                    float rxm = 1.0f, rxnm = 1.0f;
-                    if (per_token && row_ok) {
-                        rxm = 1.0f / __ldg(p.sx + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
-                        if (DUAL) rxnm = 1.0f / __ldg(p.sx_neg + b * p.sx_bs + s * p.sx_ss + m * p.sx_rs);
-                    }
-                    const uint32_t buf = one_buf ? 0u : (au & 1u);
-                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                    if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), tph, abort_flag, kWaitTmemFull)) { ok = false; break; }
-                    tc_fence_after();
-                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
-                    const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
-                    const uint32_t t_neg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (p.dual_db ? buf * BN + 128 : BN) + h * hcols;
-                    const float* rt_pos = rtab + (par * 2 + 0) * BN + h * hcols;
-                    const float* rt_neg = rtab + (par * 2 + 1) * BN + h * hcols;
-                    int32_t* dump = nullptr;
-                    if (p.acc_dump != nullptr && row_ok) {
-                        const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
-                        dump = static_cast<int32_t*>(p.acc_dump) + (u * (DUAL ? 2 : 1)) * p.M * p.N + m * p.N + n0 + h * hcols;
-                    }
-#pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        if (ch >= nch) break;
-                        uint32_t v[16];
-                        tmem_ld_x16(t_pos + ch * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
-                            float r = rt_pos[ch * 16 + j];
-                            if (per_token) r *= rxm;
-                            acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
-                        }
-                        if (dump != nullptr) {
-#pragma unroll 1
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + h * hcols + ch * 16 + j < p.N)
-                                    dump[ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
-                        }
-                        if (DUAL) {
-                            tmem_ld_x16(t_neg + ch * 16, v);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const float f = KIND == SQ_GEMM_W8A8_F8 ? __uint_as_float(v[j]) : static_cast<float>(static_cast<int32_t>(v[j]));
-                                float r = rt_neg[ch * 16 + j];
-                                if (per_token) r *= rxnm;
-                                acc[ch * 16 + j] = fmaf(f, r, acc[ch * 16 + j]);
-                            }
-                            if (dump != nullptr) {
-#pragma unroll 1
-                                for (int j = 0; j < 16; ++j)
-                                    if (n0 + h * hcols + ch * 16 + j < p.N)
-                                        dump[p.M * p.N + ch * 16 + j] = kW4 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
-                            }
-                        }
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bar_tmem_empty[buf]), 0));
-                    if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
-                    ++au;
-                    k = ke;
-                }
-            }
-            if (!ok) break;
-            store_output(p, &map_y, acc, nch, b, m, m0 + q * 32, row_ok, n0 + h * hcols,
-                         smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048, lane);
+            if (!epilogue_tile<KIND, DUAL, true>(p, &map_y, tmem_base, rtab, smem_u32(&bar_tmem_full[0]), empty_leader,
+                                                 smem_u32(&bar_epi), abort_flag, au, b, m0, n0, warp, lane,
+                                                 smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048))
+                break;
         }
         if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
     } else {
         // ===== int4 -> int8 expansion of this CTA's half of the weight tile (W4A8, both CTAs) =====
         if constexpr (kW4) {
-            reg_dec<80>();
+            reg_dec<72>();
             const int ct = threadIdx.x - 384;
             int st = 0;
             uint32_t ph = 0;
