@@ -299,7 +299,10 @@ def run_ours(args):
                        "cache": f"{ROTATE} independent layer instances cycled (operands {ROTATE * (M * K * 4 + N * K + M * N * 2) / 1e6:.0f} MB > 126 MB L2)",
                        "parallelism": f"dp{world}"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "seg_gemm_kernel<F8, dual>", "kernel_ms": gemm_ms,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
+                         # (one ncu capture; 63.6 MB against 72.3 MB of algorithmic operand + output bytes)
+                         "traffic": 63.6e6, "traffic_unit": "bytes per launch (ncu)",
+                         "kernel": "seg_gemm2_kernel<F8, dual, KSUB=2>", "kernel_ms": gemm_ms,
                          "note": ("achieved = issued 4*M*N*K per launch / mean launch time (CUDA events on the launch stream); "
                                   "peak = 2 x measured bf16 burst (of measured)" if bf16 else
                                   "achieved = issued 4*M*N*K per launch / mean launch time; peak = 2 x 1.59 PFLOP/s (of fallback)")},
