@@ -2,7 +2,7 @@
 
 The reference JIT-builds five pybind11 modules against CUTLASS through
 torch.utils.cpp_extension.load (segquant/utils/extension.py:25-64).  This library has no torch or
-CUTLASS dependency: three .cu files plus the C ABI, linked with the static CUDA runtime so the
+CUTLASS dependency: a handful of .cu files plus the C ABI, linked with the static CUDA runtime so the
 .so also loads on a machine without a GPU driver (symbol checks, CPU tests).
 
     python -m segquant_b200.build          # build if sources are newer than the .so
@@ -15,8 +15,12 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsegquant_b200.so")
-SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu", "static_scratch.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "segquant_b200.h")]
+SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu", "static_scratch.cu",
+           # one translation unit per (kind, DualScale): the GEMM kernels dominate compile time and build in parallel
+           "seg_gemm_tu_i8.cu", "seg_gemm_tu_i8_dual.cu", "seg_gemm_tu_f8.cu", "seg_gemm_tu_f8_dual.cu",
+           "seg_gemm_tu_w4.cu", "seg_gemm_tu_w4_dual.cu"]
+HEADERS = [os.path.join(CSRC, h) for h in ("common.cuh", "seg_gemm_params.cuh", "seg_gemm_kernels.cuh", "seg_gemm_2cta.cuh",
+                                           "seg_gemm_epilogue.cuh")] + [os.path.join(PKG_DIR, "..", "include", "segquant_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,693 +1,40 @@
-// Segmented quantised GEMM with fused de-quantise epilogue for sm_100a.
-//
-//   TMA (cp.async.bulk.tensor, no multicast) -> 128B-swizzled shared memory -> tcgen05.mma
-//   (kind::i8 / kind::f8f6f4, cta_group::1, 128x256x32) -> int32 / fp32 accumulators in tensor
-//   memory -> tcgen05.ld -> per-unit scale, running fp32 sum in registers, bias, cast, store.
-//
-// It replaces the CUTLASS mma.sync GemmUniversal of segquant/src/real_quant/real_gemm.cu:208-305,
-// the fp32 scratch it writes, real_dequantize_{,dual_}scaled_kernel of
-// segquant/src/real_quant/dequantizer.cuh:35-73 and the torch-side segment sum / bias add of
-// segquant/layers/SegmentLinear.py:238-241.
-//
-// Persistent kernel, one CTA per SM, warp roles:
-//   warp 0      : TMA producer (one lane)
-//   warp 1      : allocates tensor memory, issues tcgen05.mma (one lane)
-//   warps 2-3   : idle
-//   warps 4-11  : epilogue, two warpgroups; warpgroup h owns tile columns [128h, 128h+128),
-//                 warp w reads TMEM lanes 32*(w%4) .. +31 (one output row per thread)
-//   warps 12-15 : (W4A8 only) expand packed int4 weights to int8 in shared memory
-//
-// K is cut into accumulation units (activation segments x weight-scale groups).  A unit's
-// products are accumulated exactly in tensor memory; at a unit boundary the MMA warp switches to
-// the other TMEM buffer while the epilogue drains the finished one into fp32 registers, so integer
-// sums never cross a scale boundary.  With DualScale the positive and the negative activation
-// tile share the weight tile: two MMAs per K step into the two TMEM buffers.
-//
-// Every wait in this file is bounded: when one runs out the kernel records a code in the device
-// status word, raises a CTA-wide abort flag and every role leaves its loop.
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
+// Host side of the segmented quantised GEMM: argument validation, schedule choice, TMA descriptors
+// and dispatch to the kernel translation units (seg_gemm_tu_*.cu; device code in seg_gemm_kernels.cuh).
 #include <cstdlib>
 
-#include "common.cuh"
+#include "seg_gemm_params.cuh"
 
 namespace sq {
 
-constexpr int BM = 128;        // tile rows (TMEM lanes)
-constexpr int BN = 256;        // widest tile (TMEM columns per buffer); the width in use is GemmParams::bn
-constexpr int BK = 128;        // K elements per pipeline stage (= one 128-byte swizzle row)
-constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
-constexpr int kTmemCols = 512;
-constexpr int kEpiThreads = 256;
+static int g_last_tu = 0;   // (kind * 2 + dual) of the last launch; the trace reader of -DSQ_TRACE builds uses it
 
-constexpr uint32_t kABytes = BM * BK;          // 16 KB
-constexpr uint32_t kBBytes = BN * BK;          // 32 KB
-constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
-constexpr uint32_t kStoreStageBytes = 8 * 2048;  // output staging for TMA stores: 2 KB per epilogue warp
-constexpr int kTabSlots = 4;                     // per-unit scale tables in flight (the epilogue needs 3)
-constexpr uint32_t kTabBytesAll = kTabSlots * 2 * BN * sizeof(float);   // [slot][pos, neg][BN]
+#define SQ_FOR_EACH_TU(X) X(SQ_GEMM_W8A8_I8, false) X(SQ_GEMM_W8A8_I8, true) X(SQ_GEMM_W8A8_F8, false) X(SQ_GEMM_W8A8_F8, true) \
+                          X(SQ_GEMM_W4A8, false) X(SQ_GEMM_W4A8, true)
 
-// status-word codes (low byte = which wait, rest = block index)
-enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitEpi = 7 };
-
-// Written (first writer wins) when a bounded wait gives up: (block index << 8) | WaitCode.
-// One copy per device that loads this library; read and cleared by read_device_status().
-__device__ unsigned long long g_wait_status = 0ull;
-
-// Timeline instrumentation, compiled in only with -DSQ_TRACE (never in the product library):
-// clock64() stamps of block 0's producer (role 0), MMA issuer (role 1) and first epilogue thread (role 2).
-#ifdef SQ_TRACE
-__device__ long long g_trace[3 * 4096];
-#define SQ_STAMP(role, idx) do { if (blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
-#else
-#define SQ_STAMP(role, idx) do { } while (0)
-#endif
-#ifdef SQ_TRACE_EPI   // eight stamps per accumulation unit of block 0's first epilogue thread, in role 0's slots
-#undef SQ_STAMP
-#define SQ_STAMP(role, idx) do { if ((role) != 0 && blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
-#define SQ_EPI(slot) do { if (threadIdx.x == 128 && blockIdx.x == 0 && au < 500) g_trace[8 * au + (slot)] = clock64(); } while (0)
-#else
-#define SQ_EPI(slot) do { } while (0)
-#endif
-#ifdef SQ_TRACE_FINE
-#define SQ_FINE(slot) do { if (lane == 0 && blockIdx.x == 0 && trace_mma < 500) g_trace[2 * 4096 + 8 * trace_mma + (slot)] = clock64(); } while (0)
-#else
-#define SQ_FINE(slot) do { } while (0)
-#endif
-
-struct GemmParams {
-    long long M, N, K;
-    int batch;
-    int num_segs;
-    int seg_bounds[SQ_MAX_SEGS + 1];
-    int group_size;
-    int w_seg_as_batch;
-    int a_batched;
-    int w_batched;   // 0: every problem of the batch uses the same weight matrix
-    const float* sx;
-    const float* sx_neg;
-    long long sx_bs, sx_ss, sx_rs;
-    const void* sw;
-    int sw_is_bf16;
-    long long sw_bs, sw_ss, sw_gs, sw_cs;
-    const void* bias;
-    int bias_dtype;
-    long long bias_bs;
-    void* y;
-    int out_dtype;
-    long long y_bs, y_rs;
-    void* acc_dump;
-    int units;
-    int tiles_m, tiles_n;
-    long long total_tiles;
-    int y_tma;    // output goes through TMA stores (y base / strides are 16-byte aligned)
-    int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
-    int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
-};
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait: gives up after ~4e9 SM cycles (about 2 s), or as soon as another role has raised the
-// abort flag.  The timeout uses the SM-local cycle counter: reading %globaltimer costs microseconds.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-#pragma unroll 1
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > 4000000000ll) {
-                atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
-                *abort_flag = 1;
-                __threadfence_block();
-                return false;
-            }
-        }
+long long read_device_status() {
+    if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
+    long long first = 0;
+#define SQ_X(K, D)                                        \
+    {                                                     \
+        const long long v = tu_read_status<K, D>();       \
+        if (v < 0) return v;                              \
+        if (first == 0) first = v;                        \
     }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// tcgen05.commit: the mbarrier gets one arrival when every tcgen05.mma issued so far by this
-// thread has finished reading shared memory and writing tensor memory.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-template <int KIND>
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (KIND == SQ_GEMM_W8A8_F8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-            : "memory");
-    }
-}
-
-// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-template <uint32_t N>
-__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <uint32_t N>
-__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-
-// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
-// 128-byte swizzle (what TMA SWIZZLE_128B writes).  Low word: start address >> 4 (14 bits) and the
-// leading-dimension offset (unused for swizzled K-major layouts, set to 1).  High word: 8-row groups
-// are 1024 bytes apart (SBO = 64), descriptor version 1 = Blackwell (bit 46), layout type 2 =
-// SWIZZLE_128B (bits 61-63).  Stepping K by one MMA (32 bytes) adds 2 to the low word.
-constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); }
-__device__ __forceinline__ uint64_t smem_desc(uint32_t lo) { return (static_cast<uint64_t>(kSmemDescHi) << 32) | lo; }
-
-// Instruction descriptor: dense, no negate, both operands K-major, D = 128 x bn.
-template <int KIND>
-__device__ __forceinline__ constexpr uint32_t make_idesc() {
-    uint32_t d = 0;
-    if (KIND == SQ_GEMM_W8A8_F8) {
-        d |= 1u << 4;   // D format F32
-        d |= 0u << 7;   // A = E4M3
-        d |= 0u << 10;  // B = E4M3
-    } else {
-        d |= 2u << 4;   // D format S32
-        d |= 1u << 7;   // A = signed 8-bit
-        d |= 1u << 10;  // B = signed 8-bit
-    }
-    d |= static_cast<uint32_t>(BM >> 4) << 24;   // the N field (bits 17-22) is added at run time: bn >> 3
-    return d;
-}
-
-// ---------------------------------------------------------------------------------------------
-// Kernel configuration
-// ---------------------------------------------------------------------------------------------
-template <int KIND, bool DUAL>
-struct Cfg {
-    static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
-    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes + (kW4 ? kBPackedBytes : 0);
-    static constexpr int kStages = (192 * 1024) / kStageBytes;
-    static constexpr int kThreads = kW4 ? 512 : 384;
-    static constexpr uint32_t kTxBytes = kABytes * (DUAL ? 2 : 1) + (kW4 ? kBPackedBytes : kBBytes);
-    // dynamic shared memory: 1 KB alignment slack + stages + scale tables + output staging
-    static constexpr uint32_t kTabBytes = kTabBytesAll;
-    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kTabBytes + kStoreStageBytes + 256;
-};
-
-struct UnitCursor {
-    int s, k, k_end, g;
-};
-
-__device__ __forceinline__ int unit_end(const GemmParams& p, int s, int k) {
-    int e = p.seg_bounds[s + 1];
-    if (p.group_size > 0) {
-        const int ge = (k / p.group_size + 1) * p.group_size;
-        e = ge < e ? ge : e;
-    }
-    return e;
-}
-
-__device__ __forceinline__ float load_sw(const GemmParams& p, long long idx) {
-    if (p.sw_is_bf16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.sw)[idx]);
-    return static_cast<const float*>(p.sw)[idx];
-}
-
-template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst, const float (&v)[16], int valid, bool vec_ok) {
-    if (vec_ok && valid >= 16) {
-        if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    OutT lo = from_float<OutT>(v[8 * i + 2 * j]);
-                    OutT hi = from_float<OutT>(v[8 * i + 2 * j + 1]);
-                    w[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
-                           (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
-                }
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (i < valid) dst[i] = from_float<OutT>(v[i]);
-    }
-}
-
-__device__ __forceinline__ float load_bias(const void* bias, int dtype, long long idx) {
-    if (dtype == SQ_F32) return __ldg(static_cast<const float*>(bias) + idx);
-    if (dtype == SQ_F16) return __half2float(__ldg(static_cast<const __half*>(bias) + idx));
-    return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + idx));
-}
-
-// TMA store of a [rows x 16 columns] box from shared memory; out-of-range rows / columns are clipped.
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-
-// Bias, cast and store of one thread's output row segment (up to 128 columns held in acc[]).
-// Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
-// chunk; the LSU stays free for the MMA / producer warps, every DRAM sector is written whole);
-// otherwise each thread writes its row directly.  `stage` is this warp's 2 KB staging area.
-__device__ __forceinline__ void store_output(const GemmParams& p, const CUtensorMap* map_y, const float (&acc)[128], int nch,
-                                             long long b, long long m, int m_warp, bool row_ok, long long ncol0,
-                                             uint8_t* stage, int lane) {
-    const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
-    if (p.y_tma) {
-        if (m_warp >= p.M) return;                           // nothing of this warp's 32 rows exists (warp-uniform)
-        const uint32_t stage_u32 = smem_u32(stage);
-        const uint32_t buf_bytes = 32u * 16u * esz;          // 1 KB (16-bit) or 2 KB (fp32)
-        const bool two_bufs = esz == 2;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-            const long long nc = ncol0 + ch * 16;
-            if (ch >= nch || nc >= p.N) break;
-            float o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
-            if (p.bias != nullptr) {
-                const long long bo = b * p.bias_bs + nc;
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (nc + j < p.N) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
-            }
-            const uint32_t off = (two_bufs && (ch & 1)) ? buf_bytes : 0u;
-            // the buffer about to be overwritten must have been read by its previous TMA store
-            if (lane == 0) {
-                if (two_bufs) bulk_wait_read<1>();
-                else bulk_wait_read<0>();
-            }
-            __syncwarp();
-            uint8_t* dst = stage + off + lane * 16 * esz;
-            if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(dst), o, 16, true);
-            else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(dst), o, 16, true);
-            else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(dst), o, 16, true);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                tma_store_3d(map_y, stage_u32 + off, static_cast<int>(nc) * esz, m_warp, static_cast<int>(b));   // the map is byte-typed
-                bulk_commit();
-            }
-        }
-        return;
-    }
-    if (!row_ok) return;
-    uint8_t* yrow = static_cast<uint8_t*>(p.y) + (b * p.y_bs + m * p.y_rs + ncol0) * esz;
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(yrow) & 15u) == 0;
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-        const long long nc = ncol0 + ch * 16;
-        int valid = static_cast<int>(p.N - nc);
-        valid = valid > 16 ? 16 : valid;
-        if (valid > 0 && ch < nch) {
-            float o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
-            if (p.bias != nullptr) {
-                const long long bo = b * p.bias_bs + nc;
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (j < valid) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
-            }
-            if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
-            else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
-            else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
-        }
-    }
-}
-
-#include "seg_gemm_epilogue.cuh"
-
-// ---------------------------------------------------------------------------------------------
-// The kernel
-// ---------------------------------------------------------------------------------------------
-template <int KIND, bool DUAL>
-__global__ void __launch_bounds__(Cfg<KIND, DUAL>::kThreads, 1)
-seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
-                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
-                const __grid_constant__ GemmParams p) {
-    using C = Cfg<KIND, DUAL>;
-    constexpr int kStages = C::kStages;
-    constexpr bool kW4 = C::kW4;
-
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_tmem_full[2], bar_tmem_empty[2], bar_epi;
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag_s;
-    volatile int* abort_flag = &abort_flag_s;
-
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [kTabSlots][2][BN]
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-
-    auto stage_a = [&](int st) { return smem_base + st * C::kStageBytes; };
-    auto stage_an = [&](int st) { return smem_base + st * C::kStageBytes + kABytes; };
-    auto stage_b = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1); };
-    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + kBBytes; };
-
-    if (threadIdx.x == 0) {
-        abort_flag_s = 0;
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(smem_u32(&bar_full[i]), 1);
-            mbar_init(smem_u32(&bar_empty[i]), 1);
-            mbar_init(smem_u32(&bar_cvt[i]), 4);
-        }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&bar_tmem_full[i]), 1);
-            mbar_init(smem_u32(&bar_tmem_empty[i]), kEpiThreads / 32);
-        }
-        mbar_init(smem_u32(&bar_epi), kEpiThreads / 32);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0 && lane == 0) {
-        prefetch_tmap(&map_a);
-        if (DUAL) prefetch_tmap(&map_an);
-        prefetch_tmap(&map_w);
-    }
-    if (warp == 1) {
-        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = tmem_base_slot;
-
-    const int tiles_per_batch = p.tiles_m * p.tiles_n;
-
-    if (warp < 4) {
-        // ------------------------------------------------------------------ producer / MMA warps
-        // Each role's whole warp walks the (warp-uniform) loops and polls the barriers; lane 0 issues.
-        reg_dec<kW4 ? 40 : 56>();
-        if (warp == 0) {
-            // ===== TMA producer =====
-            int trace_it = 0; (void)trace_it;
-            int st = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                const int b = static_cast<int>(tile / tiles_per_batch);
-                const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
-                const int m0 = (rem / p.tiles_n) * BM;
-                const int n0 = (rem % p.tiles_n) * p.bn;
-                const int ab = p.a_batched ? b : 0;
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
-                    const int wk_off = p.w_seg_as_batch ? k_beg : 0;
-                    for (int k = k_beg; k < k_end; k += BK) {
-                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
-                        if (lane == 0) {
-                            SQ_STAMP(0, 2 * trace_it);
-                            const uint32_t full = smem_u32(&bar_full[st]);
-                            mbar_arrive_expect_tx(full, kABytes * (DUAL ? 2 : 1) + static_cast<uint32_t>(p.bn) * (kW4 ? BK / 2 : BK));
-                            tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
-                            if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
-                            if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
-                            else tma_load_3d(stage_b(st), &map_w, k - wk_off, n0, wb, full);
-                        }
-                        if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
-                        ++trace_it;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
-                    }
-                }
-            }
-        } else if (warp == 1) {
-            // ===== MMA issuer =====
-            const uint32_t idesc = make_idesc<KIND>() | (static_cast<uint32_t>(p.bn >> 3) << 17);
-            const bool one_buf = DUAL && !p.dual_db;   // DualScale with wide tiles: pos / neg fill all of TMEM
-            int st = 0;
-            uint32_t ph = 0;
-            uint32_t au = 0;       // accumulation-unit counter (selects the TMEM buffer)
-            uint32_t cur_buf = 0;  // buffer of the unit being accumulated
-            int trace_mma = 0; (void)trace_mma;
-            bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    int u_end = k_beg;  // forces "new unit" at the first step of the segment
-                    uint32_t accumulate = 0;
-                    uint32_t d_pos = 0, d_neg = 0;
-                    for (int kb = k_beg; ok && kb < k_end; kb += BK) {
-                        SQ_FINE(0);
-#ifdef SQ_VAR_LANE0_POLL
-                        {   // experiment: only lane 0 polls, the others meet it at the warp barrier
-                            int got = 1;
-                            if (lane == 0) got = mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull) ? 1 : 0;
-                            got = __shfl_sync(0xffffffffu, got, 0);
-                            if (!got) { ok = false; break; }
-                        }
-#else
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
-#endif
-                        if (kW4) {
-                            if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
-                        }
-                        SQ_FINE(1);
-#ifndef SQ_VAR_NOFENCE
-                        tc_fence_after();
-#endif
-                        SQ_FINE(2);
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
-                        const uint32_t a_lo = smem_desc_lo(stage_a(st));
-                        const uint32_t an_lo = smem_desc_lo(stage_an(st));
-                        const uint32_t b_lo = smem_desc_lo(stage_b(st));
-                        const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
-                        if (kb != u_end && kb + kmax <= u_end) {
-                            // the whole stage lies inside the current unit: no checks between the MMAs
-                            if (lane == 0) {
-#pragma unroll
-                                for (int i = 0; i < BK / UMMA_K; ++i) {
-                                    if (i * UMMA_K < kmax) {
-                                        const uint64_t db = smem_desc(b_lo + 2 * i);
-                                        umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
-                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
-                                        SQ_FINE(3 + i);
-                                    }
-                                }
-                            }
-                        } else {
-                            for (int kk = 0; kk < kmax; kk += UMMA_K) {
-                                const int k = kb + kk;
-                                if (k == u_end) {
-                                    // unit boundary: hand the finished buffer to the epilogue, take the next one
-                                    if (k != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
-                                    const uint32_t buf = one_buf ? 0u : (au & 1u);
-                                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                    if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
-                                    tc_fence_after();
-                                    cur_buf = buf;
-                                    d_pos = tmem_base + buf * BN;
-                                    d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                                    accumulate = 0;
-                                    u_end = unit_end(p, s, k);
-                                    ++au;
-                                }
-                                if (lane == 0) {
-                                    const uint64_t db = smem_desc(b_lo + (kk >> 4));
-                                    umma<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
-                                    if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
-                                }
-                                accumulate = 1;
-                            }
-                            if (!ok) break;
-                        }
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 1);
-                        if (lane == 0) umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 2);
-                        SQ_FINE(7);
-                        ++trace_mma;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
-                    }
-                    if (ok && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));  // last unit of the segment
-                    __syncwarp();
-                }
-            }
-        }
-    } else if (warp < 12) {
-        // ------------------------------------------------------------------ epilogue warps
-        reg_inc<kW4 ? 200 : 224>();
-        uint32_t au = 0;
-        for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-            const int b = static_cast<int>(tile / tiles_per_batch);
-            const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
-            const int m0 = (rem / p.tiles_n) * BM;
-            const int n0 = (rem % p.tiles_n) * p.bn;
-            if (!epilogue_tile<KIND, DUAL, false>(p, &map_y, tmem_base, rtab, smem_u32(&bar_tmem_full[0]), smem_u32(&bar_tmem_empty[0]),
-                                                  smem_u32(&bar_epi), abort_flag, au, b, m0, n0, warp, lane,
-                                                  smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048))
-                break;
-        }
-        if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
-    } else {
-        // ------------------------------------------------------------------ int4 -> int8 expansion warps (W4A8)
-        if constexpr (kW4) {
-            reg_dec<72>();
-            const int ct = threadIdx.x - 384;  // 0..127
-            uint32_t it = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    for (int kb = k_beg; kb < k_end; kb += BK, ++it) {
-                        const int st = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1u;
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
-                        const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
-                        uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
-                        // staging tile: bn rows x 64 packed bytes; 16-byte chunk c = (row, quarter)
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int c = ct + i * 128;
-                            if (c >= p.bn * 4) break;
-                            const int row = c >> 2, qd = c & 3;
-                            const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
-                            const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
-                            uint32_t out[8];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                // int8 value = 16 * int4 value: nibble moved to the top of its byte
-                                const uint32_t lo = (in[j] << 4) & 0xF0F0F0F0u;  // even k
-                                const uint32_t hi = in[j] & 0xF0F0F0F0u;         // odd k
-                                out[2 * j] = __byte_perm(lo, hi, 0x5140);
-                                out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
-                            }
-                            // 32 int8 = two 16-byte chunks of the 128-byte row, XOR-swizzled by (row % 8)
-                            uint8_t* drow = dst + row * 128;
-                            const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
-                            *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-                            *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
-                        }
-                        fence_proxy_async_smem();  // generic-proxy writes -> visible to tcgen05.mma
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_cvt[st]));
-                    }
-                }
-            }
-        }
-    }
-
-    // ---------------------------------------------------------------------- teardown
-    if (*abort_flag) {
-        // give copies that may still be in flight time to land before shared memory is released
-        const unsigned long long t0 = global_timer_ns();
-        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        __syncwarp();
-        tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
-    }
+    SQ_FOR_EACH_TU(SQ_X)
+#undef SQ_X
+    return first;
 }
 
 #ifdef SQ_TRACE
 extern "C" int sq_trace_read(long long* out, int n) {
-    if (n > 3 * 4096) n = 3 * 4096;
     if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
-    if (cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n) != cudaSuccess) return SQ_ERR_CUDA;
-    return n;
+#define SQ_X(K, D) \
+    if (g_last_tu == static_cast<int>(K) * 2 + (D ? 1 : 0)) return tu_trace_read<K, D>(out, n);
+    SQ_FOR_EACH_TU(SQ_X)
+#undef SQ_X
+    return SQ_ERR_INVALID_ARG;
 }
 #endif
-
-long long read_device_status() {
-    unsigned long long v = 0, zero = 0;
-    if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
-    if (cudaMemcpyFromSymbol(&v, g_wait_status, sizeof(v)) != cudaSuccess) return SQ_ERR_CUDA;
-    if (v != 0 && cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(zero)) != cudaSuccess) return SQ_ERR_CUDA;
-    return static_cast<long long>(v);
-}
-
-#include "seg_gemm_2cta.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // Host side
@@ -765,6 +112,25 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
     return best;
 }
 
+// longest accumulation unit (K elements) of a segment / group layout
+static int max_unit_k(int num_segs, const int* seg_bounds, int group_size) {
+    int longest = 0;
+    for (int s = 0; s < num_segs; ++s) {
+        int k = seg_bounds[s];
+        const int e = seg_bounds[s + 1];
+        while (k < e) {
+            int ue = e;
+            if (group_size > 0) {
+                const int ge = (k / group_size + 1) * group_size;
+                ue = ge < e ? ge : e;
+            }
+            longest = ue - k > longest ? ue - k : longest;
+            k = ue;
+        }
+    }
+    return longest;
+}
+
 int gemm_num_units(int num_segs, const int* seg_bounds, int group_size) {
     if (num_segs < 1 || num_segs > SQ_MAX_SEGS || seg_bounds == nullptr || group_size < 0) return SQ_ERR_INVALID_ARG;
     int units = 0;
@@ -783,25 +149,6 @@ int gemm_num_units(int num_segs, const int* seg_bounds, int group_size) {
         }
     }
     return units;
-}
-
-template <int KIND, bool DUAL>
-static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
-    using C = Cfg<KIND, DUAL>;
-    static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
-    static bool attr_set[64] = {};
-    int dev = 0;
-    SQ_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-        attr_set[dev] = true;
-    } else if (dev >= 64) {
-        SQ_CUDA_OK(cudaFuncSetAttribute(seg_gemm_kernel<KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    }
-    const long long grid = p.total_tiles < kNumSMs ? p.total_tiles : kNumSMs;
-    seg_gemm_kernel<KIND, DUAL><<<static_cast<int>(grid), C::kThreads, C::kSmemBytes, st>>>(ma, man, mw, my, p);
-    SQ_CUDA_OK(cudaGetLastError());
-    return SQ_OK;
 }
 
 int gemm(const sq_gemm_args* a, cudaStream_t st) {
@@ -875,6 +222,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
     p.bn = sched.bn;
     p.dual_db = (dual && p.bn <= 128) ? 1 : 0;
+    p.all_magic = max_unit_k(a->num_segs, a->seg_bounds, a->group_size) <= 224 ? 1 : 0;
     p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
     if (a->bias_dev)
@@ -917,14 +265,18 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     else rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK, w_box_rows, true, "wq");
     if (rc != SQ_OK) return rc;
 
-    if (sched.two_cta) {
-        if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch_2cta<SQ_GEMM_W8A8_I8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W8A8_I8, false>(ma, man, mw, my, p, st);
-        if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch_2cta<SQ_GEMM_W8A8_F8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W8A8_F8, false>(ma, man, mw, my, p, st);
-        return dual ? launch_2cta<SQ_GEMM_W4A8, true>(ma, man, mw, my, p, st) : launch_2cta<SQ_GEMM_W4A8, false>(ma, man, mw, my, p, st);
+    g_last_tu = a->kind * 2 + (dual ? 1 : 0);
+    switch (a->kind) {
+        case SQ_GEMM_W8A8_I8:
+            return dual ? launch_gemm<SQ_GEMM_W8A8_I8, true>(sched.two_cta, ma, man, mw, my, p, st)
+                        : launch_gemm<SQ_GEMM_W8A8_I8, false>(sched.two_cta, ma, man, mw, my, p, st);
+        case SQ_GEMM_W8A8_F8:
+            return dual ? launch_gemm<SQ_GEMM_W8A8_F8, true>(sched.two_cta, ma, man, mw, my, p, st)
+                        : launch_gemm<SQ_GEMM_W8A8_F8, false>(sched.two_cta, ma, man, mw, my, p, st);
+        default:
+            return dual ? launch_gemm<SQ_GEMM_W4A8, true>(sched.two_cta, ma, man, mw, my, p, st)
+                        : launch_gemm<SQ_GEMM_W4A8, false>(sched.two_cta, ma, man, mw, my, p, st);
     }
-    if (a->kind == SQ_GEMM_W8A8_I8) return dual ? launch<SQ_GEMM_W8A8_I8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W8A8_I8, false>(ma, man, mw, my, p, st);
-    if (a->kind == SQ_GEMM_W8A8_F8) return dual ? launch<SQ_GEMM_W8A8_F8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W8A8_F8, false>(ma, man, mw, my, p, st);
-    return dual ? launch<SQ_GEMM_W4A8, true>(ma, man, mw, my, p, st) : launch<SQ_GEMM_W4A8, false>(ma, man, mw, my, p, st);
 }
 
 }  // namespace sq

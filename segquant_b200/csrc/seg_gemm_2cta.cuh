@@ -1,5 +1,5 @@
 // Two-CTA (cta_group::2) variant of the segmented GEMM: a cluster of two CTAs on neighbouring SMs
-// computes one 256 x bn tile.  Included by seg_gemm.cu (inside namespace sq, after the helpers).
+// computes one 256 x bn tile.  Included by seg_gemm_kernels.cuh (inside namespace sq, after the helpers).
 //
 // Why: with one CTA per tile every SM reads a whole B tile from shared memory for each MMA and
 // fills it by TMA; operand reads plus fills need ~190 bytes/clk of shared-memory bandwidth at full
@@ -19,8 +19,6 @@
 //   * The cluster is synchronised after barrier initialisation and before exit.
 // All waits stay bounded exactly as in the one-CTA kernel.
 #pragma once
-
-constexpr int BM2 = 256;  // tile rows of a CTA pair
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -139,14 +137,14 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int BKS = BK * KSUB;   // K covered by one stage
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_epi;
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* rtab = reinterpret_cast<float*>(smem_gen + kStages * C::kStageBytes);  // [kTabSlots][2][BN]
+    uint8_t* tab = smem_gen + kStages * C::kStageBytes;   // kTabSlots scale-table slots
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -174,7 +172,10 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(smem_u32(&bar_tmem_full[i]), 1);
             mbar_init(smem_u32(&bar_tmem_empty[i]), 2 * (kEpiThreads / 32));
         }
-        mbar_init(smem_u32(&bar_epi), kEpiThreads / 32);
+        for (int i = 0; i < kTabSlots; ++i) {
+            mbar_init(smem_u32(&bar_tab_full[i]), 2);                  // the two builder warps of this CTA
+            mbar_init(smem_u32(&bar_tab_empty[i]), kEpiThreads / 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0 && lane == 0) {
@@ -342,22 +343,18 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     __syncwarp();
                 }
             }
+        } else if (warp >= 2) {
+            // ===== warps 2-3 (both CTAs): per-unit scale tables for this CTA's epilogue =====
+            table_builder<KIND, DUAL, true>(p, tab, smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, first_tile,
+                                            tile_step, static_cast<int>(rank));
         }
     } else if (warp < 12) {
         // ===== epilogue (both CTAs): same as the one-CTA kernel on this CTA's 128 rows =====
         reg_inc<kW4 ? 200 : 224>();
-        uint32_t au = 0;
-        const uint32_t empty_leader = map_to_rank(smem_u32(&bar_tmem_empty[0]), 0);
-        for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
-            const int b = static_cast<int>(tile / tiles_per_batch);
-            const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
-            const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
-            const int n0 = (rem % p.tiles_n) * p.bn;
-            if (!epilogue_tile<KIND, DUAL, true>(p, &map_y, tmem_base, rtab, smem_u32(&bar_tmem_full[0]), empty_leader,
-                                                 smem_u32(&bar_epi), abort_flag, au, b, m0, n0, warp, lane,
-                                                 smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048))
-                break;
-        }
+        epilogue_role<KIND, DUAL, true>(p, &map_y, tmem_base, tab, smem_u32(&bar_tmem_full[0]), map_to_rank(smem_u32(&bar_tmem_empty[0]), 0),
+                                        smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, first_tile, tile_step,
+                                        static_cast<int>(rank), warp, lane,
+                                        smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048);
         if (lane == 0) bulk_wait_all();   // this warp's TMA stores have reached memory before the CTA exits
     } else {
         // ===== int4 -> int8 expansion of this CTA's half of the weight tile (W4A8, both CTAs) =====

@@ -1,27 +1,35 @@
 // De-quantising epilogue shared by the one-CTA and the two-CTA segmented GEMM kernels.
-// Included by seg_gemm.cu inside namespace sq, after store_output().
+// Included by seg_gemm_kernels.cuh inside namespace sq, after store_output().
 //
-// One call handles one output tile for one epilogue warp: for every accumulation unit of the tile (a
-// K-segment, or a weight group inside a segment) it waits for the unit's accumulator in tensor memory,
-// converts it to fp32, multiplies by the unit's reciprocal scales 1 / (s_x * s_w[n]) and adds it to the
-// thread's fp32 row (128 columns at most); after the last unit it adds the bias, casts and stores.
+// Two roles live here.
 //
-// What keeps the drain of a unit short, which matters when units are short (many segments, or
-// group-wise weight scales where a unit is a single 128-byte K stage):
-//   * The scale table of unit u+1 is built while unit u is drained: the scales of u+2 are already in
-//     registers (global loads issued one unit ahead), the table has four slots, and a warp waits for
-//     table u only after every warp has published it one unit earlier, so nobody stalls on a global
-//     load or on the table barrier between two units of a tile.
-//   * Tensor-memory loads are software-pipelined: the load of chunk i+1 is in flight while chunk i is
-//     converted and accumulated.
-//   * The table is read with 128-bit shared loads (same address in all lanes: a broadcast).
-//   * int32 -> fp32 uses the magic-number trick (one integer add, one float subtract, both full-rate)
-//     instead of the quarter-rate conversion instruction whenever the unit is short enough for every
-//     accumulator to lie in [-2^22, 2^22): K_unit * 128 * 128 < 2^22, i.e. K_unit <= 224.  Both forms
-//     are exact, so results do not depend on which one ran.
+// table_builder (warps 2 and 3 of the control warpgroup, 64 threads): walks the accumulation units of
+// every tile this CTA owns (a unit = a K-segment, or a weight group inside a segment) and, up to
+// kTabSlots units ahead of the epilogue, fills a shared-memory slot per unit with
+//   r[n]   = 1 / (s_x * s_w[n])   for the tile's bn columns, positive and (DualScale) negative side,
+//   rx[m]  = 1 / s_x[m]           for the tile's 128 rows when activation scales are per token
+//                                 (r[n] is then 1 / s_w[n]).
+// Global loads of the next unit's scales are issued before the current unit is written, so the
+// builder's own period is a few hundred cycles.  Slots cycle through "full" / "empty" mbarriers.
+//
+// epilogue_tile (warps 4-11): for every unit waits for the slot and for the accumulator in tensor
+// memory, and adds float(acc) * r[n] (* rx[m]) into the thread's fp32 row (128 columns at most); after
+// the last unit it adds the bias, casts and stores.  Nothing but the drain is on its critical path:
+// no cursor arithmetic, no global loads, no divisions.  Tensor-memory loads are software-pipelined
+// (the next chunk is in flight while the current one is converted), the table is read with 128-bit
+// broadcast loads, the fp32 math uses the packed two-wide instructions, and int32 -> fp32 uses one
+// integer add and one float subtract (both full rate) instead of the quarter-rate conversion when every
+// unit of the launch has K_unit <= 224, which guarantees |acc| < 2^22.  All forms are exact, so results
+// do not depend on which ran.
 #pragma once
 
 constexpr int kMagicMaxUnitK = 224;
+
+// ---- slot layout (bytes): r_pos[BN] | r_neg[BN] | rx_pos[128] | rx_neg[128]
+constexpr uint32_t kSlotRNeg = BN * 4;
+constexpr uint32_t kSlotRx = 2 * BN * 4;
+constexpr uint32_t kSlotRxNeg = kSlotRx + BM * 4;
+static_assert(kSlotRxNeg + BM * 4 <= kTabSlotBytes, "table slot too small");
 
 // tcgen05.wait::ld that also "touches" the destination registers of the load it completes, so the
 // compiler cannot schedule a use of them above the wait.
@@ -32,69 +40,167 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[16]) {
                  :
                  : "memory");
 }
-
-template <int KIND, bool MAGIC>
-__device__ __forceinline__ float acc_to_float(uint32_t v) {
-    if constexpr (KIND == SQ_GEMM_W8A8_F8) return __uint_as_float(v);
-    else if constexpr (MAGIC) return __uint_as_float(v + 0x4B400000u) - 12582912.0f;   // exact for v in [-2^22, 2^22)
-    else return static_cast<float>(static_cast<int32_t>(v));
+// Tile index -> batch, first row of THIS CTA's 128 rows, first column of the tile.
+template <bool PAIR>
+__device__ __forceinline__ void tile_coords(const GemmParams& p, long long tile, int rank, int& b, int& m0, int& n0) {
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    b = static_cast<int>(tile / tiles_per_batch);
+    const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+    m0 = PAIR ? (rem / p.tiles_n) * (2 * BM) + rank * BM : (rem / p.tiles_n) * BM;
+    n0 = (rem % p.tiles_n) * p.bn;
 }
 
-// Position of an accumulation unit inside a tile: segment s, first K index k.  s == num_segs: past the end.
-struct UnitPos {
-    int s, k;
+// ---------------------------------------------------------------------------------------------
+// Scale-table builder: 64 threads (warps 2 and 3).
+// ---------------------------------------------------------------------------------------------
+struct BuilderRegs {
+    float sw[4];     // weight scales of columns t, t+64, t+128, t+192 of the tile
+    float sx, sxn;   // segment activation scales (per-tensor mode)
+    float rx[2];     // per-token activation scales of rows t, t+64 (per-token mode)
+    float rxn[2];
 };
-__device__ __forceinline__ void unit_next(const GemmParams& p, UnitPos& u) {
-    const int e = unit_end(p, u.s, u.k);
-    if (e < p.seg_bounds[u.s + 1]) {
-        u.k = e;
-    } else {
-        ++u.s;
-        u.k = e;   // segments are contiguous: the next one starts where this one ends
-    }
-}
 
-// Raw scales of one unit as this thread needs them: the weight scale of the table column it builds
-// (column n0 + epi_tid) and the activation scales -- of the segment, or with per-token scales of the
-// thread's own row (the table then holds 1 / s_w only).
 template <bool DUAL>
-__device__ __forceinline__ void load_unit_scales(const GemmParams& p, const UnitPos& u, int b, long long n, bool col_ok, int m,
-                                                 bool row_ok, bool per_token, float& sw, float& sx, float& sxn) {
-    sw = 1.0f;
-    sx = 1.0f;
-    sxn = 1.0f;
-    if (u.s >= p.num_segs) return;
-    const int g = p.group_size > 0 ? u.k / p.group_size : 0;
-    if (col_ok) sw = load_sw(p, b * p.sw_bs + u.s * p.sw_ss + g * p.sw_gs + n * p.sw_cs);
-    const long long off = b * p.sx_bs + u.s * p.sx_ss + (per_token ? m * p.sx_rs : 0);
-    if (!per_token || row_ok) {
-        sx = __ldg(p.sx + off);
-        if (DUAL) sxn = __ldg(p.sx_neg + off);
+__device__ __forceinline__ void builder_load(const GemmParams& p, BuilderRegs& r, int t, int b, int m0, int n0, int s, int g,
+                                             bool per_token) {
+    const long long sw_base = b * p.sw_bs + s * p.sw_ss + g * p.sw_gs;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = t + 64 * i;
+        const long long n = n0 + c;
+        r.sw[i] = (c < p.bn && n < p.N) ? load_sw(p, sw_base + n * p.sw_cs) : 1.0f;
+    }
+    const long long sx_base = b * p.sx_bs + s * p.sx_ss;
+    r.sx = 1.0f;
+    r.sxn = 1.0f;
+    if (!per_token) {
+        r.sx = __ldg(p.sx + sx_base);
+        if (DUAL) r.sxn = __ldg(p.sx_neg + sx_base);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const long long m = m0 + t + 64 * j;
+        r.rx[j] = 1.0f;
+        r.rxn[j] = 1.0f;
+        if (per_token && m < p.M) {
+            r.rx[j] = __ldg(p.sx + sx_base + m * p.sx_rs);
+            if (DUAL) r.rxn[j] = __ldg(p.sx_neg + sx_base + m * p.sx_rs);
+        }
     }
 }
 
-template <int KIND, bool DUAL>
-__device__ __forceinline__ void write_table(float* rtab, uint32_t slot, int epi_tid, float sw, float sx, float sxn, bool col_ok,
-                                            bool per_token) {
-    float r = 0.0f, rn = 0.0f;
-    if (col_ok) {
-        r = 1.0f / ((per_token ? 1.0f : sx) * sw);
-        if (DUAL) rn = 1.0f / ((per_token ? 1.0f : sxn) * sw);
-        if (KIND == SQ_GEMM_W4A8) { r *= 0.0625f; rn *= 0.0625f; }   // int4 weights are expanded as 16*w
+template <int KIND, bool DUAL, bool PAIR>
+__device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab, uint32_t bar_tab_full, uint32_t bar_tab_empty,
+                                              volatile int* abort_flag, long long first_tile, long long tile_step, int rank) {
+    const int t = threadIdx.x - 64;   // 0..63
+    const int lane = threadIdx.x & 31;
+    const bool per_token = p.sx_rs != 0;
+    uint32_t au = 0;
+    BuilderRegs cur, nxt;
+    for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
+        int b, m0, n0;
+        tile_coords<PAIR>(p, tile, rank, b, m0, n0);
+        int s = 0, k = 0, g = 0;   // unit cursor: segment, first K index, weight group of k (k / group_size)
+        builder_load<DUAL>(p, cur, t, b, m0, n0, s, g, per_token);
+        for (int u = 0; u < p.units; ++u, ++au) {
+            // end of this unit and cursor of the next one (segments and groups are walked, never divided)
+            const int seg_end = p.seg_bounds[s + 1];
+            const int grp_end = p.group_size > 0 ? (g + 1) * p.group_size : seg_end;
+            const int ke = grp_end < seg_end ? grp_end : seg_end;
+            const int s2 = ke == seg_end ? s + 1 : s;
+            (void)k;
+            const int g2 = (p.group_size > 0 && ke == grp_end) ? g + 1 : g;
+            if (u + 1 < p.units) builder_load<DUAL>(p, nxt, t, b, m0, n0, s2, g2, per_token);
+
+            const uint32_t slot = au & (kTabSlots - 1);
+            const uint32_t par = (au / kTabSlots) & 1u;
+            if (!mbar_wait(bar_tab_empty + slot * 8, par ^ 1u, abort_flag, kWaitTabEmpty)) return;
+            uint8_t* sl = tab + slot * kTabSlotBytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = t + 64 * i;
+                float r = 1.0f / (cur.sx * cur.sw[i]);
+                float rn = DUAL ? 1.0f / (cur.sxn * cur.sw[i]) : 0.0f;
+                if (KIND == SQ_GEMM_W4A8) { r *= 0.0625f; rn *= 0.0625f; }   // int4 weights are expanded as 16*w
+                reinterpret_cast<float*>(sl)[c] = r;
+                if (DUAL) reinterpret_cast<float*>(sl + kSlotRNeg)[c] = rn;
+            }
+            if (per_token) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    reinterpret_cast<float*>(sl + kSlotRx)[t + 64 * j] = 1.0f / cur.rx[j];
+                    if (DUAL) reinterpret_cast<float*>(sl + kSlotRxNeg)[t + 64 * j] = 1.0f / cur.rxn[j];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tab_full + slot * 8);
+            cur = nxt;
+            s = s2;
+            g = g2;
+            k = ke;
+        }
     }
-    rtab[(slot * 2 + 0) * BN + epi_tid] = r;
-    if (DUAL) rtab[(slot * 2 + 1) * BN + epi_tid] = rn;
 }
 
-// acc[0 .. 16 nch) += float(accumulator columns) * table, for one unit.  The TMEM load of the next
-// 16-column chunk is issued before the current one is consumed.  rt_pos / t_pos address the positive
-// side; the negative side sits BN floats / neg_cols TMEM columns further.
-template <int KIND, bool DUAL, bool MAGIC>
-__device__ __forceinline__ void drain_unit(const GemmParams& p, float (&acc)[128], uint32_t t_pos, const float* rt_pos, int nch,
-                                           bool per_token, float rxm, float rxnm, int b, int unit_in_tile, int m, bool row_ok,
-                                           int ncol0) {
+// ---------------------------------------------------------------------------------------------
+// Drain
+// ---------------------------------------------------------------------------------------------
+// 16 columns: acc += float(v) * r (* rx).  Packed two-wide fp32 instructions (fma / add / mul .f32x2)
+// halve the issue slots and the instruction bytes of the drain, whose straight-line code is otherwise
+// limited by instruction fetch.  Each component is rounded exactly like the scalar instruction.
+template <int KIND, bool MAGIC, bool PER_TOKEN>
+__device__ __forceinline__ void fma16(float* acc, const uint32_t (&v)[16], const float* rt, float rx) {
+    const float4* rt4 = reinterpret_cast<const float4*>(rt);
+    const float2 rx2 = make_float2(rx, rx);
+    const float2 unmagic = make_float2(-12582912.0f, -12582912.0f);
+#pragma unroll
+    for (int j4 = 0; j4 < 4; ++j4) {
+        const float4 r4 = rt4[j4];
+#pragma unroll
+        for (int hp = 0; hp < 2; ++hp) {
+            const int j = 4 * j4 + 2 * hp;
+            float2 r = hp ? make_float2(r4.z, r4.w) : make_float2(r4.x, r4.y);
+            if (PER_TOKEN) r = __fmul2_rn(r, rx2);
+            float2 f;
+            if constexpr (KIND == SQ_GEMM_W8A8_F8) {
+                f = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            } else if constexpr (MAGIC) {   // exact for accumulators in [-2^22, 2^22)
+                f = __fadd2_rn(make_float2(__uint_as_float(v[j] + 0x4B400000u), __uint_as_float(v[j + 1] + 0x4B400000u)), unmagic);
+            } else {
+                f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])), static_cast<float>(static_cast<int32_t>(v[j + 1])));
+            }
+#ifdef SQ_EXP_SCALAR
+            acc[j] = fmaf(f.x, r.x, acc[j]);
+            acc[j + 1] = fmaf(f.y, r.y, acc[j + 1]);
+#else
+            const float2 a = __ffma2_rn(f, r, make_float2(acc[j], acc[j + 1]));
+            acc[j] = a.x;
+            acc[j + 1] = a.y;
+#endif
+        }
+    }
+}
+
+template <int KIND>
+__device__ __forceinline__ void dump16(const GemmParams& p, const uint32_t (&v)[16], int b, int unit_in_tile, int sides, int side, int m,
+                                       int ncol) {
+    // raw accumulators for the parity tests: [batch][unit][side][M][N] int32
+    const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
+    int32_t* d = static_cast<int32_t*>(p.acc_dump) + (u * sides + side) * p.M * p.N + static_cast<long long>(m) * p.N + ncol;
+#pragma unroll   // static indices only: a dynamic index would move the accumulator registers to local memory
+    for (int j = 0; j < 16; ++j)
+        if (ncol + j < p.N) d[j] = KIND == SQ_GEMM_W4A8 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
+}
+
+// Drain of one unit: the tensor-memory load of the next 16-column chunk is in flight while the current
+// one is consumed.  rt_pos / t_pos address the positive side; the negative side sits BN floats /
+// neg_cols TMEM columns further.  The variant (MAGIC, PER_TOKEN, DUMP) is chosen once per unit so the
+// code that runs is one contiguous block.
+template <int KIND, bool DUAL, bool MAGIC, bool PER_TOKEN, bool DUMP>
+__device__ __forceinline__ void drain_unit(const GemmParams& p, float (&acc)[128], uint32_t t_pos, const float* rt_pos, int hcols,
+                                           float rxm, float rxnm, int b, int unit_in_tile, int m, bool row_ok, int ncol0) {
     constexpr int SIDES = DUAL ? 2 : 1;
-    const int nld = nch * SIDES;
+    const int nld = (hcols >> 4) * SIDES;             // 16-column chunks per unit, sides interleaved
     const uint32_t neg_cols = p.dual_db ? 128u : static_cast<uint32_t>(BN);
     uint32_t va[16], vb[16];
     tmem_ld_x16(t_pos, va);
@@ -102,128 +208,123 @@ __device__ __forceinline__ void drain_unit(const GemmParams& p, float (&acc)[128
 #pragma unroll
     for (int i = 0; i < 8 * SIDES; ++i) {
         if (i >= nld) break;
-        const int ch = DUAL ? (i >> 1) : i;
-        const bool neg = DUAL && (i & 1);
         uint32_t (&cur)[16] = (i & 1) ? vb : va;
         uint32_t (&nxt)[16] = (i & 1) ? va : vb;
-        if (i + 1 < nld) {
-            const int chn = DUAL ? ((i + 1) >> 1) : (i + 1);
-            tmem_ld_x16(t_pos + ((DUAL && ((i + 1) & 1)) ? neg_cols : 0u) + chn * 16, nxt);
-        }
-        const float4* rt4 = reinterpret_cast<const float4*>(rt_pos + (neg ? BN : 0) + ch * 16);
-        const float rx = neg ? rxnm : rxm;
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-            const float4 r4 = rt4[j4];
-            float r0 = r4.x, r1 = r4.y, r2 = r4.z, r3 = r4.w;
-            if (per_token) { r0 *= rx; r1 *= rx; r2 *= rx; r3 *= rx; }
-            acc[ch * 16 + 4 * j4 + 0] = fmaf(acc_to_float<KIND, MAGIC>(cur[4 * j4 + 0]), r0, acc[ch * 16 + 4 * j4 + 0]);
-            acc[ch * 16 + 4 * j4 + 1] = fmaf(acc_to_float<KIND, MAGIC>(cur[4 * j4 + 1]), r1, acc[ch * 16 + 4 * j4 + 1]);
-            acc[ch * 16 + 4 * j4 + 2] = fmaf(acc_to_float<KIND, MAGIC>(cur[4 * j4 + 2]), r2, acc[ch * 16 + 4 * j4 + 2]);
-            acc[ch * 16 + 4 * j4 + 3] = fmaf(acc_to_float<KIND, MAGIC>(cur[4 * j4 + 3]), r3, acc[ch * 16 + 4 * j4 + 3]);
-        }
-        if (p.acc_dump != nullptr && row_ok) {
-            // raw accumulators for the parity tests: [batch][unit][side][M][N] int32
-            const long long u = static_cast<long long>(b) * p.units + unit_in_tile;
-            int32_t* d = static_cast<int32_t*>(p.acc_dump) + (u * SIDES + (neg ? 1 : 0)) * p.M * p.N + static_cast<long long>(m) * p.N + ncol0;
-#pragma unroll   // static indices only: a dynamic index would move the accumulator registers to local memory
-            for (int j = 0; j < 16; ++j)
-                if (ncol0 + ch * 16 + j < p.N)
-                    d[ch * 16 + j] = KIND == SQ_GEMM_W4A8 ? (static_cast<int32_t>(cur[j]) >> 4) : static_cast<int32_t>(cur[j]);
-        }
+        if (i + 1 < nld)
+            tmem_ld_x16(t_pos + static_cast<uint32_t>(((i + 1) / SIDES) * 16) + ((DUAL && ((i + 1) & 1)) ? neg_cols : 0u), nxt);
+        const int c0 = (i / SIDES) * 16;
+        const bool neg = DUAL && (i & 1);
+        fma16<KIND, MAGIC, PER_TOKEN>(&acc[c0], cur, rt_pos + (neg ? BN : 0) + c0, neg ? rxnm : rxm);
+        if (DUMP && row_ok) dump16<KIND>(p, cur, b, unit_in_tile, SIDES, neg ? 1 : 0, m, ncol0 + c0);
         if (i + 1 < nld) tmem_ld_wait_on(nxt);
     }
 }
 
 // One tile for one epilogue warp.  `bar_tmem_empty` is the address arrivals go to: the CTA's own
 // barrier array, or (PAIR) the cluster address of the leader's.  Returns false after a wait gave up.
-template <int KIND, bool DUAL, bool PAIR>
-__device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, float* rtab,
-                                              uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_epi,
-                                              volatile int* abort_flag, uint32_t& au, int b, int m0, int n0, int warp, int lane,
-                                              uint8_t* stage) {
-    const int epi_tid = threadIdx.x - 128;       // 0..255
+template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP>
+__device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+                                              uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
+                                              uint32_t bar_tab_empty, volatile int* abort_flag, uint32_t& au, int b, int m0, int n0,
+                                              int warp, int lane, uint8_t* stage) {
     const int q = warp & 3;                      // TMEM lane quarter of this warp
     const int h = (warp - 4) >> 2;               // column half
-    const bool per_token = p.sx_rs != 0;
     const bool one_buf = DUAL && !p.dual_db;
     const int hcols = p.bn >> 1;                 // columns per warpgroup: 64, 96 or 128
-    const int nch = hcols >> 4;                  // 16-column chunks per thread
     const int m = m0 + q * 32 + lane;
     const bool row_ok = m < p.M;
-    const long long n_tab = n0 + epi_tid;
-    const bool col_ok = n_tab < p.N && epi_tid < p.bn;
 
     float acc[128];
 #pragma unroll
     for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
 
-    // table of the first unit (its latency is exposed once per tile), then look one unit further ahead
-    UnitPos wr = {0, 0};
-    float sw_n, sx_n, sxn_n;          // raw scales of the unit `wr` points at
-    float sx_c, sxn_c;                // per-token scales of the unit being drained
-    load_unit_scales<DUAL>(p, wr, b, n_tab, col_ok, m, row_ok, per_token, sw_n, sx_n, sxn_n);
-    write_table<KIND, DUAL>(rtab, au & (kTabSlots - 1), epi_tid, sw_n, sx_n, sxn_n, col_ok, per_token);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_epi);
-    sx_c = sx_n;
-    sxn_c = sxn_n;
-    unit_next(p, wr);
-    load_unit_scales<DUAL>(p, wr, b, n_tab, col_ok, m, row_ok, per_token, sw_n, sx_n, sxn_n);
-
-    UnitPos rd = {0, 0};
-    int unit_in_tile = 0;
-    while (rd.s < p.num_segs) {
-        const int ke = unit_end(p, rd.s, rd.k);
-        SQ_EPI(0);
-        // table of this unit: published by every warp one unit ago (or just above for the first unit)
-        if (!mbar_wait(bar_epi, au & 1u, abort_flag, kWaitEpi)) return false;
-        SQ_EPI(1);
+    for (int u = 0; u < p.units; ++u) {
+        const uint32_t slot = au & (kTabSlots - 1);
+        if (!mbar_wait(bar_tab_full + slot * 8, (au / kTabSlots) & 1u, abort_flag, kWaitTabFull)) return false;
+        const uint8_t* sl = tab + slot * kTabSlotBytes;
         float rxm = 1.0f, rxnm = 1.0f;
-        if (per_token) {
-            rxm = 1.0f / sx_c;
-            if (DUAL) rxnm = 1.0f / sxn_c;
+        if (PER_TOKEN && p.sx_rs != 0) {
+            rxm = reinterpret_cast<const float*>(sl + kSlotRx)[q * 32 + lane];
+            if (DUAL) rxnm = reinterpret_cast<const float*>(sl + kSlotRxNeg)[q * 32 + lane];
         }
-        // publish the next unit's table and start the loads of the one after it
-        if (wr.s < p.num_segs) {
-            write_table<KIND, DUAL>(rtab, (au + 1) & (kTabSlots - 1), epi_tid, sw_n, sx_n, sxn_n, col_ok, per_token);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_epi);
-            SQ_EPI(2);
-            sx_c = sx_n;
-            sxn_c = sxn_n;
-            unit_next(p, wr);
-            load_unit_scales<DUAL>(p, wr, b, n_tab, col_ok, m, row_ok, per_token, sw_n, sx_n, sxn_n);
-        }
-        SQ_EPI(3);
         const uint32_t buf = one_buf ? 0u : (au & 1u);
         const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
         if (!mbar_wait(bar_tmem_full + buf * 8, tph, abort_flag, kWaitTmemFull)) return false;
-        SQ_EPI(4);
         tc_fence_after();
         if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
+        SQ_EPI(0);
         const uint32_t t_pos = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * hcols;
-        const float* rt_pos = rtab + ((au & (kTabSlots - 1)) * 2) * BN + h * hcols;
-        if (KIND != SQ_GEMM_W8A8_F8 && ke - rd.k <= kMagicMaxUnitK)
-            drain_unit<KIND, DUAL, true>(p, acc, t_pos, rt_pos, nch, per_token, rxm, rxnm, b, unit_in_tile, m, row_ok, n0 + h * hcols);
-        else
-            drain_unit<KIND, DUAL, false>(p, acc, t_pos, rt_pos, nch, per_token, rxm, rxnm, b, unit_in_tile, m, row_ok, n0 + h * hcols);
-        // buffer drained: give it back to the MMA warp
-        SQ_EPI(5);
+        const float* rt_pos = reinterpret_cast<const float*>(sl) + h * hcols;
+#ifdef SQ_TRACE_EPI
+        {   // latency of one extra tensor-memory load + wait, measured in place
+            uint32_t tmp[16];
+            SQ_EPI(1);
+            tmem_ld_x16(t_pos, tmp);
+            tmem_ld_wait_on(tmp);
+            SQ_EPI(2);
+            asm volatile("" ::"r"(tmp[0]), "r"(tmp[15]));
+        }
+#endif
+        // every lane runs the drain (its tensor-memory loads are warp-collective); rows past M only skip the dump stores
+        drain_unit<KIND, DUAL, MAGIC, PER_TOKEN, DUMP>(p, acc, t_pos, rt_pos, hcols, rxm, rxnm, b, u, m, row_ok, n0 + h * hcols);
+        // accumulator and table slot consumed: hand both back
+        SQ_EPI(3);
         tc_fence_before();
         __syncwarp();
-        SQ_EPI(6);
         if (lane == 0) {
             if constexpr (PAIR) mbar_arrive_cluster(bar_tmem_empty + buf * 8);
             else mbar_arrive(bar_tmem_empty + buf * 8);
+            mbar_arrive(bar_tab_empty + slot * 8);
         }
         if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
-        SQ_EPI(7);
+        SQ_EPI(4);
         ++au;
-        ++unit_in_tile;
-        unit_next(p, rd);
     }
     // ---- bias, cast, store
-    store_output(p, map_y, acc, nch, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane);
+    store_output(p, map_y, acc, hcols >> 4, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane);
     return true;
+}
+
+// All tiles of this CTA for one epilogue warp, with ONE drain variant.
+template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP>
+__device__ __forceinline__ void epilogue_tiles(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+                                               uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
+                                               uint32_t bar_tab_empty, volatile int* abort_flag, long long first_tile,
+                                               long long tile_step, int rank, int warp, int lane, uint8_t* stage) {
+    uint32_t au = 0;
+    for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
+        int b, m0, n0;
+        tile_coords<PAIR>(p, tile, rank, b, m0, n0);
+        if (!epilogue_tile<KIND, DUAL, PAIR, MAGIC, PER_TOKEN, DUMP>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full,
+                                                                     bar_tab_empty, abort_flag, au, b, m0, n0, warp, lane, stage))
+            break;
+    }
+}
+
+// The epilogue role.  The drain variant is picked once per launch and each variant is its own copy of
+// the tile loop: what runs is then one compact, contiguous block of code.  With the choice made per
+// unit inside one loop the variants' blocks interleaved, the drain overflowed the instruction cache
+// and ran 2x slower (measured: "no instruction" was the top stall reason).
+//   DUMP       parity tests (raw accumulators are also written): generic arithmetic,
+//   PER_TOKEN  per-row activation scales multiply the table entry,
+//   MAGIC      every unit of the launch is short enough for the magic-number int->float conversion.
+template <int KIND, bool DUAL, bool PAIR>
+__device__ __forceinline__ void epilogue_role(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+                                              uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
+                                              uint32_t bar_tab_empty, volatile int* abort_flag, long long first_tile,
+                                              long long tile_step, int rank, int warp, int lane, uint8_t* stage) {
+#define SQ_EPI_RUN(MAGIC, PT, DUMP)                                                                                               \
+    epilogue_tiles<KIND, DUAL, PAIR, MAGIC, PT, DUMP>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full,     \
+                                                      bar_tab_empty, abort_flag, first_tile, tile_step, rank, warp, lane, stage)
+    constexpr bool kInt = KIND != SQ_GEMM_W8A8_F8;
+    if (p.acc_dump != nullptr) {
+        SQ_EPI_RUN(false, true, true);
+    } else if (p.sx_rs != 0) {
+        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, true, false);
+        else SQ_EPI_RUN(false, true, false);
+    } else {
+        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, false, false);
+        else SQ_EPI_RUN(false, false, false);
+    }
+#undef SQ_EPI_RUN
 }

@@ -1,0 +1,76 @@
+// Constants and the kernel parameter block shared by the host dispatch (seg_gemm.cu) and the kernel
+// translation units (seg_gemm_tu_*.cu, which include seg_gemm_kernels.cuh).
+#pragma once
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace sq {
+
+
+constexpr int BM = 128;        // tile rows (TMEM lanes)
+constexpr int BN = 256;        // widest tile (TMEM columns per buffer); the width in use is GemmParams::bn
+constexpr int BK = 128;        // K elements per pipeline stage (= one 128-byte swizzle row)
+constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int kTmemCols = 512;
+constexpr int kEpiThreads = 256;
+
+constexpr uint32_t kABytes = BM * BK;          // 16 KB
+constexpr uint32_t kBBytes = BN * BK;          // 32 KB
+constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
+constexpr uint32_t kStoreStageBytes = 8 * 2048;  // output staging for TMA stores: 2 KB per epilogue warp
+constexpr int kTabSlots = 4;                     // per-unit scale tables the builder warps may run ahead
+constexpr uint32_t kTabSlotBytes = 3072;         // r[2][BN] + rx[2][BM] floats, see seg_gemm_epilogue.cuh
+constexpr uint32_t kTabBytesAll = kTabSlots * kTabSlotBytes;
+
+// status-word codes (low byte = which wait, rest = block index)
+enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitTabFull = 7, kWaitTabEmpty = 8 };
+
+constexpr int BM2 = 256;  // tile rows of a CTA pair
+
+struct GemmParams {
+    long long M, N, K;
+    int batch;
+    int num_segs;
+    int seg_bounds[SQ_MAX_SEGS + 1];
+    int group_size;
+    int w_seg_as_batch;
+    int a_batched;
+    int w_batched;   // 0: every problem of the batch uses the same weight matrix
+    const float* sx;
+    const float* sx_neg;
+    long long sx_bs, sx_ss, sx_rs;
+    const void* sw;
+    int sw_is_bf16;
+    long long sw_bs, sw_ss, sw_gs, sw_cs;
+    const void* bias;
+    int bias_dtype;
+    long long bias_bs;
+    void* y;
+    int out_dtype;
+    long long y_bs, y_rs;
+    void* acc_dump;
+    int units;
+    int tiles_m, tiles_n;
+    long long total_tiles;
+    int y_tma;    // output goes through TMA stores (y base / strides are 16-byte aligned)
+    int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
+    int all_magic;  // every accumulation unit has K <= 224: int32 accumulators stay inside [-2^22, 2^22)
+    int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
+};
+
+// One explicit specialisation per (KIND, DUAL), each in its own translation unit so the twelve-odd
+// kernel instantiations compile in parallel.
+template <int KIND, bool DUAL>
+int launch_gemm(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my,
+                const GemmParams& p, cudaStream_t st);
+// Reads and clears the status word kernels of that translation unit write when a bounded wait gives up.
+template <int KIND, bool DUAL>
+long long tu_read_status();
+#ifdef SQ_TRACE
+template <int KIND, bool DUAL>
+int tu_trace_read(long long* out, int n);
+#endif
+
+}  // namespace sq

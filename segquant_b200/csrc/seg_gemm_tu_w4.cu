@@ -1,0 +1,4 @@
+// Kernel translation unit: SQ_GEMM_W4A8.  All code is in seg_gemm_kernels.cuh.
+#define SQ_TU_KIND SQ_GEMM_W4A8
+#define SQ_TU_DUAL false
+#include "seg_gemm_kernels.cuh"
