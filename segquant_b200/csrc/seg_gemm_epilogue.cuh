@@ -8,7 +8,8 @@
 // kTabSlots units ahead of the epilogue, fills a shared-memory slot per unit with
 //   r[n]   = 1 / (s_x * s_w[n])   for the tile's bn columns, positive and (DualScale) negative side,
 //   rx[m]  = 1 / s_x[m]           for the tile's 128 rows when activation scales are per token
-//                                 (r[n] is then 1 / s_w[n]).
+//                                 (r[n] is then 1 / s_w[n]),
+//   bias[n]                       as fp32, in the slot of the tile's last unit.
 // Global loads of the next unit's scales are issued before the current unit is written, so the
 // builder's own period is a few hundred cycles.  Slots cycle through "full" / "empty" mbarriers.
 //
@@ -25,11 +26,12 @@
 
 constexpr int kMagicMaxUnitK = 224;
 
-// ---- slot layout (bytes): r_pos[BN] | r_neg[BN] | rx_pos[128] | rx_neg[128]
+// ---- slot layout (bytes): r_pos[BN] | r_neg[BN] | rx_pos[128] | rx_neg[128] | bias[BN] (last unit of a tile only)
 constexpr uint32_t kSlotRNeg = BN * 4;
 constexpr uint32_t kSlotRx = 2 * BN * 4;
 constexpr uint32_t kSlotRxNeg = kSlotRx + BM * 4;
-static_assert(kSlotRxNeg + BM * 4 <= kTabSlotBytes, "table slot too small");
+constexpr uint32_t kSlotBias = kSlotRx + 2 * BM * 4;
+static_assert(kSlotBias + BN * 4 <= kTabSlotBytes, "table slot too small");
 
 // tcgen05.wait::ld that also "touches" the destination registers of the load it completes, so the
 // compiler cannot schedule a use of them above the wait.
@@ -58,33 +60,60 @@ struct BuilderRegs {
     float sx, sxn;   // segment activation scales (per-tensor mode)
     float rx[2];     // per-token activation scales of rows t, t+64 (per-token mode)
     float rxn[2];
+    float bias[4];   // bias of the same four columns (loaded for the last unit of a tile only)
 };
 
+// Every address formed here is in bounds even for columns / rows outside the problem (the index is
+// clamped to a valid one and the value replaced afterwards), and the optional pointers (bias, per-token
+// scales) are only dereferenced inside a block guarded by a warp-uniform test, through plain loads: a
+// load the compiler is free to speculate (a read-only intrinsic under a select) must never see a null
+// or out-of-range address.
 template <bool DUAL>
 __device__ __forceinline__ void builder_load(const GemmParams& p, BuilderRegs& r, int t, int b, int m0, int n0, int s, int g,
-                                             bool per_token) {
+                                             bool per_token, bool want_bias) {
     const long long sw_base = b * p.sw_bs + s * p.sw_ss + g * p.sw_gs;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int c = t + 64 * i;
-        const long long n = n0 + c;
-        r.sw[i] = (c < p.bn && n < p.N) ? load_sw(p, sw_base + n * p.sw_cs) : 1.0f;
+        const bool valid = c < p.bn && n0 + c < p.N;
+        const long long n = valid ? n0 + c : n0;          // n0 < N always
+        const float w = load_sw(p, sw_base + n * p.sw_cs);
+        r.sw[i] = valid ? w : 1.0f;
+        r.bias[i] = 0.0f;
+    }
+    if (want_bias) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = t + 64 * i;
+            const bool valid = c < p.bn && n0 + c < p.N;
+            const long long idx = b * p.bias_bs + (valid ? n0 + c : n0);
+            float v;
+            if (p.bias_dtype == SQ_F32) v = static_cast<const float*>(p.bias)[idx];
+            else if (p.bias_dtype == SQ_F16) v = __half2float(static_cast<const __half*>(p.bias)[idx]);
+            else v = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[idx]);
+            r.bias[i] = valid ? v : 0.0f;
+        }
     }
     const long long sx_base = b * p.sx_bs + s * p.sx_ss;
     r.sx = 1.0f;
     r.sxn = 1.0f;
+    r.rx[0] = r.rx[1] = 1.0f;
+    r.rxn[0] = r.rxn[1] = 1.0f;
     if (!per_token) {
-        r.sx = __ldg(p.sx + sx_base);
-        if (DUAL) r.sxn = __ldg(p.sx_neg + sx_base);
-    }
+        r.sx = p.sx[sx_base];
+        if (DUAL) r.sxn = p.sx_neg[sx_base];
+    } else {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const long long m = m0 + t + 64 * j;
-        r.rx[j] = 1.0f;
-        r.rxn[j] = 1.0f;
-        if (per_token && m < p.M) {
-            r.rx[j] = __ldg(p.sx + sx_base + m * p.sx_rs);
-            if (DUAL) r.rxn[j] = __ldg(p.sx_neg + sx_base + m * p.sx_rs);
+        for (int j = 0; j < 2; ++j) {
+            const long long mm = m0 + t + 64 * j;
+            const bool valid = mm < p.M;
+            const long long m = valid ? mm : 0;            // row 0 always exists
+            const float a = p.sx[sx_base + m * p.sx_rs];
+            r.rx[j] = valid ? a : 1.0f;
+            if (DUAL) {
+                const float an = p.sx_neg[sx_base + m * p.sx_rs];
+                r.rxn[j] = valid ? an : 1.0f;
+            }
         }
     }
 }
@@ -101,7 +130,7 @@ __device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab,
         int b, m0, n0;
         tile_coords<PAIR>(p, tile, rank, b, m0, n0);
         int s = 0, k = 0, g = 0;   // unit cursor: segment, first K index, weight group of k (k / group_size)
-        builder_load<DUAL>(p, cur, t, b, m0, n0, s, g, per_token);
+        builder_load<DUAL>(p, cur, t, b, m0, n0, s, g, per_token, p.bias != nullptr && p.units == 1);
         for (int u = 0; u < p.units; ++u, ++au) {
             // end of this unit and cursor of the next one (segments and groups are walked, never divided)
             const int seg_end = p.seg_bounds[s + 1];
@@ -110,7 +139,7 @@ __device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab,
             const int s2 = ke == seg_end ? s + 1 : s;
             (void)k;
             const int g2 = (p.group_size > 0 && ke == grp_end) ? g + 1 : g;
-            if (u + 1 < p.units) builder_load<DUAL>(p, nxt, t, b, m0, n0, s2, g2, per_token);
+            if (u + 1 < p.units) builder_load<DUAL>(p, nxt, t, b, m0, n0, s2, g2, per_token, p.bias != nullptr && u + 2 == p.units);
 
             const uint32_t slot = au & (kTabSlots - 1);
             const uint32_t par = (au / kTabSlots) & 1u;
@@ -124,6 +153,10 @@ __device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab,
                 if (KIND == SQ_GEMM_W4A8) { r *= 0.0625f; rn *= 0.0625f; }   // int4 weights are expanded as 16*w
                 reinterpret_cast<float*>(sl)[c] = r;
                 if (DUAL) reinterpret_cast<float*>(sl + kSlotRNeg)[c] = rn;
+            }
+            if (p.bias != nullptr && u + 1 == p.units) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<float*>(sl + kSlotBias)[t + 64 * i] = cur.bias[i];
             }
             if (per_token) {
 #pragma unroll
@@ -274,14 +307,18 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtenso
         if (lane == 0) {
             if constexpr (PAIR) mbar_arrive_cluster(bar_tmem_empty + buf * 8);
             else mbar_arrive(bar_tmem_empty + buf * 8);
-            mbar_arrive(bar_tab_empty + slot * 8);
+            if (u + 1 < p.units) mbar_arrive(bar_tab_empty + slot * 8);   // the last slot also holds the bias: released below
         }
         if (threadIdx.x == 128) SQ_STAMP(2, 2 * au + 1);
         SQ_EPI(4);
         ++au;
     }
     // ---- bias, cast, store
-    store_output(p, map_y, acc, hcols >> 4, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane);
+    const uint32_t last_slot = (au - 1) & (kTabSlots - 1);
+    store_output(p, map_y, acc, hcols >> 4, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane,
+                 reinterpret_cast<const float*>(tab + last_slot * kTabSlotBytes + kSlotBias) + h * hcols);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_tab_empty + last_slot * 8);
     return true;
 }
 

@@ -283,12 +283,13 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 
 // Bias, cast and store of one thread's output row segment (up to 128 columns held in acc[]).
+// bias_s: this thread's columns of the tile's bias in shared memory, as fp32 (written by the table builder).
 // Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
 // chunk; the LSU stays free for the MMA / producer warps, every DRAM sector is written whole);
 // otherwise each thread writes its row directly.  `stage` is this warp's 2 KB staging area.
 __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensorMap* map_y, const float (&acc)[128], int nch,
                                              long long b, long long m, int m_warp, bool row_ok, long long ncol0,
-                                             uint8_t* stage, int lane) {
+                                             uint8_t* stage, int lane, const float* bias_s) {
     const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
     if (p.y_tma) {
         if (m_warp >= p.M) return;                           // nothing of this warp's 32 rows exists (warp-uniform)
@@ -303,10 +304,14 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
             if (p.bias != nullptr) {
-                const long long bo = b * p.bias_bs + nc;
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (nc + j < p.N) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
+                for (int j4 = 0; j4 < 4; ++j4) {
+                    const float4 bv = reinterpret_cast<const float4*>(bias_s + ch * 16)[j4];   // 0 beyond column N
+                    o[4 * j4 + 0] += bv.x;
+                    o[4 * j4 + 1] += bv.y;
+                    o[4 * j4 + 2] += bv.z;
+                    o[4 * j4 + 3] += bv.w;
+                }
             }
             const uint32_t off = (two_bufs && (ch & 1)) ? buf_bytes : 0u;
             // the buffer about to be overwritten must have been read by its previous TMA store
@@ -341,10 +346,8 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
             if (p.bias != nullptr) {
-                const long long bo = b * p.bias_bs + nc;
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (j < valid) o[j] += load_bias(p.bias, p.bias_dtype, bo + j);
+                for (int j = 0; j < 16; ++j) o[j] += bias_s[ch * 16 + j];
             }
             if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
             else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);

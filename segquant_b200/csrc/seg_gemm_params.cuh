@@ -21,7 +21,7 @@ constexpr uint32_t kBBytes = BN * BK;          // 32 KB
 constexpr uint32_t kBPackedBytes = BN * BK / 2;// 16 KB (int4 staging)
 constexpr uint32_t kStoreStageBytes = 8 * 2048;  // output staging for TMA stores: 2 KB per epilogue warp
 constexpr int kTabSlots = 4;                     // per-unit scale tables the builder warps may run ahead
-constexpr uint32_t kTabSlotBytes = 3072;         // r[2][BN] + rx[2][BM] floats, see seg_gemm_epilogue.cuh
+constexpr uint32_t kTabSlotBytes = 4096;         // r[2][BN] + rx[2][BM] + bias[BN] floats, see seg_gemm_epilogue.cuh
 constexpr uint32_t kTabBytesAll = kTabSlots * kTabSlotBytes;
 
 // status-word codes (low byte = which wait, rest = block index)
