@@ -91,21 +91,26 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
     const int widths[3] = {256, 192, 128};
     Schedule best{256, false};
     double best_cost = 1e300;
+    const double nst = static_cast<double>((K + BK - 1) / BK);   // 128-byte K stages per tile
     for (int mode = 0; mode < 2; ++mode) {
         if (force_cta2 >= 0 && mode != force_cta2) continue;
-        // measured on B200: the CTA pair (256-byte K stages) wins for 8-bit weights once K is long enough to
-        // amortise its longer prologue; int4 expansion and short K run faster on single CTAs
+        // measured on B200: the CTA pair wins for 8-bit weights once K is long enough to amortise its longer
+        // prologue; int4 expansion and short K run faster on single CTAs
         if (force_cta2 < 0 && mode == 1 && (kind == SQ_GEMM_W4A8 || K < 2048)) continue;
         const long long rows = mode ? BM2 : BM;
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;
-        const double eff = mode ? 0.76 : 0.67;
         for (int w : widths) {
             if (force_bn && w != force_bn) continue;
             const long long tiles = batch * ((M + rows - 1) / rows) * ((N + w - 1) / w);
             const long long rounds = (tiles + slots - 1) / slots;
-            double per_tile = (w + 40.0) / eff;
-            if (dual && w > 128) per_tile += 0.08 * w;  // epilogue of a wide DualScale tile is not overlapped
-            const double cost = static_cast<double>(rounds) * per_tile;
+            // SM cycles, fitted to in-kernel timelines: a K stage costs the issuing thread a fixed ~500 cycles
+            // (barrier wait, commit, issue) plus ~1.2 per tile column (twice with DualScale); a pair is ~17 % cheaper
+            // per stage; every tile pays ~3400 cycles of prologue / hand-over, and a wide DualScale tile, whose two
+            // accumulators fill tensor memory, also pays its un-overlapped drain and store
+            double stage = 500.0 + 1.2 * w * (dual ? 2.0 : 1.0);
+            if (mode) stage *= 0.83;
+            const double fixed = 3400.0 + ((dual && w > 128) ? 4600.0 : 0.0);
+            const double cost = static_cast<double>(rounds) * (nst * stage + fixed);
             if (cost < best_cost * 0.97) { best_cost = cost; best = Schedule{w, mode == 1}; }
         }
     }

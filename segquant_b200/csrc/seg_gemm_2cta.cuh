@@ -261,29 +261,36 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     uint32_t accumulate = 0;
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
-#ifdef SQ_VAR_LANE0_POLL
-                        {   // experiment: only lane 0 polls, the others meet it at the warp barrier
-                            int got = 1;
-                            if (lane == 0) got = mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull) ? 1 : 0;
-                            got = __shfl_sync(0xffffffffu, got, 0);
-                            if (!got) { ok = false; break; }
-                        }
-#else
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
-#endif
                         if (kW4) {
                             if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
                         }
-#ifndef SQ_VAR_NOFENCE
                         tc_fence_after();
-#endif
                         if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
                         // sub-tile j of an operand starts (tile bytes >> 4) descriptor units after sub-tile j-1
                         const uint32_t a_lo = smem_desc_lo(stage_a(st, 0));
                         const uint32_t an_lo = smem_desc_lo(stage_an(st, 0));
                         const uint32_t b_lo = smem_desc_lo(stage_b(st, 0));
                         const int kmax = (k_end - kb) < BKS ? (k_end - kb) : BKS;
-                        if (kb != u_end && kb + kmax <= u_end) {
+                        if (kb == u_end) {
+                            // the stage opens a new unit: hand the finished TMEM buffer to both CTAs' epilogues and take the
+                            // other one, once, before any MMA of the stage
+                            if (kb != k_beg && lane == 0) {
+                                umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                                umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+                            }
+                            const uint32_t buf = one_buf ? 0u : (au & 1u);
+                            const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                            tc_fence_after();
+                            cur_buf = buf;
+                            d_pos = tmem_base + buf * BN;
+                            d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                            accumulate = 0;
+                            u_end = unit_end(p, s, kb);
+                            ++au;
+                        }
+                        if (kb + kmax <= u_end) {
                             if (lane == 0) {
 #pragma unroll
                                 for (int i = 0; i < BKS / UMMA_K; ++i) {
@@ -292,16 +299,19 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                         const uint32_t ao = (i / kPerSub) * (kABytes >> 4) + 2 * (i % kPerSub);
                                         const uint32_t bo = (i / kPerSub) * (C::kBHalfBytes >> 4) + 2 * (i % kPerSub);
                                         const uint64_t db = smem_desc(b_lo + bo);
-                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + ao), db, idesc, 1u);
-                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + ao), db, idesc, 1u);
+                                        const uint32_t accf = i == 0 ? accumulate : 1u;
+                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + ao), db, idesc, accf);
+                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + ao), db, idesc, accf);
                                     }
                                 }
                             }
+                            accumulate = 1;
                         } else {
+                            // a unit ends inside this stage
                             for (int kk = 0; kk < kmax; kk += UMMA_K) {
                                 const int k = kb + kk;
                                 if (k == u_end) {
-                                    if (k != k_beg && lane == 0) {
+                                    if (lane == 0) {
                                         umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
                                         umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
                                     }

@@ -202,14 +202,9 @@ __device__ __forceinline__ void fma16(float* acc, const uint32_t (&v)[16], const
             } else {
                 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])), static_cast<float>(static_cast<int32_t>(v[j + 1])));
             }
-#ifdef SQ_EXP_SCALAR
-            acc[j] = fmaf(f.x, r.x, acc[j]);
-            acc[j + 1] = fmaf(f.y, r.y, acc[j + 1]);
-#else
             const float2 a = __ffma2_rn(f, r, make_float2(acc[j], acc[j + 1]));
             acc[j] = a.x;
             acc[j + 1] = a.y;
-#endif
         }
     }
 }

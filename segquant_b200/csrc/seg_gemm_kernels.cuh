@@ -477,48 +477,54 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BK) {
                         SQ_FINE(0);
-#ifdef SQ_VAR_LANE0_POLL
-                        {   // experiment: only lane 0 polls, the others meet it at the warp barrier
-                            int got = 1;
-                            if (lane == 0) got = mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull) ? 1 : 0;
-                            got = __shfl_sync(0xffffffffu, got, 0);
-                            if (!got) { ok = false; break; }
-                        }
-#else
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
-#endif
                         if (kW4) {
                             if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
                         }
                         SQ_FINE(1);
-#ifndef SQ_VAR_NOFENCE
                         tc_fence_after();
-#endif
                         SQ_FINE(2);
                         if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
                         const uint32_t a_lo = smem_desc_lo(stage_a(st));
                         const uint32_t an_lo = smem_desc_lo(stage_an(st));
                         const uint32_t b_lo = smem_desc_lo(stage_b(st));
                         const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
-                        if (kb != u_end && kb + kmax <= u_end) {
+                        if (kb == u_end) {
+                            // the stage opens a new unit (the common place for a boundary): hand the finished TMEM
+                            // buffer to the epilogue and take the other one, once, before any MMA of the stage
+                            if (kb != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
+                            const uint32_t buf = one_buf ? 0u : (au & 1u);
+                            const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                            if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                            tc_fence_after();
+                            cur_buf = buf;
+                            d_pos = tmem_base + buf * BN;
+                            d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                            accumulate = 0;
+                            u_end = unit_end(p, s, kb);
+                            ++au;
+                        }
+                        if (kb + kmax <= u_end) {
                             // the whole stage lies inside the current unit: no checks between the MMAs
                             if (lane == 0) {
 #pragma unroll
                                 for (int i = 0; i < BK / UMMA_K; ++i) {
                                     if (i * UMMA_K < kmax) {
                                         const uint64_t db = smem_desc(b_lo + 2 * i);
-                                        umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, 1u);
-                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, 1u);
+                                        const uint32_t accf = i == 0 ? accumulate : 1u;
+                                        umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, accf);
+                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, accf);
                                         SQ_FINE(3 + i);
                                     }
                                 }
                             }
+                            accumulate = 1;
                         } else {
+                            // a unit ends inside this stage (segment bounds or groups that are not multiples of 128)
                             for (int kk = 0; kk < kmax; kk += UMMA_K) {
                                 const int k = kb + kk;
                                 if (k == u_end) {
-                                    // unit boundary: hand the finished buffer to the epilogue, take the next one
-                                    if (k != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
+                                    if (lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
                                     const uint32_t buf = one_buf ? 0u : (au & 1u);
                                     const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
                                     if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
