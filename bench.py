@@ -425,7 +425,12 @@ def run_sweep(args):
     points = []
     modes = [("int8", "Wint8Aint8", L.SQ_Q_INT8, 0), ("fp8", "Wfpe4m3Afpe4m3", L.SQ_Q_E4M3, 0), ("w4a8", "Wint4Aint8", L.SQ_Q_INT4, 128)]
     Ms = [int(m) for m in args.sweep_m.split(",")]
-    for (N, K) in SWEEP_NK:
+    nks = SWEEP_NK if not args.sweep_nk else [tuple(int(v) for v in nk.split("x")) for nk in args.sweep_nk.split(",")]
+    modes = [m for m in modes if m[0] in args.sweep_modes.split(",")]
+    seg_counts = [int(v) for v in args.sweep_segs.split(",")]
+    w4_group = args.sweep_w4_group
+    modes = [(n_, k_, w_, (w4_group if n_ == "w4a8" else g_)) for (n_, k_, w_, g_) in modes]
+    for (N, K) in nks:
         if N % world:
             continue
         lo, hi = shard_range(N, world, rank)
@@ -440,11 +445,12 @@ def run_sweep(args):
                 wq3, strides = wq.view(1, n_loc, K // 2), (0, 0, 1, K // group)
             else:
                 sw = (qmax / w.float().abs().amax(-1)).contiguous()
-                wq = torch.empty((n_loc, K), dtype=torch.uint8, device=dev)
-                ops.quantize_weight(w, wq, sw, wkind)
-                wq3, strides = wq.view(1, n_loc, K), (0, 0, 0, 1)
+                kb = K // 2 if wkind == L.SQ_Q_INT4 else K          # bytes per weight row
+                wq = torch.empty(n_loc * kb, dtype=torch.uint8, device=dev)
+                ops.quantize_weight(w, wq if wkind == L.SQ_Q_INT4 else wq.view(n_loc, K), sw, wkind)
+                wq3, strides = wq.view(1, n_loc, kb), (0, 0, 0, 1)
             for M in Ms:
-                for S in (1, 2, 4, 8):
+                for S in seg_counts:
                     if K % (S * 32):
                         continue
                     bounds = ops.uniform_bounds(K, S)
@@ -462,18 +468,29 @@ def run_sweep(args):
                     for _ in range(3):
                         y = fwd()
                     torch.cuda.synchronize()
-                    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                     it = args.sweep_iters
+                    # `it` forwards recorded once into a CUDA graph: small layers are otherwise bound by the Python / ctypes
+                    # launch path (~30 us per call), not by the GPU
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(graph, stream=side):
+                            for _ in range(it):
+                                y = fwd()
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                     e[0].record()
-                    for _ in range(it):
-                        y = fwd()
+                    graph.replay()
                     e[1].record()
-                    for _ in range(it):
+                    for _ in range(it if world > 1 else 0):
                         y = fwd()
-                        if world > 1:
-                            all_gather_slices(y)
+                        all_gather_slices(y)
                     e[2].record()
                     torch.cuda.synchronize()
+                    del graph
                     t = torch.tensor([e[0].elapsed_time(e[1]) / it, e[1].elapsed_time(e[2]) / it], dtype=torch.float64, device=dev)
                     if world > 1:
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -492,18 +509,80 @@ def run_sweep(args):
         dist.destroy_process_group()
 
 
+def run_kernels(args):
+    """The HBM-bound kernels alone on [rows, 12288] tensors (larger than L2): activation quantise (bf16 / fp32, single,
+    DualScale, dynamic per-token), weight quantise (int8, packed int4 with group scales) and int4 unpack.
+    GB/s = algorithmic bytes / mean CUDA-event time; frac = GB/s / measured copy bandwidth."""
+    from segquant_b200 import _lib as L
+    from segquant_b200 import ops
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    R, K = args.kernel_rows, 12288
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    hbm = peaks.get("hbm_gbs") or 6650.0
+    g = torch.Generator().manual_seed(11)
+    x32 = torch.randn(R, K, generator=g).to(dev)
+    x16 = x32.to(torch.bfloat16)
+    bounds = ops.uniform_bounds(K, 4)
+    sx = torch.full((4,), 30.0, device=dev)
+    sxn = torch.full((4,), 60.0, device=dev)
+    wq8 = torch.empty((R, K), dtype=torch.uint8, device=dev)
+    wq4 = torch.empty(R * K // 2, dtype=torch.uint8, device=dev)
+    sw_row = (127.0 / x16.float().abs().amax(-1)).contiguous()
+    sw_grp = (7.0 / x16.float().view(R, K // 128, 128).abs().amax(-1)).contiguous()
+    ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128)
+    cases = [
+        ("act_quant bf16 -> int8, 4 segments", lambda: ops.quantize_act(x16, bounds, sx, None, L.SQ_Q_INT8), R * K * 3),
+        ("act_quant bf16 -> e4m3 DualScale", lambda: ops.quantize_act(x16, bounds, sx, sxn, L.SQ_Q_E4M3), R * K * 4),
+        ("act_quant fp32 -> int8, 4 segments", lambda: ops.quantize_act(x32, bounds, sx, None, L.SQ_Q_INT8), R * K * 5),
+        ("act_quant_dynamic bf16 -> int8 per token", lambda: ops.quantize_act_dynamic(x16, [0, K], L.SQ_Q_INT8), R * K * 3 + R * 4),
+        ("weight_quant bf16 -> int8 per row", lambda: ops.quantize_weight(x16, wq8, sw_row, L.SQ_Q_INT8), R * K * 3),
+        ("weight_quant bf16 -> packed int4, groups of 128", lambda: ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128),
+         R * K * 2.5 + R * K // 128 * 4),
+        ("unpack_int4", lambda: ops.unpack_int4(wq4), R * K * 1.5),
+    ]
+    rows = []
+    for name, fn, nbytes in cases:
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        rows.append({"kernel": name, "ms": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / hbm, "bytes": nbytes})
+    print(json.dumps({"metric": "hbm_kernel_gbs", "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
+                      "value": max(r["gbs"] for r in rows), "peak": hbm, "peak_source": "measured" if peaks.get("hbm_gbs") else "fallback",
+                      "config": {"workload": f"HBM-bound kernels on [{R}, {K}] tensors ({R * K * 2 / 1e6:.0f} MB bf16 > 126 MB L2)",
+                                 "steps": args.steps}, "kernels": rows, "device_status": ops.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep"],
-                    help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep)")
+    ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep", "kernels"],
+                    help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep), "
+                         "kernels (the HBM-bound quantise / unpack kernels against the measured copy bandwidth)")
     ap.add_argument("--out-proj-segments", type=int, default=1, help="mmdit: K-segments of the attention output projections (1 or 24)")
     ap.add_argument("--no-graph", action="store_true", help="mmdit: launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384")
     ap.add_argument("--sweep-iters", type=int, default=10)
+    ap.add_argument("--sweep-nk", default="", help="sweep: comma list of NxK pairs (default: the seven shapes of config[4])")
+    ap.add_argument("--sweep-modes", default="int8,fp8,w4a8")
+    ap.add_argument("--sweep-segs", default="1,2,4,8")
+    ap.add_argument("--sweep-w4-group", type=int, default=128, help="sweep: weight-scale group size of the W4A8 points (0 = per channel)")
+    ap.add_argument("--kernel-rows", type=int, default=16384, help="kernels: rows of the [rows, 12288] tensors the HBM-bound kernels run on")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -511,6 +590,8 @@ def main():
         run_mmdit(args)
     elif args.workload == "sweep":
         run_sweep(args)
+    elif args.workload == "kernels":
+        run_kernels(args)
     else:
         run_ours(args)
 

@@ -91,26 +91,36 @@ __global__ void __launch_bounds__(256) weight_quant_scalar_kernel(const __grid_c
     }
 }
 
-// int4 -> int8: 16 packed bytes in, 32 int8 out per thread step.
-__global__ void __launch_bounds__(256) unpack_int4_kernel(const uint4* __restrict__ packed, uint4* __restrict__ out,
-                                                          long long nvec) {
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const uint4 pk = __ldg(packed + i);
-        const uint32_t src[4] = {pk.x, pk.y, pk.z, pk.w};
-        uint32_t dst[8];
+// int4 -> int8: every lane takes 8 packed bytes and writes 16 int8, so a warp reads 256 and writes 512
+// contiguous bytes per instruction; four independent loads are in flight per lane.
+__device__ __forceinline__ uint4 unpack8(uint2 pk) {
+    const uint32_t src[2] = {pk.x, pk.y};
+    uint32_t dst[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // low nibbles -> even elements, high nibbles -> odd elements; sign-extend 4 -> 8 bits
-            const uint32_t lo = src[j] & 0x0F0F0F0Fu;
-            const uint32_t hi = (src[j] >> 4) & 0x0F0F0F0Fu;
-            const uint32_t lo_s = lo | ((lo & 0x08080808u) * 0x1Eu);
-            const uint32_t hi_s = hi | ((hi & 0x08080808u) * 0x1Eu);
-            dst[2 * j] = __byte_perm(lo_s, hi_s, 0x5140);
-            dst[2 * j + 1] = __byte_perm(lo_s, hi_s, 0x7362);
-        }
-        out[2 * i] = make_uint4(dst[0], dst[1], dst[2], dst[3]);
-        out[2 * i + 1] = make_uint4(dst[4], dst[5], dst[6], dst[7]);
+    for (int j = 0; j < 2; ++j) {
+        // low nibbles -> even elements, high nibbles -> odd elements; sign-extend 4 -> 8 bits
+        const uint32_t lo = src[j] & 0x0F0F0F0Fu;
+        const uint32_t hi = (src[j] >> 4) & 0x0F0F0F0Fu;
+        const uint32_t lo_s = lo | ((lo & 0x08080808u) * 0x1Eu);
+        const uint32_t hi_s = hi | ((hi & 0x08080808u) * 0x1Eu);
+        dst[2 * j] = __byte_perm(lo_s, hi_s, 0x5140);
+        dst[2 * j + 1] = __byte_perm(lo_s, hi_s, 0x7362);
+    }
+    return make_uint4(dst[0], dst[1], dst[2], dst[3]);
+}
+
+__global__ void __launch_bounds__(256) unpack_int4_kernel(const uint2* __restrict__ packed, uint4* __restrict__ out,
+                                                          long long nvec) {
+    constexpr int U = 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride * U) {
+        uint2 pk[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (i + u * stride < nvec) pk[u] = __ldg(packed + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (i + u * stride < nvec) out[i + u * stride] = unpack8(pk[u]);
     }
 }
 
@@ -175,18 +185,18 @@ int unpack_int4(const void* packed, void* out, long long numel, cudaStream_t st)
     SQ_REQUIRE(numel >= 0 && numel % 2 == 0, SQ_ERR_ALIGNMENT, "sq_unpack_int4: numel must be even and >= 0");
     if (numel == 0) return SQ_OK;
     const long long nbytes = numel / 2;
-    long long nvec = 0;
-    if (reinterpret_cast<uintptr_t>(packed) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) nvec = nbytes / 16;
+    long long nvec = 0;   // 8-byte input vectors (16 output bytes each)
+    if (reinterpret_cast<uintptr_t>(packed) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) nvec = nbytes / 8;
     if (nvec > 0) {
-        long long ctas = (nvec + 255) / 256;
+        long long ctas = (nvec + 4 * 256 - 1) / (4 * 256);
         if (ctas > kNumSMs * 8) ctas = kNumSMs * 8;
-        unpack_int4_kernel<<<static_cast<int>(ctas), 256, 0, st>>>(static_cast<const uint4*>(packed),
+        unpack_int4_kernel<<<static_cast<int>(ctas), 256, 0, st>>>(static_cast<const uint2*>(packed),
                                                                   static_cast<uint4*>(out), nvec);
     }
-    const long long tail = nbytes - nvec * 16;
+    const long long tail = nbytes - nvec * 8;
     if (tail > 0)
         unpack_int4_tail_kernel<<<static_cast<int>((tail + 255) / 256), 256, 0, st>>>(
-            static_cast<const uint8_t*>(packed), static_cast<int8_t*>(out), nvec * 16, nbytes);
+            static_cast<const uint8_t*>(packed), static_cast<int8_t*>(out), nvec * 8, nbytes);
     SQ_CUDA_OK(cudaGetLastError());
     return SQ_OK;
 }
