@@ -1,8 +1,9 @@
 // Segmented quantised GEMM with fused de-quantise epilogue for sm_100a.
 //
 //   TMA (cp.async.bulk.tensor, no multicast) -> 128B-swizzled shared memory -> tcgen05.mma
-//   (kind::i8 / kind::f8f6f4, cta_group::1, 128x256x32) -> int32 / fp32 accumulators in tensor
-//   memory -> tcgen05.ld -> per-unit scale, running fp32 sum in registers, bias, cast, store.
+//   (kind::i8 / kind::f8f6f4, 128 x bn x 32 per CTA or 256 x bn x 32 per CTA pair) -> int32 / fp32
+//   accumulators in tensor memory -> tcgen05.ld -> per-unit scale, running fp32 sum in registers, bias,
+//   cast, TMA store.
 //
 // It replaces the CUTLASS mma.sync GemmUniversal of segquant/src/real_quant/real_gemm.cu:208-305,
 // the fp32 scratch it writes, real_dequantize_{,dual_}scaled_kernel of
@@ -12,10 +13,10 @@
 // Persistent kernel, one CTA per SM, warp roles:
 //   warp 0      : TMA producer (one lane)
 //   warp 1      : allocates tensor memory, issues tcgen05.mma (one lane)
-//   warps 2-3   : idle
-//   warps 4-11  : epilogue, two warpgroups; warpgroup h owns tile columns [128h, 128h+128),
+//   warps 2-3   : build the epilogue's per-unit scale tables (and stage the bias) in shared memory
+//   warps 4-11  : epilogue, two warpgroups; warpgroup h owns half of the tile's columns,
 //                 warp w reads TMEM lanes 32*(w%4) .. +31 (one output row per thread)
-//   warps 12-15 : (W4A8 only) expand packed int4 weights to int8 in shared memory
+//   warps 12-15 : (W4A8 only) expand packed int4 weights to int8 in shared memory, in place
 //
 // K is cut into accumulation units (activation segments x weight-scale groups).  A unit's
 // products are accumulated exactly in tensor memory; at a unit boundary the MMA warp switches to
@@ -209,7 +210,8 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
 template <int KIND, bool DUAL>
 struct Cfg {
     static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
-    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes + (kW4 ? kBPackedBytes : 0);
+    // W4A8: the packed int4 tile lands in the upper half of the operand buffer and is expanded in place (no extra staging)
+    static constexpr uint32_t kStageBytes = kABytes * (DUAL ? 2 : 1) + kBBytes;
     static constexpr int kStages = (192 * 1024) / kStageBytes;
     static constexpr int kThreads = kW4 ? 512 : 384;
     static constexpr uint32_t kTxBytes = kABytes * (DUAL ? 2 : 1) + (kW4 ? kBPackedBytes : kBBytes);
@@ -371,7 +373,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr bool kW4 = C::kW4;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_ld[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
@@ -386,7 +388,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     auto stage_a = [&](int st) { return smem_base + st * C::kStageBytes; };
     auto stage_an = [&](int st) { return smem_base + st * C::kStageBytes + kABytes; };
     auto stage_b = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1); };
-    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + kBBytes; };
+    auto stage_bp = [&](int st) { return smem_base + st * C::kStageBytes + kABytes * (DUAL ? 2 : 1) + kBBytes / 2; };   // upper half of B
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
@@ -394,6 +396,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_u32(&bar_full[i]), 1);
             mbar_init(smem_u32(&bar_empty[i]), 1);
             mbar_init(smem_u32(&bar_cvt[i]), 4);
+            mbar_init(smem_u32(&bar_ld[i]), 4);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_tmem_full[i]), 1);
@@ -585,14 +588,24 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
                         const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
                         uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
-                        // staging tile: bn rows x 64 packed bytes; 16-byte chunk c = (row, quarter)
+                        // The packed tile (bn rows x 64 bytes, 16-byte chunk c = (row, quarter)) sits in the upper half
+                        // of the buffer it expands into: every thread first pulls its chunks into registers, the four
+                        // expansion warps meet on a (bounded) barrier, and only then is anything written.
+                        uint4 pk[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int c = ct + i * 128;
+                            if (c < p.bn * 4) pk[i] = *reinterpret_cast<const uint4*>(src + (c >> 2) * 64 + (c & 3) * 16);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
+                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int c = ct + i * 128;
                             if (c >= p.bn * 4) break;
                             const int row = c >> 2, qd = c & 3;
-                            const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
-                            const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
+                            const uint32_t in[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
                             uint32_t out[8];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {

@@ -230,3 +230,165 @@ class DefaultOptimizer(BaseOptimizer):
                     zip(self.input_calibrators, input_manager.iter_list(), self.weight_manager.iter_list())]
             return torch.stack(outs)
         return self.call_func(input_manager.iter_view(), self.weight_manager.iter_view())
+
+
+@OptimizerRegistry.register("smooth")
+class SmoothOptimizer(BaseOptimizer):
+    """SmoothQuant-style migration of activation outliers into the weights, per segment
+    (segquant/optimum/optimizer.py:295-521): for chunk i, `s_i = max|x_i|^a / max|w_i|^(1-a)` per input
+    channel, the weight chunk is multiplied by s_i once and every input chunk is divided by s_i before it
+    is quantised.  Life cycle: trace(x)... -> smooth() -> calibrate(x)... -> finish_calibrate() -> forward.
+
+    On the real-quant path the division is fused into the activation-quantise kernel (`smooth_dev`), so
+    the forward makes no smoothed copy of x (the reference clones and divides, :514-517):
+    * K-segments: ONE quantise + ONE GEMM; the concatenated s vector spans K, the per-segment weight
+      scales `(S, N)` are applied by the GEMM epilogue unit by unit;
+    * N-segments: every chunk smooths x with its own s_i, so x is quantised once per chunk and each
+      chunk's GEMM writes its column range of the output in place.
+    The alpha search of the reference (`search_alpha_config`) is not provided."""
+
+    def __init__(self, seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                 real_quant=False, dual_scale=False, kernel_type=None, alpha=0.5, search_alpha_config=None,
+                 verbose=False, **kwargs):
+        assert len(input_calibrators) == chunks and len(weight_calibrators) == chunks, \
+            "SmoothOptimizer needs one input and one weight calibrator per chunk"
+        if search_alpha_config is not None and search_alpha_config.get("enable"):
+            raise NotImplementedError("SmoothOptimizer: alpha search is not provided; pass a fixed alpha")
+        super().__init__(seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                         real_quant, dual_scale, kernel_type)
+        self.alpha = [float(alpha)] * chunks
+        self.max_x, self.max_w = [], []
+        self.s = [None] * chunks
+        self.has_smoothed = False
+        self.verbose = verbose
+
+    def __repr__(self):
+        head = f"SmoothOptimizer(alpha={self.alpha},kernel={self.kernel_type}\n" if self.real_quant else f"SmoothOptimizer(alpha={self.alpha}\n"
+        iq = ",\n      ".join(repr(c) for c in self.input_calibrators)
+        wq = ",\n      ".join(repr(c) for c in self.weight_calibrators)
+        return f"{head}    input_quantizers=[\n      {iq}\n  ],\n    weight_quantizers=[\n      {wq}\n  ]\n)"
+
+    # ---- calibration ---------------------------------------------------------------------------
+    @staticmethod
+    def _channel_max(t):
+        return t.abs().amax(dim=tuple(range(t.ndim - 1))).float()
+
+    def trace(self, input_manager):
+        for i, chunk in enumerate(input_manager.iter_list()):
+            m = self._channel_max(chunk)
+            if len(self.max_x) < self.chunks:
+                self.max_x.append(m)
+            else:
+                self.max_x[i] = torch.maximum(self.max_x[i], m)
+        if not self.max_w:
+            self.max_w = [self._channel_max(w) for w in self.weight_manager.iter_list()]
+
+    def smooth(self):
+        assert len(self.max_x) == self.chunks and len(self.max_w) == self.chunks, "trace() must run before smooth()"
+        eps = 1.0 / (1 << 31)
+        for i in range(self.chunks):
+            s = (self.max_x[i] ** self.alpha[i]) / (self.max_w[i] ** (1 - self.alpha[i]))
+            s = torch.where(s <= eps, torch.ones_like(s), s)
+            self.s[i] = torch.clamp(s.to(torch.float32), min=1e-4, max=1e4)
+        for w, s in zip(self.weight_manager.iter_list(), self.s):
+            w.mul_(s.to(device=w.device, dtype=w.dtype))
+        self.has_smoothed = True
+
+    def _smoothed(self, input_manager):
+        return [x / s.to(device=x.device, dtype=x.dtype) for x, s in zip(input_manager.iter_list(), self.s)]
+
+    def calibrate(self, input_manager):
+        assert self.has_smoothed, "SmoothOptimizer: linear is not smoothed"
+        chunks = self._smoothed(input_manager)
+        for cal, x in zip(self.input_calibrators, chunks):
+            cal.calibrate(x)
+        self._calibrate_weights(chunks, self.weight_manager.iter_list())
+
+    def finish_calibrate(self):
+        for i, cal in enumerate(self.input_calibrators):
+            cal.finish_calibrate()
+            self.input_calibrators[i] = cal.quantizer
+        wm = self.weight_manager
+        parts = []
+        for i, (cal, chunk) in enumerate(zip(self.weight_calibrators, wm.iter_list())):
+            parts.append(cal.finish_calibrate(chunk.contiguous()))
+            self.weight_calibrators[i] = cal.quantizer
+        if self.seg_mode == "input":
+            if self.packed:
+                wm.weight_tensor = torch.cat([p.reshape(wm.out_features, -1) for p in parts], dim=1).contiguous()
+                wm.packed = True
+            else:
+                wm.weight_tensor = torch.cat(parts, dim=1).contiguous()
+        else:
+            wm.replace_with_segments_layout(torch.stack(parts, dim=0), packed=self.packed)
+        self.max_x, self.max_w = None, None
+        self.has_calibrated = True
+        self.make_scale_tensor()
+
+    # ---- forward -------------------------------------------------------------------------------
+    def forward(self, input_manager):
+        """Un-summed per-segment outputs (the reference's contract): smoothed input copies, then call_func."""
+        if not input_manager.uniform and self.seg_mode == "input":
+            raise NotImplementedError("chunked outputs need equal segments; use forward(x) (fused)")
+        chunks = torch.stack(self._smoothed(input_manager))
+        return self.call_func(chunks, self.weight_manager.iter_view())
+
+    def _build_fused(self):
+        wm = self.weight_manager
+        N, K = wm.out_features, wm.in_features
+        S = self.chunks
+        dev = wm.device()
+        if self._input_quantizer().dynamic:
+            raise RuntimeError("SmoothOptimizer: dynamic activation scales are not supported")
+        if getattr(self._weight_quantizer(), "group_size", None):
+            raise RuntimeError("SmoothOptimizer: group-wise weight scales are not supported")
+        sw = self.scale_tensor[-1]
+        sx = self.scale_tensor[0].reshape(-1).contiguous()
+        sxn = self.scale_tensor[1].reshape(-1).contiguous() if self.dual_scale else None
+        if sx.numel() != S:
+            raise RuntimeError("static per-token activation scales are only served by forward(x, chunked=True)")
+        s_all = [s.to(device=dev, dtype=torch.float32).contiguous() for s in self.s]
+        if self.seg_mode == "input":
+            # one launch pair: s spans K, weight scales are per (segment, column) or per segment
+            if sw.numel() == S:
+                sw_t, strides = sw.reshape(S).contiguous(), (0, 1, 0, 0)
+            else:
+                sw_t, strides = sw.reshape(S, N).contiguous(), (0, N, 0, 1)
+            self._fused = dict(mode="input", bounds=wm.bounds, sx=sx, sx_neg=sxn, sw=sw_t, sw_strides=strides,
+                               wq=wm.weight_tensor.reshape(1, N, -1), N=N, smooth=torch.cat(s_all).contiguous())
+        else:
+            n = N // S
+            wq = wm.weight_tensor.reshape(S, n, -1)
+            per = []
+            for i in range(S):
+                if sw.numel() == S:
+                    sw_i, strides = sw.reshape(S)[i:i + 1].contiguous(), (0, 0, 0, 0)
+                else:
+                    sw_i, strides = sw.reshape(S, n)[i].contiguous(), (0, 0, 0, 1)
+                per.append(dict(sx=sx[i:i + 1].contiguous(), sx_neg=None if sxn is None else sxn[i:i + 1].contiguous(),
+                                sw=sw_i, sw_strides=strides, wq=wq[i:i + 1], smooth=s_all[i]))
+            self._fused = dict(mode="weight", per=per, N=N, n=n, K=K)
+
+    def fused_forward(self, x, bias=None, out=None):
+        if not self.real_quant:
+            raise RuntimeError("fused_forward is the real-quant path")
+        if self._fused is None:
+            self._build_fused()
+        f = self._fused
+        if f["mode"] == "input":
+            return ops.seg_linear(self.kernel_type, x, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"], sx_neg=f["sx_neg"],
+                                  sw_strides=f["sw_strides"], bias=bias, smooth=f["smooth"], out=out)
+        # N-segments: chunk i writes columns [i n, (i+1) n) of the output in place
+        lead = x.shape[:-1]
+        x3 = x.reshape(1, -1, f["K"]) if x.dim() != 3 else x
+        y = out if out is not None else torch.empty((*x3.shape[:2], f["N"]), dtype=x.dtype, device=x.device)
+        n = f["n"]
+        for i, c in enumerate(f["per"]):
+            ops.seg_linear(self.kernel_type, x3, c["wq"], n, [0, f["K"]], c["sx"], c["sw"], sx_neg=c["sx_neg"],
+                           sw_strides=c["sw_strides"], bias=None if bias is None else bias[i * n:(i + 1) * n],
+                           smooth=c["smooth"], out=y[..., i * n:(i + 1) * n])
+        return y if out is not None else y.reshape(*lead, f["N"])
+
+    def _move(self, device):
+        super()._move(device)
+        self.s = [None if s is None else s.to(device) for s in self.s]

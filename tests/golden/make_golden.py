@@ -121,6 +121,31 @@ def gen_weight_seg_dual_int8(SegmentLinear, seed=3, M=4, K=128, N=192, S=6):
                 w_fake=t2n(lin.optimizer.weight_manager.weight_tensor), chunks=np.int32(S))
 
 
+def gen_smooth_int8(SegmentLinear, seed=6, M=80, K=256, N=64, S=4, mode="input"):
+    """SmoothOptimizer recipe (config/sd3/dit/intw8a8.yaml: opt smooth, alpha 0.5) at toy size: outlier
+    channels migrate into the weights; one input and one weight quantiser per chunk."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    perm = torch.randperm(K, generator=g)[:6]
+    x[:, perm] *= 25.0
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    lin = SegmentLinear(K, N, bias=True, seg_mode=mode, chunks=S, custom_weight_tensor=w.clone(),
+                        custom_bias_tensor=b.clone(), input_quant_type="int8", weight_quant_type="int8",
+                        input_quant_args={"real_quant": False, "axis": None},
+                        weight_quant_args={"real_quant": False, "axis": 1},
+                        opt_type="smooth", opt_kwargs={"alpha": 0.5}, calib_type="amax", calib_kwargs={}, device="cpu")
+    lin.trace(x.clone())
+    lin.smooth()
+    lin.calibrate(x.clone())
+    lin.finish_calibrate()
+    y = lin(x.clone())
+    sx, sw = lin.optimizer.scale_tensor
+    s = torch.stack([v.float() for v in lin.optimizer.s])
+    return dict(x=t2n(x), w=t2n(w), b=t2n(b), y=t2n(y), sx=t2n(sx), sw=t2n(sw), s=t2n(s), chunks=np.int32(S),
+                w_fake=t2n(lin.optimizer.weight_manager.weight_tensor))
+
+
 def gen_quantizer_vectors(q, seed=4):
     """Scale definitions and fake-quant outputs straight from the reference's quantizer classes."""
     g = torch.Generator().manual_seed(seed)
@@ -174,6 +199,8 @@ def main():
         "dual_fp8": gen_dual_fp8(SegmentLinear),
         "weight_seg_dual_int8": gen_weight_seg_dual_int8(SegmentLinear),
         "quantizers": gen_quantizer_vectors(q),
+        "smooth_input_seg_int8": gen_smooth_int8(SegmentLinear, mode="input"),
+        "smooth_weight_seg_int8": gen_smooth_int8(SegmentLinear, seed=7, S=2, mode="weight"),
     }
     for name, d in fixtures.items():
         path = os.path.join(HERE, name + ".npz")

@@ -451,3 +451,35 @@ def test_full_size_config2_dual_fp8_properties():
     want = F.seg_linear_fake(x.float(), wf, b.float(), [0, K], act="fp8", sx_pos=[sp], sx_neg=[sn]).numpy()
     got = y.float().cpu().numpy()
     assert max_rel(got, want) <= 1e-2 and cosine(got, want) >= 0.9999
+
+
+@pytest.mark.parametrize("name,mode,chunks", [("smooth_input_seg_int8", "input", 4), ("smooth_weight_seg_int8", "weight", 2)])
+def test_smooth_optimizer_real_path_vs_reference_golden(golden, name, mode, chunks):
+    """SmoothOptimizer on the real-quant path: the division by s runs inside the activation-quantise kernel, K-segments
+    take one GEMM with per-(segment, column) weight scales, N-segments one GEMM per chunk writing its columns in place."""
+    from segquant_b200.layers.SegmentLinear import SegmentLinear
+    g = golden(name)
+    x, w, b = (torch.from_numpy(g[k]).to(DEV) for k in "xwb")
+    lin = SegmentLinear(w.shape[1], w.shape[0], bias=True, seg_mode=mode, chunks=chunks, custom_weight_tensor=w,
+                        custom_bias_tensor=b, input_quant_type="int8", weight_quant_type="int8",
+                        input_quant_args={"real_quant": True, "axis": None}, weight_quant_args={"real_quant": True, "axis": 1},
+                        opt_type="smooth", opt_kwargs={"alpha": 0.5}, device=DEV)
+    lin.trace(x)
+    lin.smooth()
+    lin.calibrate(x)
+    lin.finish_calibrate()
+    assert np.allclose(torch.stack(lin.optimizer.s).cpu().numpy(), g["s"], rtol=1e-6)
+    sx, sw = lin.optimizer.scale_tensor
+    assert np.allclose(sx.cpu().numpy(), g["sx"], rtol=1e-6) and np.allclose(sw.cpu().numpy(), g["sw"], rtol=1e-6)
+    x0 = x.clone()
+    y = lin(x).cpu().numpy()
+    assert torch.equal(x, x0)
+    want = g["y"]
+    assert max_rel(y, want) <= 1e-2                     # stated tolerance against the reference's fake-quant output
+    cos = float((y * want).sum() / (np.linalg.norm(y) * np.linalg.norm(want)))
+    assert cos >= 0.9999
+    # the un-summed reference contract gives the same numbers
+    parts = lin(x, chunked=True)
+    y2 = (parts.sum(0) if mode == "input" else parts.movedim(0, -2).reshape(x.shape[0], -1)) + lin.bias_data
+    assert max_rel(y2.cpu().numpy(), y) <= 1e-5
+    assert ops.device_status() == 0

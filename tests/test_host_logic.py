@@ -188,3 +188,32 @@ def test_extension_loader_names(native_lib):
     assert f.tolist() == [448.0, 16.0, -0.3125]
     with pytest.raises(RuntimeError, match="CUDA device"):
         ext.Wint8Aint8_real_quantized_gemm_scaled(torch.zeros(1, 4, 32), torch.zeros(1, 8, 32, dtype=torch.int8), torch.ones(1), torch.ones(1))
+
+
+@pytest.mark.parametrize("name,mode,chunks", [("smooth_input_seg_int8", "input", 4), ("smooth_weight_seg_int8", "weight", 2)])
+def test_smooth_optimizer_equals_reference(golden, name, mode, chunks):
+    """trace -> smooth -> calibrate -> finish -> forward against vectors the reference's SmoothOptimizer produced
+    (segquant/optimum/optimizer.py:295-521)."""
+    g = golden(name)
+    x, w, b = (torch.from_numpy(g[k]) for k in "xwb")
+    lin = SegmentLinear(w.shape[1], w.shape[0], bias=True, seg_mode=mode, chunks=chunks, custom_weight_tensor=w,
+                        custom_bias_tensor=b, input_quant_type="int8", weight_quant_type="int8",
+                        input_quant_args={"real_quant": False, "axis": None}, weight_quant_args={"real_quant": False, "axis": 1},
+                        opt_type="smooth", opt_kwargs={"alpha": 0.5}, device="cpu")
+    with pytest.raises(AssertionError):
+        lin.calibrate(x)                      # not smoothed yet
+    lin.trace(x)
+    lin.smooth()
+    lin.calibrate(x)
+    lin.finish_calibrate()
+    s = torch.stack(lin.optimizer.s)
+    assert np.allclose(s.numpy(), g["s"], rtol=1e-6)
+    sx, sw = lin.optimizer.scale_tensor
+    assert np.allclose(sx.numpy(), g["sx"], rtol=1e-6) and np.allclose(sw.numpy(), g["sw"], rtol=1e-6)
+    x0 = x.clone()
+    y = lin(x)
+    assert torch.equal(x, x0)
+    assert torch.allclose(y, torch.from_numpy(g["y"]), rtol=1e-5, atol=1e-5)
+    with pytest.raises(NotImplementedError):
+        SegmentLinear(8, 8, input_quant_type="int8", weight_quant_type="int8", opt_type="smooth",
+                      opt_kwargs={"search_alpha_config": {"enable": True, "min": 0.1, "max": 0.9, "step": 0.1}}, device="cpu")
