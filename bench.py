@@ -435,6 +435,14 @@ def run_sweep(args):
             continue
         lo, hi = shard_range(N, world, rank)
         n_loc = hi - lo
+        full = peers = flag = None
+        if world > 1 and args.fused_gather:
+            # every rank's [M, N] result buffer, mapped into all processes: the GEMM epilogue stores tiles to all of them
+            import torch.distributed._symmetric_memory as symm
+            full = symm.empty((max(Ms), N), dtype=torch.bfloat16, device=dev)
+            handle = symm.rendezvous(full, dist.group.WORLD)
+            peers = [int(p_) for r_, p_ in enumerate(handle.buffer_ptrs) if r_ != rank]
+            flag = torch.zeros(1, dtype=torch.int32, device=dev)
         w = (torch.randn(n_loc, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
         for name, ktype, wkind, group in modes:
             qmax = {L.SQ_Q_INT8: 127.0, L.SQ_Q_E4M3: 448.0, L.SQ_Q_INT4: 7.0}[wkind]
@@ -487,16 +495,38 @@ def run_sweep(args):
                     e[1].record()
                     for _ in range(it if world > 1 else 0):
                         y = fwd()
-                        all_gather_slices(y)
+                        gathered = all_gather_slices(y)
                     e[2].record()
                     torch.cuda.synchronize()
                     del graph
+                    ms_fused, fused_ok = None, None
+                    if full is not None:
+                        def fwd_fused():
+                            ops.seg_linear(ktype, x.unsqueeze(0), wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides,
+                                           out=full[:M, lo:hi].unsqueeze(0), peer_outputs=(peers, N, lo))
+                            dist.all_reduce(flag)      # stream-ordered: every rank's kernel is complete after it
+                        for _ in range(2):
+                            fwd_fused()
+                        torch.cuda.synchronize()
+                        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        f0.record()
+                        for _ in range(it):
+                            fwd_fused()
+                        f1.record()
+                        torch.cuda.synchronize()
+                        tf = torch.tensor([f0.elapsed_time(f1) / it], dtype=torch.float64, device=dev)
+                        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+                        ms_fused = tf.item()
+                        same = torch.tensor([int(torch.equal(full[:M], gathered.permute(1, 0, 2).reshape(M, N)))], device=dev)
+                        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                        fused_ok = bool(same.item())
                     t = torch.tensor([e[0].elapsed_time(e[1]) / it, e[1].elapsed_time(e[2]) / it], dtype=torch.float64, device=dev)
                     if world > 1:
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
                     ms_c, ms_t = t.tolist()
                     points.append({"mode": name, "M": M, "N": N, "K": K, "S": S, "layer_ms": ms_c, "layer_tops": 2.0 * M * N * K / ms_c / 1e9,
-                                   "with_allgather_ms": ms_t if world > 1 else None})
+                                   "with_allgather_ms": ms_t if world > 1 else None, "with_fused_gather_ms": ms_fused,
+                                   "fused_equals_allgather": fused_ok})
     status = ops.device_status()
     if rank == 0:
         best = {m: max((p["layer_tops"] for p in points if p["mode"] == m), default=0.0) for m in ("int8", "fp8", "w4a8")}
@@ -578,6 +608,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="mmdit: launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384")
     ap.add_argument("--sweep-iters", type=int, default=10)
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="sweep at N > 1: also time the fused form (epilogue stores every tile into all ranks' buffers over NVLink)")
     ap.add_argument("--sweep-nk", default="", help="sweep: comma list of NxK pairs (default: the seven shapes of config[4])")
     ap.add_argument("--sweep-modes", default="int8,fp8,w4a8")
     ap.add_argument("--sweep-segs", default="1,2,4,8")

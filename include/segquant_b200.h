@@ -57,7 +57,8 @@ extern "C" {
 #define SQ_GEMM_W8A8_F8 1   /* Wfpe4m3Afpe4m3  : e4m3 x e4m3  -> fp32                             */
 #define SQ_GEMM_W4A8 2      /* Wint4Aint8      : int8 x int4  -> int32                            */
 
-#define SQ_MAX_SEGS 64      /* most activation-scale segments along K in one call                 */
+#define SQ_MAX_SEGS 64
+#define SQ_MAX_PEERS 8      /* most activation-scale segments along K in one call                 */
 
 typedef void* sq_stream_t;  /* a cudaStream_t */
 
@@ -192,6 +193,16 @@ typedef struct sq_gemm_args {
     void* y_dev;
     int64_t y_batch_stride, y_row_stride;        /* elements */
     void* acc_dump_dev;
+    /* Optional fused all-gather (column-sharded layers, one process per GPU): besides y_dev, every finished
+     * tile is also written into num_peer_outputs further [M, *] matrices -- peer GPUs' output buffers mapped
+     * into this process (CUDA IPC / symmetric memory) -- at columns [peer_col_offset, peer_col_offset + N)
+     * with row stride peer_row_stride (elements of out_dtype; both must keep rows 16-byte aligned).
+     * Plain peer stores from the epilogue; no multicast.  batch must be 1.  The caller synchronises the
+     * ranks (e.g. an NCCL barrier) before anyone reads its buffer.  No counterpart in the reference. */
+    int32_t num_peer_outputs;  /* 0 .. SQ_MAX_PEERS */
+    int32_t reserved1;
+    void* peer_y_dev[SQ_MAX_PEERS];
+    int64_t peer_row_stride, peer_col_offset;
 } sq_gemm_args;
 
 int sq_gemm(const sq_gemm_args* args, sq_stream_t stream);

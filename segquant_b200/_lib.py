@@ -7,6 +7,7 @@ import ctypes
 import os
 
 SQ_MAX_SEGS = 64
+SQ_MAX_PEERS = 8
 SQ_STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
 SQ_OK = 0
@@ -77,6 +78,11 @@ class GemmArgs(ctypes.Structure):
         ("y_dev", ctypes.c_void_p),
         ("y_batch_stride", ctypes.c_int64), ("y_row_stride", ctypes.c_int64),
         ("acc_dump_dev", ctypes.c_void_p),
+        ("num_peer_outputs", ctypes.c_int32),
+        ("reserved1", ctypes.c_int32),
+        ("peer_y_dev", ctypes.c_void_p * SQ_MAX_PEERS),
+        ("peer_row_stride", ctypes.c_int64),
+        ("peer_col_offset", ctypes.c_int64),
     ]
 
 

@@ -222,6 +222,23 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.bias = a->bias_dev; p.bias_dtype = a->bias_dtype; p.bias_bs = a->bias_batch_stride;
     p.y = a->y_dev; p.out_dtype = a->out_dtype; p.y_bs = a->y_batch_stride; p.y_rs = a->y_row_stride;
     p.acc_dump = a->acc_dump_dev; p.units = units;
+    p.n_peers = a->num_peer_outputs;
+    p.peer_rs = a->peer_row_stride;
+    p.peer_co = a->peer_col_offset;
+    for (int j = 0; j < SQ_MAX_PEERS; ++j) p.peer_y[j] = j < a->num_peer_outputs ? a->peer_y_dev[j] : nullptr;
+    if (a->num_peer_outputs != 0) {
+        const long long pesz = a->out_dtype == SQ_F32 ? 4 : 2;
+        SQ_REQUIRE(a->num_peer_outputs > 0 && a->num_peer_outputs <= SQ_MAX_PEERS, SQ_ERR_INVALID_ARG,
+                   "sq_gemm: num_peer_outputs %d out of range", a->num_peer_outputs);
+        SQ_REQUIRE(a->batch == 1, SQ_ERR_UNSUPPORTED, "sq_gemm: peer outputs need batch == 1");
+        SQ_REQUIRE(a->peer_row_stride >= a->peer_col_offset + a->N && a->peer_col_offset >= 0, SQ_ERR_INVALID_ARG,
+                   "sq_gemm: peer_row_stride / peer_col_offset do not hold N columns");
+        SQ_REQUIRE((a->peer_row_stride * pesz) % 16 == 0 && (a->peer_col_offset * pesz) % 16 == 0 && (a->N * pesz) % 16 == 0,
+                   SQ_ERR_ALIGNMENT, "sq_gemm: peer outputs need 16-byte aligned rows and column offset");
+        for (int j = 0; j < a->num_peer_outputs; ++j)
+            SQ_REQUIRE(a->peer_y_dev[j] != nullptr && reinterpret_cast<uintptr_t>(a->peer_y_dev[j]) % 16 == 0, SQ_ERR_INVALID_ARG,
+                       "sq_gemm: peer_y_dev[%d] is NULL or not 16-byte aligned", j);
+    }
     const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind);
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);

@@ -284,6 +284,22 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 
+// Fused all-gather: the same 16 output columns of row m go to every peer GPU's [M, *] buffer with plain
+// 128-bit stores (peer memory mapped into this process; N is a multiple of 8 / 4 elements and every row
+// offset is 16-byte aligned, checked on the host, so a 16-column chunk is either whole or absent).
+__device__ __forceinline__ void store_peers(const GemmParams& p, const float (&o)[16], long long m, long long nc) {
+    const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
+    int valid = static_cast<int>(p.N - nc);
+    valid = valid > 16 ? 16 : valid;
+    if (valid <= 0) return;
+    for (int j = 0; j < p.n_peers; ++j) {
+        uint8_t* dst = static_cast<uint8_t*>(p.peer_y[j]) + (m * p.peer_rs + p.peer_co + nc) * esz;
+        if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(dst), o, valid, true);
+        else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(dst), o, valid, true);
+        else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(dst), o, valid, true);
+    }
+}
+
 // Bias, cast and store of one thread's output row segment (up to 128 columns held in acc[]).
 // bias_s: this thread's columns of the tile's bias in shared memory, as fp32 (written by the table builder).
 // Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
@@ -332,6 +348,7 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
                 tma_store_3d(map_y, stage_u32 + off, static_cast<int>(nc) * esz, m_warp, static_cast<int>(b));   // the map is byte-typed
                 bulk_commit();
             }
+            if (p.n_peers > 0 && row_ok) store_peers(p, o, m, nc);
         }
         return;
     }
@@ -354,6 +371,7 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
             if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
             else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
             else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
+            if (p.n_peers > 0) store_peers(p, o, m, nc);
         }
     }
 }

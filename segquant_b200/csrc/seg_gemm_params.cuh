@@ -56,6 +56,9 @@ struct GemmParams {
     long long total_tiles;
     int y_tma;    // output goes through TMA stores (y base / strides are 16-byte aligned)
     int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
+    int n_peers;              // fused all-gather: further [M, *] outputs on peer GPUs
+    void* peer_y[SQ_MAX_PEERS];
+    long long peer_rs, peer_co;
     int all_magic;  // every accumulation unit has K <= 224: int32 accumulators stay inside [-2^22, 2^22)
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
 };

@@ -156,10 +156,14 @@ class SegmentLinear(nn.Module):
             self.bias_data = self.bias_data.to(device)
 
     # ---- forward ---------------------------------------------------------------------------------------
-    def forward(self, x, chunked=False, out=None):
-        """out (real-quant path only): a (B, M, N) view to write into, e.g. a slice of a larger buffer."""
+    def forward(self, x, chunked=False, out=None, peer_outputs=None):
+        """out (real-quant path only): a (B, M, N) view to write into, e.g. a slice of a larger buffer.
+        peer_outputs (with out=, B = 1): (pointers, row stride, column offset) of peer GPUs' buffers that receive the
+        same tiles straight from the GEMM epilogue (column-sharded layers, segquant_b200/sharded.py)."""
         opt = self.optimizer
         if opt.real_quant and not chunked:
+            if peer_outputs is not None:
+                return opt.fused_forward(x, self.bias_data if self.bias else None, out=out, peer_outputs=peer_outputs)
             return opt.fused_forward(x, self.bias_data if self.bias else None, out=out)
         if out is not None:
             raise ValueError("out= is served by the fused real-quant forward only")

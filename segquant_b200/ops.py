@@ -192,7 +192,7 @@ def num_units(bounds, group_size=0):
 
 def gemm(kind, xq, wq, N, bounds, sx, sw, *, xq_neg=None, sx_neg=None, per_token=False, group_size=0,
          sw_strides=(0, 0, 0, 1), bias=None, out_dtype=torch.float32, out=None, x_batched=True, w_seg_as_batch=False,
-         y_strides=None, sx_batch_stride=None, want_acc=False):
+         y_strides=None, sx_batch_stride=None, want_acc=False, peer_outputs=None):
     """xq: (B, M, K) uint8 contiguous (or B == 1 shared by `batch` problems when x_batched=False).
 
     wq: weights, (Bw, N, K) bytes or (Bw, N, K/2) packed int4, contiguous.
@@ -240,6 +240,15 @@ def gemm(kind, xq, wq, N, bounds, sx, sw, *, xq_neg=None, sx_neg=None, per_token
     y = out if out is not None else torch.empty((batch, M, N), dtype=out_dtype, device=xq.device)
     a.y_dev = y.data_ptr()
     a.y_batch_stride, a.y_row_stride = y_strides if y_strides is not None else (M * N, N)
+    if peer_outputs is not None:
+        # fused all-gather: (device pointers of the peers' [M, *] buffers, row stride, column offset) in elements
+        ptrs, prs, pco = peer_outputs
+        if len(ptrs) > L.SQ_MAX_PEERS:
+            raise ValueError(f"at most {L.SQ_MAX_PEERS} peer outputs")
+        a.num_peer_outputs = len(ptrs)
+        for j, ptr in enumerate(ptrs):
+            a.peer_y_dev[j] = int(ptr)
+        a.peer_row_stride, a.peer_col_offset = int(prs), int(pco)
     acc = None
     if want_acc:
         units = num_units(bounds, group_size)
@@ -261,7 +270,8 @@ def device_status():
 # fused layer forward
 # ---------------------------------------------------------------------------------------------
 def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=False, group_size=0,
-               sw_strides=(0, 0, 0, 1), bias=None, smooth=None, w_seg_as_batch=False, out_dtype=None, out=None):
+               sw_strides=(0, 0, 0, 1), bias=None, smooth=None, w_seg_as_batch=False, out_dtype=None, out=None,
+               peer_outputs=None):
     """SegmentLinear.forward on the real-quant path in two launches: quantise x [.., K] with the
     per-K-segment (or DualScale, or dynamic per-token) scales, then one GEMM that sums the
     segments in fp32 registers, adds the bias and casts.  Returns [.., N] in x.dtype."""
@@ -277,8 +287,11 @@ def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=Fa
             raise ValueError("out= needs a static-scale (B, M, K) input and a (B, M, N) output view with a contiguous last dim")
         xq, xqn = quantize_act(x if x.stride(-1) == 1 else x.contiguous(), bounds, sx, sx_neg, a_kind, smooth=smooth, shared_scales=True)
         gemm(kind, xq, wq, N, bounds, sx, sw, xq_neg=xqn, sx_neg=sx_neg, group_size=group_size, sw_strides=sw_strides, bias=bias,
-             out_dtype=out.dtype, out=out, y_strides=(out.stride(0), out.stride(1)), sx_batch_stride=0, w_seg_as_batch=w_seg_as_batch)
+             out_dtype=out.dtype, out=out, y_strides=(out.stride(0), out.stride(1)), sx_batch_stride=0, w_seg_as_batch=w_seg_as_batch,
+             peer_outputs=peer_outputs)
         return out
+    if peer_outputs is not None:
+        raise ValueError("peer_outputs needs out= (a (1, M, N) view of this rank's own buffer)")
     if x.dim() == 3 and x.stride(-1) == 1 and not x.is_contiguous() and not dynamic:
         # a strided (B, M, K) view (e.g. a token slice of a joint sequence): the quantise kernel reads it
         # in place and writes contiguous bytes, so no copy of x is made

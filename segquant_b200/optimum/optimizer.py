@@ -116,7 +116,7 @@ class BaseOptimizer:
         wq3 = wq.reshape(1, N, -1)
         self._fused = dict(bounds=bounds, sx=sx, sx_neg=sxn, sw=sw_t, sw_strides=strides, group=group, wq=wq3, N=N)
 
-    def fused_forward(self, x, bias=None, out=None):
+    def fused_forward(self, x, bias=None, out=None, peer_outputs=None):
         """Final (..., N) output of the real-quant layer: quantise + segmented GEMM + bias."""
         if not self.real_quant:
             raise RuntimeError("fused_forward is the real-quant path")
@@ -125,7 +125,8 @@ class BaseOptimizer:
         f = self._fused
         iq = self._input_quantizer()
         return ops.seg_linear(self.kernel_type, x, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"], sx_neg=f["sx_neg"],
-                              dynamic=bool(iq.dynamic), group_size=f["group"], sw_strides=f["sw_strides"], bias=bias, out=out)
+                              dynamic=bool(iq.dynamic), group_size=f["group"], sw_strides=f["sw_strides"], bias=bias, out=out,
+                              peer_outputs=peer_outputs)
 
     # ---- housekeeping ------------------------------------------------------------------------------
     def _calibrate_weights(self, i_view, w_view):

@@ -8,6 +8,10 @@ layer forward on its slice and the slices are exchanged with NCCL `all_gather_in
 NVLink.  The exchange moves (g-1)/g * M*N*2 bytes in and out of every GPU, which at B200 tensor
 rates costs more than the GEMM itself for every K <= 12288; `forward` therefore reports nothing
 by itself -- bench.py times the GEMM phase and the whole step separately.
+
+forward_fused() is the fused form: the peers' output buffers are mapped into every process (symmetric
+memory) and the GEMM epilogue stores each finished tile into all of them, so the exchange overlaps the
+mainloop tile by tile and no gather kernel or interleave copy runs; only a barrier follows.
 """
 import torch
 import torch.distributed as dist
@@ -77,3 +81,27 @@ class ColumnShardedSegLinear:
         return assemble(gathered).reshape(*lead, self.n_total)
 
     __call__ = forward
+
+    # ---- fused all-gather: the GEMM epilogue stores every tile into all ranks' [M, N] buffers ----------
+    def enable_fused_gather(self, max_rows, dtype=torch.bfloat16):
+        """Allocate this rank's [max_rows, N] output in symmetric memory and exchange the mappings (one
+        rendezvous; NCCL group).  After this, forward_fused() replaces local GEMM + all-gather + interleave."""
+        import torch.distributed._symmetric_memory as symm
+        dev = self.layer.bias_data.device if self.layer.bias_data is not None else self.layer.optimizer.weight_manager.device()
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._full = symm.empty((max_rows, self.n_total), dtype=dtype, device=dev)
+        self._handle = symm.rendezvous(self._full, group)
+        self._peer_ptrs = [int(p) for r, p in enumerate(self._handle.buffer_ptrs) if r != self.rank]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def forward_fused(self, x):
+        """x [M, K] (same on every rank).  Every rank's epilogue writes its column slice into its own buffer
+        (TMA stores) and into every peer's buffer (plain stores over NVLink); a one-word all-reduce then orders all
+        ranks' kernels before anyone reads.  Returns this rank's full [M, N] result (a view of the symmetric buffer:
+        it is overwritten by the next call)."""
+        m = x.shape[0]
+        lo, hi = shard_range(self.n_total, self.world, self.rank)
+        full = self._full[:m]
+        self.layer(x.unsqueeze(0), out=full[:, lo:hi].unsqueeze(0), peer_outputs=(self._peer_ptrs, self.n_total, lo))
+        dist.all_reduce(self._flag, group=self.group)   # stream-ordered barrier: completes after every rank's GEMM
+        return full

@@ -81,6 +81,19 @@ def test_argument_errors_are_status_codes(native_lib):
     with pytest.raises(L.SegQuantError) as e:
         L.check(L.SQ_ERR_ALIGNMENT, "sq_gemm")
     assert e.value.status == L.SQ_ERR_ALIGNMENT
+    # fused all-gather outputs: range, batch and alignment are checked before anything is launched
+    a.K = 64
+    L.set_bounds(a.seg_bounds, [0, 64])
+    a.xq_row_stride = a.wq_row_stride = 64
+    a.y_row_stride = 16
+    a.num_peer_outputs = L.SQ_MAX_PEERS + 1
+    assert native_lib.sq_gemm(ctypes.byref(a), None) == L.SQ_ERR_INVALID_ARG
+    a.num_peer_outputs, a.peer_row_stride, a.peer_col_offset = 1, 32, 3          # column offset not 16-byte aligned
+    a.peer_y_dev[0] = addr
+    assert native_lib.sq_gemm(ctypes.byref(a), None) == L.SQ_ERR_ALIGNMENT
+    a.peer_col_offset, a.batch = 16, 2
+    assert native_lib.sq_gemm(ctypes.byref(a), None) == L.SQ_ERR_UNSUPPORTED
+    assert b"batch" in native_lib.sq_last_error()
     q = L.ActQuantArgs()
     q.x_dev = q.xq_dev = q.sx_dev = addr
     q.x_dtype, q.out_kind, q.batch, q.M, q.K, q.num_segs = L.SQ_F32, L.SQ_Q_INT4, 1, 4, 64, 1
