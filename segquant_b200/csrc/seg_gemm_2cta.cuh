@@ -118,7 +118,8 @@ struct Cfg2 {
     static constexpr bool kW4 = KIND == SQ_GEMM_W4A8;
     static constexpr uint32_t kBHalfBytes = 128 * BK;        // up to 128 rows of B per CTA and sub-tile
     static constexpr uint32_t kBpHalfBytes = 128 * BK / 2;   // packed int4 staging per sub-tile
-    static constexpr uint32_t kStageBytes = KSUB * (kABytes * (DUAL ? 2 : 1) + kBHalfBytes + (kW4 ? kBpHalfBytes : 0));
+    // W4A8: packed int4 lands in the upper half of each B sub-tile buffer and is expanded in place
+    static constexpr uint32_t kStageBytes = KSUB * (kABytes * (DUAL ? 2 : 1) + kBHalfBytes);
     static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kThreads = kW4 ? 512 : 384;
@@ -137,7 +138,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int BKS = BK * KSUB;   // K covered by one stage
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_ld[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
@@ -152,13 +153,11 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t peer = rank ^ 1u;
     const int hb = p.bn >> 1;                     // B rows / accumulator-column share of one CTA
 
-    // stage layout: A[KSUB] | A_neg[KSUB] | B[KSUB] | B_packed[KSUB]
+    // stage layout: A[KSUB] | A_neg[KSUB] | B[KSUB] (W4A8: packed bytes arrive in the upper half of each B sub-tile)
     auto stage_a = [&](int st, int j) { return smem_base + st * C::kStageBytes + j * kABytes; };
     auto stage_an = [&](int st, int j) { return smem_base + st * C::kStageBytes + (KSUB + j) * kABytes; };
     auto stage_b = [&](int st, int j) { return smem_base + st * C::kStageBytes + KSUB * kABytes * (DUAL ? 2 : 1) + j * C::kBHalfBytes; };
-    auto stage_bp = [&](int st, int j) {
-        return smem_base + st * C::kStageBytes + KSUB * (kABytes * (DUAL ? 2 : 1) + C::kBHalfBytes) + j * C::kBpHalfBytes;
-    };
+    auto stage_bp = [&](int st, int j) { return stage_b(st, j) + C::kBHalfBytes / 2; };
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
@@ -167,6 +166,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(smem_u32(&bar_empty[i]), 1);
             mbar_init(smem_u32(&bar_cvt[i]), 8);
             mbar_init(smem_u32(&bar_bp[i]), 1);
+            mbar_init(smem_u32(&bar_ld[i]), 4);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_tmem_full[i]), 1);
@@ -381,29 +381,46 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
                         const int left = k_end - kb;
                         const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;
-                        for (int jsub = 0; jsub < nsub; ++jsub) {
-                        const uint8_t* src = smem_gen + (stage_bp(st, jsub) - smem_base);
-                        uint8_t* dst = smem_gen + (stage_b(st, jsub) - smem_base);
+                        // packed bytes sit in the upper half of the buffer they expand into: pull every chunk into
+                        // registers, meet the other expansion warps on a bounded barrier, then write
+                        uint4 pk[KSUB][4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int c = ct + i * 128;
-                            if (c >= hb * 4) break;
-                            const int row = c >> 2, qd = c & 3;
-                            const uint4 pk = *reinterpret_cast<const uint4*>(src + row * 64 + qd * 16);
-                            const uint32_t in[4] = {pk.x, pk.y, pk.z, pk.w};
-                            uint32_t out[8];
+                        for (int jsub = 0; jsub < KSUB; ++jsub) {
+                            if (jsub < nsub) {
+                                const uint8_t* src = smem_gen + (stage_bp(st, jsub) - smem_base);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t lo = (in[j] << 4) & 0xF0F0F0F0u;
-                                const uint32_t hi = in[j] & 0xF0F0F0F0u;
-                                out[2 * j] = __byte_perm(lo, hi, 0x5140);
-                                out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                                for (int i = 0; i < 4; ++i) {
+                                    const int c = ct + i * 128;
+                                    if (c < hb * 4) pk[jsub][i] = *reinterpret_cast<const uint4*>(src + (c >> 2) * 64 + (c & 3) * 16);
+                                }
                             }
-                            uint8_t* drow = dst + row * 128;
-                            const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
-                            *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-                            *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
                         }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
+                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+#pragma unroll
+                        for (int jsub = 0; jsub < KSUB; ++jsub) {
+                            if (jsub >= nsub) break;
+                            uint8_t* dst = smem_gen + (stage_b(st, jsub) - smem_base);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int c = ct + i * 128;
+                                if (c >= hb * 4) break;
+                                const int row = c >> 2, qd = c & 3;
+                                const uint32_t in[4] = {pk[jsub][i].x, pk[jsub][i].y, pk[jsub][i].z, pk[jsub][i].w};
+                                uint32_t out[8];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t lo = (in[j] << 4) & 0xF0F0F0F0u;
+                                    const uint32_t hi = in[j] & 0xF0F0F0F0u;
+                                    out[2 * j] = __byte_perm(lo, hi, 0x5140);
+                                    out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                                }
+                                uint8_t* drow = dst + row * 128;
+                                const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
+                                *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+                                *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+                            }
                         }
                         fence_proxy_async_smem();
                         __syncwarp();

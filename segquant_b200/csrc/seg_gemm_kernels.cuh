@@ -55,6 +55,13 @@ static __device__ long long g_trace[3 * 4096];
 #else
 #define SQ_EPI(slot) do { } while (0)
 #endif
+#ifdef SQ_TRACE_CVT   // eight stamps per stage of block 0's first int4-expansion thread, in role 0's slots
+#undef SQ_STAMP
+#define SQ_STAMP(role, idx) do { if ((role) != 0 && blockIdx.x == 0 && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
+#define SQ_CVT(slot) do { if (threadIdx.x == 384 && blockIdx.x == 0 && it < 500) g_trace[8 * it + (slot)] = clock64(); } while (0)
+#else
+#define SQ_CVT(slot) do { } while (0)
+#endif
 #ifdef SQ_TRACE_FINE
 #define SQ_FINE(slot) do { if (lane == 0 && blockIdx.x == 0 && trace_mma < 500) g_trace[2 * 4096 + 8 * trace_mma + (slot)] = clock64(); } while (0)
 #else
@@ -603,27 +610,24 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int kb = k_beg; kb < k_end; kb += BK, ++it) {
                         const int st = it % kStages;
                         const uint32_t ph = (it / kStages) & 1u;
+                        SQ_CVT(0);
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        SQ_CVT(1);
                         const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
                         uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
-                        // The packed tile (bn rows x 64 bytes, 16-byte chunk c = (row, quarter)) sits in the upper half
-                        // of the buffer it expands into: every thread first pulls its chunks into registers, the four
-                        // expansion warps meet on a (bounded) barrier, and only then is anything written.
-                        uint4 pk[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int c = ct + i * 128;
-                            if (c < p.bn * 4) pk[i] = *reinterpret_cast<const uint4*>(src + (c >> 2) * 64 + (c & 3) * 16);
-                        }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
-                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int c = ct + i * 128;
-                            if (c >= p.bn * 4) break;
-                            const int row = c >> 2, qd = c & 3;
-                            const uint32_t in[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
+                        // The packed tile (bn rows x 64 bytes; 16-byte chunk = (row, quarter)) sits in the upper half of
+                        // the 32 KB buffer it expands into.  Thread ct owns chunks (row0 + 32 i, qd), i = 0..7: the swizzle
+                        // term (row % 8) and qd do not depend on i, so the destination offsets inside a row are constants.
+                        // Rows < 128 expand into the lower half, which holds no packed bytes: done first, straight from
+                        // shared memory.  Rows >= 128 overwrite the packed area: their chunks are pulled into registers
+                        // up front, the four expansion warps meet on a (bounded) barrier once everybody has read, and only
+                        // then are they written.
+                        const int row0 = ct >> 2, qd = ct & 3;
+                        const int o0 = ((2 * qd) ^ (row0 & 7)) * 16, o1 = ((2 * qd + 1) ^ (row0 & 7)) * 16;
+                        const uint8_t* srow = src + row0 * 64 + qd * 16;
+                        uint8_t* drow = dst + row0 * 128;
+                        auto expand_store = [&](const uint4& v, int i) {
+                            const uint32_t in[4] = {v.x, v.y, v.z, v.w};
                             uint32_t out[8];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -634,14 +638,33 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 out[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
                             }
                             // 32 int8 = two 16-byte chunks of the 128-byte row, XOR-swizzled by (row % 8)
-                            uint8_t* drow = dst + row * 128;
-                            const int c0 = (2 * qd) ^ (row & 7), c1 = (2 * qd + 1) ^ (row & 7);
-                            *reinterpret_cast<uint4*>(drow + c0 * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-                            *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
-                        }
+                            *reinterpret_cast<uint4*>(drow + i * 4096 + o0) = make_uint4(out[0], out[1], out[2], out[3]);
+                            *reinterpret_cast<uint4*>(drow + i * 4096 + o1) = make_uint4(out[4], out[5], out[6], out[7]);
+                        };
+                        uint4 hi4[4], lo4[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (row0 + 32 * (i + 4) < p.bn) hi4[i] = *reinterpret_cast<const uint4*>(srow + (i + 4) * 2048);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (row0 + 32 * i < p.bn) lo4[i] = *reinterpret_cast<const uint4*>(srow + i * 2048);
+                        SQ_CVT(2);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (row0 + 32 * i < p.bn) expand_store(lo4[i], i);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
+                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        SQ_CVT(3);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (row0 + 32 * (i + 4) < p.bn) expand_store(hi4[i], i + 4);
+                        SQ_CVT(4);
                         fence_proxy_async_smem();  // generic-proxy writes -> visible to tcgen05.mma
+                        SQ_CVT(5);
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bar_cvt[st]));
+                        SQ_CVT(6);
                     }
                 }
             }
