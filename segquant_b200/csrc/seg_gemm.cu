@@ -6,6 +6,10 @@
 
 namespace sq {
 
+// skinny-M path (seg_gemv.cu)
+bool gemv_applies(const sq_gemm_args* a, bool dual);
+int launch_gemv(const GemmParams& p, const sq_gemm_args* a, bool dual, cudaStream_t st);
+
 static int g_last_tu = 0;   // (kind * 2 + dual) of the last launch; the trace reader of -DSQ_TRACE builds uses it
 
 #define SQ_FOR_EACH_TU(X) X(SQ_GEMM_W8A8_I8, false) X(SQ_GEMM_W8A8_I8, true) X(SQ_GEMM_W8A8_F8, false) X(SQ_GEMM_W8A8_F8, true) \
@@ -239,6 +243,8 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
             SQ_REQUIRE(a->peer_y_dev[j] != nullptr && reinterpret_cast<uintptr_t>(a->peer_y_dev[j]) % 16 == 0, SQ_ERR_INVALID_ARG,
                        "sq_gemm: peer_y_dev[%d] is NULL or not 16-byte aligned", j);
     }
+    // a handful of rows: stream the weights once on the CUDA cores instead of padding 128-row tensor-core tiles
+    if (gemv_applies(a, dual)) return launch_gemv(p, a, dual, st);
     const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind);
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);

@@ -483,3 +483,49 @@ def test_smooth_optimizer_real_path_vs_reference_golden(golden, name, mode, chun
     y2 = (parts.sum(0) if mode == "input" else parts.movedim(0, -2).reshape(x.shape[0], -1)) + lin.bias_data
     assert max_rel(y2.cpu().numpy(), y) <= 1e-5
     assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# skinny-M path (M <= 4): CUDA-core weight streaming, same arithmetic as the tensor-core kernels
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind,M,N,K,bounds,group,dual,per_token", [
+    ("i8", 2, 9216, 1536, None, 0, True, False),            # the adaLN projection of the MMDiT step
+    ("i8", 1, 50, 96, None, 0, False, False),               # N not a multiple of the 4 columns a warp owns
+    ("i8", 3, 260, 1024, [0, 256, 1024], 0, False, False),  # unequal segments
+    ("i8", 4, 128, 1024, None, 128, False, True),           # groups of 128 + per-token activation scales
+    ("i8", 4, 96, 3072, [0, 1024, 2048, 3072], 512, True, False),
+    ("f8", 2, 300, 1536, None, 0, True, False),
+    ("f8", 3, 64, 512, [0, 256, 512], 0, False, True),
+])
+def test_skinny_m_path_matches_oracle_and_tensor_core_path(monkeypatch, kind, M, N, K, bounds, group, dual, per_token):
+    gk = {"i8": L.SQ_GEMM_W8A8_I8, "f8": L.SQ_GEMM_W8A8_F8}[kind]
+    ok = {"i8": O.GEMM_I8, "f8": O.GEMM_F8}[kind]
+    xq, xn, wq, _ = random_operands(kind, M, N, K, seed=11)
+    bounds = bounds or [0, K]
+    S = len(bounds) - 1
+    rng = np.random.default_rng(5)
+    sx = rng.uniform(0.5, 4.0, (S, M) if per_token else (S,)).astype(np.float32)
+    sxn = rng.uniform(0.5, 4.0, (S, M) if per_token else (S,)).astype(np.float32)
+    if group:
+        sw = rng.uniform(50, 150, (K // group, N)).astype(np.float32)
+        strides = (0, 0, N, 1)
+    else:
+        sw = rng.uniform(50, 150, (S, N)).astype(np.float32)
+        strides = (0, N, 0, 1)
+    bias = rng.standard_normal(N).astype(np.float32)
+    y_ref = O.seg_gemm(ok, xq, wq, bounds, sx, sw, xq_neg=xn if dual else None, sx_neg=sxn if dual else None, group_size=group, bias=bias)
+
+    def run():
+        return ops.gemm(gk, t(xq.view(np.uint8)).unsqueeze(0), t(wq.view(np.uint8)).unsqueeze(0), N, bounds, t(sx), t(sw),
+                        xq_neg=t(xn.view(np.uint8)).unsqueeze(0) if dual else None, sx_neg=t(sxn) if dual else None, per_token=per_token,
+                        group_size=group, sw_strides=strides, bias=t(bias), out_dtype=torch.float32)[0].cpu().numpy()
+
+    y_skinny = run()
+    monkeypatch.setenv("SEGQUANT_B200_NO_GEMV", "1")
+    y_tc = run()
+    monkeypatch.delenv("SEGQUANT_B200_NO_GEMV")
+    assert max_rel(y_skinny, y_ref) < 1e-5
+    assert max_rel(y_tc, y_ref) < 1e-5
+    if kind == "i8":
+        assert np.array_equal(y_skinny, y_tc)     # integer sums are exact on both paths and the fp32 steps are the same
+    assert ops.device_status() == 0
