@@ -1,6 +1,6 @@
 """Compile the reference's fake-quant fp8 extension from its own sources into oracle/_ref/.
 
-    python oracle/build_ref.py /root/reference
+    python oracle/build_ref.py [<reference checkout>]
 
 The two files (segquant/src/fake_quant/quantizer_fp8.cpp and .cu) are compiled where they lie; only
 build products are written, and only under oracle/_ref/.  The result is the function

@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory by running the REFERENCE's own Python code.
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [<reference checkout>]
 
 The reference (OptiSys-ZJU/segquant) is imported from its read-only checkout; nothing of it is
 copied.  `import segquant` would JIT-build its CUDA/CUTLASS extensions, so the package module is
