@@ -522,6 +522,9 @@ def run_sweep(args):
                     torch.cuda.current_stream().wait_stream(side)
                     graph.replay()
                     torch.cuda.synchronize()
+                    if world > 1:
+                        all_gather_slices(y)          # communicator set-up and buffers happen outside the timed loop
+                        torch.cuda.synchronize()
                     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                     e[0].record()
                     graph.replay()

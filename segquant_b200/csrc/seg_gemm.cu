@@ -235,6 +235,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
         SQ_REQUIRE(a->num_peer_outputs > 0 && a->num_peer_outputs <= SQ_MAX_PEERS, SQ_ERR_INVALID_ARG,
                    "sq_gemm: num_peer_outputs %d out of range", a->num_peer_outputs);
         SQ_REQUIRE(a->batch == 1, SQ_ERR_UNSUPPORTED, "sq_gemm: peer outputs need batch == 1");
+        SQ_REQUIRE(a->acc_dump_dev == nullptr, SQ_ERR_UNSUPPORTED, "sq_gemm: peer outputs cannot be combined with acc_dump_dev");
         SQ_REQUIRE(a->peer_row_stride >= a->peer_col_offset + a->N && a->peer_col_offset >= 0, SQ_ERR_INVALID_ARG,
                    "sq_gemm: peer_row_stride / peer_col_offset do not hold N columns");
         SQ_REQUIRE((a->peer_row_stride * pesz) % 16 == 0 && (a->peer_col_offset * pesz) % 16 == 0 && (a->N * pesz) % 16 == 0,
@@ -274,7 +275,10 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
                "sq_gemm: w_seg_as_batch needs a non-zero wq_batch_stride");
     p.w_batched = (w_nb > 1 && !a->w_seg_as_batch) ? 1 : 0;   // wq_batch_stride == 0: one weight matrix for all problems
     // output: TMA stores need a 16-byte aligned base and strides; anything else is written by the threads
-    CUtensorMap my = ma;
+    OutMaps my;
+    my.y = ma;
+    for (int j = 0; j < SQ_MAX_PEERS; ++j) my.peer[j] = ma;
+    p.peer_tma = 0;
     {
         const long long esz = a->out_dtype == SQ_F32 ? 4 : 2;
         const bool aligned = (reinterpret_cast<uintptr_t>(a->y_dev) & 15u) == 0 && (a->y_row_stride * esz) % 16 == 0 &&
@@ -282,9 +286,17 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
         p.y_tma = 0;
         if (aligned) {
             const uint64_t y_bstride = a->batch > 1 ? a->y_batch_stride * esz : static_cast<uint64_t>(a->y_row_stride) * esz * a->M;
-            rc = make_map(&my, a->y_dev, a->N * esz, a->M, a->batch, a->y_row_stride * esz, y_bstride, 16 * esz, 32, false, "y");
+            rc = make_map(&my.y, a->y_dev, a->N * esz, a->M, a->batch, a->y_row_stride * esz, y_bstride, 16 * esz, 32, false, "y");
             if (rc != SQ_OK) return rc;
             p.y_tma = 1;
+            // peers: the map starts at their column offset, so the kernel uses the coordinates of y
+            for (int j = 0; j < a->num_peer_outputs; ++j) {
+                const uint8_t* base = static_cast<const uint8_t*>(a->peer_y_dev[j]) + a->peer_col_offset * esz;
+                rc = make_map(&my.peer[j], base, a->N * esz, a->M, 1, a->peer_row_stride * esz,
+                              static_cast<uint64_t>(a->peer_row_stride) * esz * a->M, 16 * esz, 32, false, "peer_y");
+                if (rc != SQ_OK) return rc;
+            }
+            p.peer_tma = a->num_peer_outputs > 0 ? 1 : 0;
         }
     }
     // B tile rows staged per CTA: the whole tile, or half of it in a CTA pair

@@ -130,7 +130,7 @@ struct Cfg2 {
 template <int KIND, bool DUAL, int KSUB>
 __global__ void __launch_bounds__(Cfg2<KIND, DUAL, KSUB>::kThreads, 1)
 seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
-                 const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+                 const __grid_constant__ CUtensorMap map_w, const __grid_constant__ OutMaps map_y,
                 const __grid_constant__ GemmParams p) {
     using C = Cfg2<KIND, DUAL, KSUB>;
     constexpr int kStages = C::kStages;
@@ -451,7 +451,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // Launch on as many CTA pairs as can be resident.  Returns SQ_ERR_UNSUPPORTED if the device cannot
 // host a pair of this kernel (the caller then uses the one-CTA kernel).
 template <int KIND, bool DUAL, int KSUB>
-static int launch_2cta_k(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+static int launch_2cta_k(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     using C = Cfg2<KIND, DUAL, KSUB>;
     static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
     static int max_clusters[64] = {};
@@ -490,7 +490,7 @@ static int launch_2cta_k(const CUtensorMap& ma, const CUtensorMap& man, const CU
 // 256-byte K stages wherever two of them fit in shared memory (all but W4A8 + DualScale).
 // SEGQUANT_B200_KSUB=1 forces 128-byte stages (tuning aid).
 template <int KIND, bool DUAL>
-static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     constexpr bool can2 = Cfg2<KIND, DUAL, 2>::kStagesRaw >= 2;
     bool want2 = can2;
     if (const char* env = getenv("SEGQUANT_B200_KSUB")) want2 = can2 && atoi(env) != 1;

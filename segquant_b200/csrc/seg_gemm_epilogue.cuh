@@ -250,8 +250,8 @@ __device__ __forceinline__ void drain_unit(const GemmParams& p, float (&acc)[128
 
 // One tile for one epilogue warp.  `bar_tmem_empty` is the address arrivals go to: the CTA's own
 // barrier array, or (PAIR) the cluster address of the leader's.  Returns false after a wait gave up.
-template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP>
-__device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP, bool PEERS>
+__device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const OutMaps* map_y, uint32_t tmem_base, const uint8_t* tab,
                                               uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
                                               uint32_t bar_tab_empty, volatile int* abort_flag, uint32_t& au, int b, int m0, int n0,
                                               int warp, int lane, uint8_t* stage) {
@@ -310,7 +310,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtenso
     }
     // ---- bias, cast, store
     const uint32_t last_slot = (au - 1) & (kTabSlots - 1);
-    store_output(p, map_y, acc, hcols >> 4, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane,
+    store_output<PEERS>(p, map_y, acc, hcols >> 4, b, m, m0 + q * 32, row_ok, n0 + h * hcols, stage, lane,
                  reinterpret_cast<const float*>(tab + last_slot * kTabSlotBytes + kSlotBias) + h * hcols);
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_tab_empty + last_slot * 8);
@@ -318,8 +318,8 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const CUtenso
 }
 
 // All tiles of this CTA for one epilogue warp, with ONE drain variant.
-template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP>
-__device__ __forceinline__ void epilogue_tiles(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+template <int KIND, bool DUAL, bool PAIR, bool MAGIC, bool PER_TOKEN, bool DUMP, bool PEERS>
+__device__ __forceinline__ void epilogue_tiles(const GemmParams& p, const OutMaps* map_y, uint32_t tmem_base, const uint8_t* tab,
                                                uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
                                                uint32_t bar_tab_empty, volatile int* abort_flag, long long first_tile,
                                                long long tile_step, int rank, int warp, int lane, uint8_t* stage) {
@@ -327,7 +327,7 @@ __device__ __forceinline__ void epilogue_tiles(const GemmParams& p, const CUtens
     for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
         int b, m0, n0;
         tile_coords<PAIR>(p, tile, rank, b, m0, n0);
-        if (!epilogue_tile<KIND, DUAL, PAIR, MAGIC, PER_TOKEN, DUMP>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full,
+        if (!epilogue_tile<KIND, DUAL, PAIR, MAGIC, PER_TOKEN, DUMP, PEERS>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full,
                                                                      bar_tab_empty, abort_flag, au, b, m0, n0, warp, lane, stage))
             break;
     }
@@ -337,26 +337,29 @@ __device__ __forceinline__ void epilogue_tiles(const GemmParams& p, const CUtens
 // the tile loop: what runs is then one compact, contiguous block of code.  With the choice made per
 // unit inside one loop the variants' blocks interleaved, the drain overflowed the instruction cache
 // and ran 2x slower (measured: "no instruction" was the top stall reason).
+//   PEERS      fused all-gather (tiles also go to peer GPUs' buffers): generic arithmetic,
 //   DUMP       parity tests (raw accumulators are also written): generic arithmetic,
 //   PER_TOKEN  per-row activation scales multiply the table entry,
 //   MAGIC      every unit of the launch is short enough for the magic-number int->float conversion.
 template <int KIND, bool DUAL, bool PAIR>
-__device__ __forceinline__ void epilogue_role(const GemmParams& p, const CUtensorMap* map_y, uint32_t tmem_base, const uint8_t* tab,
+__device__ __forceinline__ void epilogue_role(const GemmParams& p, const OutMaps* map_y, uint32_t tmem_base, const uint8_t* tab,
                                               uint32_t bar_tmem_full, uint32_t bar_tmem_empty, uint32_t bar_tab_full,
                                               uint32_t bar_tab_empty, volatile int* abort_flag, long long first_tile,
                                               long long tile_step, int rank, int warp, int lane, uint8_t* stage) {
-#define SQ_EPI_RUN(MAGIC, PT, DUMP)                                                                                               \
-    epilogue_tiles<KIND, DUAL, PAIR, MAGIC, PT, DUMP>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full,     \
-                                                      bar_tab_empty, abort_flag, first_tile, tile_step, rank, warp, lane, stage)
+#define SQ_EPI_RUN(MAGIC, PT, DUMP, PEERS)                                                                                        \
+    epilogue_tiles<KIND, DUAL, PAIR, MAGIC, PT, DUMP, PEERS>(p, map_y, tmem_base, tab, bar_tmem_full, bar_tmem_empty, bar_tab_full, \
+                                                             bar_tab_empty, abort_flag, first_tile, tile_step, rank, warp, lane, stage)
     constexpr bool kInt = KIND != SQ_GEMM_W8A8_F8;
-    if (p.acc_dump != nullptr) {
-        SQ_EPI_RUN(false, true, true);
+    if (p.n_peers > 0) {
+        SQ_EPI_RUN(false, true, false, true);      // fused all-gather: one generic variant (exact arithmetic, see DUMP)
+    } else if (p.acc_dump != nullptr) {
+        SQ_EPI_RUN(false, true, true, false);
     } else if (p.sx_rs != 0) {
-        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, true, false);
-        else SQ_EPI_RUN(false, true, false);
+        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, true, false, false);
+        else SQ_EPI_RUN(false, true, false, false);
     } else {
-        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, false, false);
-        else SQ_EPI_RUN(false, false, false);
+        if (kInt && p.all_magic) SQ_EPI_RUN(kInt, false, false, false);
+        else SQ_EPI_RUN(false, false, false, false);
     }
 #undef SQ_EPI_RUN
 }

@@ -312,7 +312,10 @@ __device__ __forceinline__ void store_peers(const GemmParams& p, const float (&o
 // Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
 // chunk; the LSU stays free for the MMA / producer warps, every DRAM sector is written whole);
 // otherwise each thread writes its row directly.  `stage` is this warp's 2 KB staging area.
-__device__ __forceinline__ void store_output(const GemmParams& p, const CUtensorMap* map_y, const float (&acc)[128], int nch,
+// PEERS: the launch also writes peer GPUs' buffers (fused all-gather); a compile-time switch, because even a skipped
+// branch per chunk in this fully unrolled loop costs every launch about 1.5 % (measured).
+template <bool PEERS>
+__device__ __forceinline__ void store_output(const GemmParams& p, const OutMaps* map_y, const float (&acc)[128], int nch,
                                              long long b, long long m, int m_warp, bool row_ok, long long ncol0,
                                              uint8_t* stage, int lane, const float* bias_s) {
     const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
@@ -352,10 +355,17 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(map_y, stage_u32 + off, static_cast<int>(nc) * esz, m_warp, static_cast<int>(b));   // the map is byte-typed
+                tma_store_3d(&map_y->y, stage_u32 + off, static_cast<int>(nc) * esz, m_warp, static_cast<int>(b));   // the map is byte-typed
+                if constexpr (PEERS) {
+                    if (p.peer_tma)   // fused all-gather: the same box goes to every peer GPU, asynchronously
+                        for (int j = 0; j < p.n_peers; ++j)
+                            tma_store_3d(&map_y->peer[j], stage_u32 + off, static_cast<int>(nc) * esz, m_warp, 0);
+                }
                 bulk_commit();
             }
-            if (p.n_peers > 0 && row_ok) store_peers(p, o, m, nc);
+            if constexpr (PEERS) {
+                if (!p.peer_tma && row_ok) store_peers(p, o, m, nc);
+            }
         }
         return;
     }
@@ -378,7 +388,7 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
             if (p.out_dtype == SQ_F32) store_row_chunk<float>(reinterpret_cast<float*>(yrow) + ch * 16, o, valid, vec_ok);
             else if (p.out_dtype == SQ_F16) store_row_chunk<__half>(reinterpret_cast<__half*>(yrow) + ch * 16, o, valid, vec_ok);
             else store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(yrow) + ch * 16, o, valid, vec_ok);
-            if (p.n_peers > 0) store_peers(p, o, m, nc);
+            if constexpr (PEERS) store_peers(p, o, m, nc);
         }
     }
 }
@@ -391,7 +401,7 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const CUtensor
 template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(Cfg<KIND, DUAL>::kThreads, 1)
 seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_an,
-                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+                const __grid_constant__ CUtensorMap map_w, const __grid_constant__ OutMaps map_y,
                 const __grid_constant__ GemmParams p) {
     using C = Cfg<KIND, DUAL>;
     constexpr int kStages = C::kStages;
@@ -689,7 +699,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #include "seg_gemm_2cta.cuh"
 
 template <int KIND, bool DUAL>
-static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     using C = Cfg<KIND, DUAL>;
     static_assert(C::kStages >= 2 && C::kStages <= 8, "stage count");
     static bool attr_set[64] = {};
@@ -712,7 +722,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorM
 // ---------------------------------------------------------------------------------------------
 template <>
 int launch_gemm<SQ_TU_KIND, SQ_TU_DUAL>(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw,
-                                        const CUtensorMap& my, const GemmParams& p, cudaStream_t st) {
+                                        const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     return two_cta ? launch_2cta<SQ_TU_KIND, SQ_TU_DUAL>(ma, man, mw, my, p, st) : launch<SQ_TU_KIND, SQ_TU_DUAL>(ma, man, mw, my, p, st);
 }
 

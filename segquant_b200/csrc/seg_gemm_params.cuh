@@ -57,16 +57,24 @@ struct GemmParams {
     int y_tma;    // output goes through TMA stores (y base / strides are 16-byte aligned)
     int bn;       // tile width in use: 128, 192 or 256 (chosen on the host against wave quantisation)
     int n_peers;              // fused all-gather: further [M, *] outputs on peer GPUs
+    int peer_tma;             // they are written by TMA stores (OutMaps::peer) rather than by the threads
     void* peer_y[SQ_MAX_PEERS];
     long long peer_rs, peer_co;
     int all_magic;  // every accumulation unit has K <= 224: int32 accumulators stay inside [-2^22, 2^22)
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
 };
 
+// Output descriptors: this rank's matrix and, for the fused all-gather, the same column range of every
+// peer GPU's buffer (plain, non-multicast TMA stores; unused entries are copies of `y`).
+struct OutMaps {
+    CUtensorMap y;
+    CUtensorMap peer[SQ_MAX_PEERS];
+};
+
 // One explicit specialisation per (KIND, DUAL), each in its own translation unit so the twelve-odd
 // kernel instantiations compile in parallel.
 template <int KIND, bool DUAL>
-int launch_gemm(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const CUtensorMap& my,
+int launch_gemm(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my,
                 const GemmParams& p, cudaStream_t st);
 // Reads and clears the status word kernels of that translation unit write when a bounded wait gives up.
 template <int KIND, bool DUAL>
