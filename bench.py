@@ -331,8 +331,8 @@ def run_ours(args):
                        "parallelism": f"dp{world}"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
-                         # (one ncu capture; 65.4 MB against 72.3 MB of algorithmic operand + output bytes)
-                         "traffic": 65.4e6, "traffic_unit": "bytes per launch (ncu)",
+                         # (one ncu capture; 65.6 MB against 72.3 MB of algorithmic operand + output bytes)
+                         "traffic": 65.6e6, "traffic_unit": "bytes per launch (ncu)",
                          "kernel": "seg_gemm2_kernel<F8, dual, KSUB=2>", "kernel_ms": gemm_ms,
                          "note": ("achieved = issued 4*M*N*K per launch / mean launch time (CUDA events on the launch stream); "
                                   "peak = 2 x measured bf16 burst (of measured)" if bf16 else
