@@ -346,13 +346,21 @@ static int grid_for(long long warp_items) {
 
 template <typename T, int OUT>
 static void launch_static(const ActQuantParams& p, bool dual, bool smooth, cudaStream_t st) {
-    const int grid = grid_for(p.batch * p.M);
+    // One warp per row.  When all rows fit on the GPU at once (<= 32 warps per SM) small CTAs spread them evenly:
+    // 4096 rows as 512 CTAs of 8 warps leave SMs with 4 or 3 CTAs (15 % tail), as 2048 CTAs of 2 warps with 14 or 13.
+    const long long rows = p.batch * p.M;
+    int block = 256;
+    int grid = grid_for(rows);
+    if (rows <= static_cast<long long>(kNumSMs) * 32) {
+        block = 64;
+        grid = static_cast<int>((rows + 1) / 2 < 1 ? 1 : (rows + 1) / 2);
+    }
     if (dual) {
-        if (smooth) act_quant_kernel<T, OUT, true, true><<<grid, 256, 0, st>>>(p);
-        else act_quant_kernel<T, OUT, true, false><<<grid, 256, 0, st>>>(p);
+        if (smooth) act_quant_kernel<T, OUT, true, true><<<grid, block, 0, st>>>(p);
+        else act_quant_kernel<T, OUT, true, false><<<grid, block, 0, st>>>(p);
     } else {
-        if (smooth) act_quant_kernel<T, OUT, false, true><<<grid, 256, 0, st>>>(p);
-        else act_quant_kernel<T, OUT, false, false><<<grid, 256, 0, st>>>(p);
+        if (smooth) act_quant_kernel<T, OUT, false, true><<<grid, block, 0, st>>>(p);
+        else act_quant_kernel<T, OUT, false, false><<<grid, block, 0, st>>>(p);
     }
 }
 

@@ -8,7 +8,7 @@
 // products are exact in fp32 and summed in fp32.
 //
 // One warp owns four output columns: every lane streams 16 bytes of each of the four weight rows per
-// step (four independent 128-bit loads in flight, 512 contiguous bytes per row and warp), the few
+// step (512 contiguous bytes per row and warp, twelve independent 128-bit loads in flight), the few
 // activation rows sit in shared memory (both DualScale planes), partial sums are reduced with warp
 // shuffles once per unit.  Algorithmic bytes: N * K (weights) + M * K * (1 | 2) + M * N * b_out.
 #include <cuda_fp8.h>
@@ -22,6 +22,7 @@ namespace sq {
 
 constexpr int kGemvCols = 4;        // output columns per warp
 constexpr int kGemvWarps = 8;       // warps per CTA
+constexpr int kGemvSteps = 3;       // 512-byte steps of a weight row whose loads are in flight together
 constexpr int kGemvMaxRows = 4;      // measured: at 8 rows the tensor-core path is faster again
 constexpr long long kGemvMaxSmem = 96 * 1024;   // activation rows staged per CTA (both sides)
 
@@ -92,31 +93,43 @@ __global__ void __launch_bounds__(kGemvWarps * 32) seg_gemv_kernel(const __grid_
 #pragma unroll
                     for (int m = 0; m < MR; ++m) acc[sd][c][m] = 0;
 
-            for (int k = k0 + (lane << 4); k < k1; k += 512) {
-                uint4 wv[kGemvCols];
+            // kGemvSteps x 4 weight loads are issued before the first of them is consumed (12 independent 128-bit
+            // loads per lane: a K = 1536 row is a single round trip to memory)
+            for (int kb = k0 + (lane << 4); kb < k1; kb += 512 * kGemvSteps) {
+                uint4 wv[kGemvSteps][kGemvCols];
 #pragma unroll
-                for (int c = 0; c < kGemvCols; ++c) wv[c] = __ldg(reinterpret_cast<const uint4*>(wrow[c] + k));
+                for (int t = 0; t < kGemvSteps; ++t)
 #pragma unroll
-                for (int sd = 0; sd < SIDES; ++sd) {
+                    for (int c = 0; c < kGemvCols; ++c)
+                        if (kb + 512 * t < k1) wv[t][c] = __ldg(reinterpret_cast<const uint4*>(wrow[c] + kb + 512 * t));
 #pragma unroll
-                    for (int m = 0; m < MR; ++m) {
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(sd * MR + m) * K + k);
-                        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                for (int t = 0; t < kGemvSteps; ++t) {
+                    const int k = kb + 512 * t;
+                    if (k < k1) {
 #pragma unroll
-                        for (int c = 0; c < kGemvCols; ++c) {
-                            const uint32_t ww[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
-                            if constexpr (kF8) {
+                        for (int sd = 0; sd < SIDES; ++sd) {
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    float xf[4], wf[4];
-                                    e4m3x4_to_float(xw[q], xf);
-                                    e4m3x4_to_float(ww[q], wf);
+                            for (int m = 0; m < MR; ++m) {
+                                const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(sd * MR + m) * K + k);
+                                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-                                    for (int e = 0; e < 4; ++e) acc[sd][c][m] = fmaf(xf[e], wf[e], acc[sd][c][m]);
+                                for (int c = 0; c < kGemvCols; ++c) {
+                                    const uint32_t ww[4] = {wv[t][c].x, wv[t][c].y, wv[t][c].z, wv[t][c].w};
+                                    if constexpr (kF8) {
+#pragma unroll
+                                        for (int q = 0; q < 4; ++q) {
+                                            float xf[4], wf[4];
+                                            e4m3x4_to_float(xw[q], xf);
+                                            e4m3x4_to_float(ww[q], wf);
+#pragma unroll
+                                            for (int e = 0; e < 4; ++e) acc[sd][c][m] = fmaf(xf[e], wf[e], acc[sd][c][m]);
+                                        }
+                                    } else {
+#pragma unroll
+                                        for (int q = 0; q < 4; ++q)
+                                            acc[sd][c][m] = __dp4a(static_cast<int>(xw[q]), static_cast<int>(ww[q]), acc[sd][c][m]);
+                                    }
                                 }
-                            } else {
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) acc[sd][c][m] = __dp4a(static_cast<int>(xw[q]), static_cast<int>(ww[q]), acc[sd][c][m]);
                             }
                         }
                     }
