@@ -236,6 +236,7 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
 
         float amax = 0.0f, nmax = 0.0f;
+#pragma unroll 4   // several independent 128-bit loads in flight per lane
         for (int k = k0 + (lane << 4); k < k1; k += 512) {
             float v[16];
             load16<T>(xr + k, v);
@@ -261,6 +262,7 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
             p.sx_out[(b * p.num_segs + s) * p.M + r] = sc;
             if constexpr (DUAL) p.sx_neg_out[(b * p.num_segs + s) * p.M + r] = scn;
         }
+#pragma unroll 4
         for (int k = k0 + (lane << 4); k < k1; k += 512) {
             float v[16];
             load16<T>(xr + k, v);
@@ -366,7 +368,31 @@ static void launch_static(const ActQuantParams& p, bool dual, bool smooth, cudaS
 
 template <typename T, int OUT>
 static void launch_dynamic(const ActQuantParams& p, bool dual, cudaStream_t st) {
-    const int grid = grid_for(p.batch * p.M * p.num_segs);
+    // The second pass re-reads every row segment.  It only finds it in L2 if the segments in flight on the whole GPU
+    // fit there: with long segments (>= 8 KB) residency is held to 16 warps per SM -- 148 x 16 x 24 KB = 57 MB for a
+    // 12288-wide bf16 row, against 227 MB with 64 warps per SM, which L2 (126 MB) cannot hold -- by giving every
+    // 128-thread CTA a quarter of the shared memory it never touches.
+    int longest = 0;
+    for (int s = 0; s < p.num_segs; ++s) longest = p.seg_bounds[s + 1] - p.seg_bounds[s] > longest ? p.seg_bounds[s + 1] - p.seg_bounds[s] : longest;
+    const long long items = p.batch * p.M * p.num_segs;
+    if (static_cast<long long>(longest) * sizeof(T) >= 8192) {
+        constexpr int kHoldSmem = 56 * 1024;
+        static bool attr_set[2][64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 64 || !attr_set[dual ? 1 : 0][dev]) {
+            if (dual) cudaFuncSetAttribute(act_quant_dynamic_kernel<T, OUT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHoldSmem);
+            else cudaFuncSetAttribute(act_quant_dynamic_kernel<T, OUT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHoldSmem);
+            if (dev < 64) attr_set[dual ? 1 : 0][dev] = true;
+        }
+        long long ctas = (items + 3) / 4;
+        if (ctas > kNumSMs * 4) ctas = kNumSMs * 4;
+        const int grid = static_cast<int>(ctas < 1 ? 1 : ctas);
+        if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 128, kHoldSmem, st>>>(p);
+        else act_quant_dynamic_kernel<T, OUT, false><<<grid, 128, kHoldSmem, st>>>(p);
+        return;
+    }
+    const int grid = grid_for(items);
     if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 256, 0, st>>>(p);
     else act_quant_dynamic_kernel<T, OUT, false><<<grid, 256, 0, st>>>(p);
 }

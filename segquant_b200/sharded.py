@@ -105,3 +105,16 @@ class ColumnShardedSegLinear:
         self.layer(x.unsqueeze(0), out=full[:, lo:hi].unsqueeze(0), peer_outputs=(self._peer_ptrs, self.n_total, lo))
         dist.all_reduce(self._flag, group=self.group)   # stream-ordered barrier: completes after every rank's GEMM
         return full
+
+    # bytes one GPU sends to its peers above which the NCCL all-gather is faster than the fused stores (measured on
+    # 2 and 8 B200s: the epilogue's 32-row x 16-column boxes are 32-byte row segments on NVLink, which costs bandwidth
+    # once the exchange, not the GEMM, sets the time)
+    FUSED_MAX_BYTES = 70 * 1024 * 1024
+
+    def forward_auto(self, x):
+        """Fused exchange for small and medium outputs, NCCL all-gather for large ones.  x [M, K]."""
+        out_bytes = x.shape[0] * (self.n_total // self.world) * 2 * (self.world - 1)
+        if getattr(self, "_full", None) is not None and x.dim() == 2 and x.shape[0] <= self._full.shape[0] \
+                and out_bytes <= self.FUSED_MAX_BYTES:
+            return self.forward_fused(x)
+        return self.forward(x)
