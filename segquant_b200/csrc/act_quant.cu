@@ -7,6 +7,8 @@
 //
 // Work split: one warp walks one row, one 128-bit load per lane and step, eight loads in flight per
 // lane; the dynamic per-token kernel gives one warp to a (row, segment).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace sq {
@@ -236,17 +238,43 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
 
         float amax = 0.0f, nmax = 0.0f;
+        if constexpr (sizeof(T) == 2) {
+            // 16-bit inputs: the extremes are taken on packed pairs (one abs + one max instruction per two elements;
+            // max of values is exact in their own format), converted to fp32 once per row
+            using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+            uint32_t zero_bits = 0u;
+            T2 pmax = *reinterpret_cast<T2*>(&zero_bits), pneg = pmax;
 #pragma unroll 4   // several independent 128-bit loads in flight per lane
-        for (int k = k0 + (lane << 4); k < k1; k += 512) {
-            float v[16];
-            load16<T>(xr + k, v);
+            for (int k = k0 + (lane << 4); k < k1; k += 512) {
+                const uint4 a = __ldg(reinterpret_cast<const uint4*>(xr + k));
+                const uint4 c = __ldg(reinterpret_cast<const uint4*>(xr + k + 8));
+                const uint32_t w[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                if constexpr (DUAL) {
-                    amax = fmaxf(amax, v[i]);    // max over x > 0 of x (0 if none)
-                    nmax = fmaxf(nmax, -v[i]);   // max over x < 0 of |x|
-                } else {
-                    amax = fmaxf(amax, fabsf(v[i]));
+                for (int i = 0; i < 8; ++i) {
+                    const T2 v = *reinterpret_cast<const T2*>(&w[i]);
+                    if constexpr (DUAL) {
+                        pmax = __hmax2(pmax, v);             // max over x > 0 of x (0 if none)
+                        pneg = __hmax2(pneg, __hneg2(v));    // max over x < 0 of |x|
+                    } else {
+                        pmax = __hmax2(pmax, __habs2(v));
+                    }
+                }
+            }
+            amax = fmaxf(to_float<T>(pmax.x), to_float<T>(pmax.y));
+            if constexpr (DUAL) nmax = fmaxf(to_float<T>(pneg.x), to_float<T>(pneg.y));
+        } else {
+#pragma unroll 4
+            for (int k = k0 + (lane << 4); k < k1; k += 512) {
+                float v[16];
+                load16<T>(xr + k, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if constexpr (DUAL) {
+                        amax = fmaxf(amax, v[i]);    // max over x > 0 of x (0 if none)
+                        nmax = fmaxf(nmax, -v[i]);   // max over x < 0 of |x|
+                    } else {
+                        amax = fmaxf(amax, fabsf(v[i]));
+                    }
                 }
             }
         }
@@ -368,31 +396,11 @@ static void launch_static(const ActQuantParams& p, bool dual, bool smooth, cudaS
 
 template <typename T, int OUT>
 static void launch_dynamic(const ActQuantParams& p, bool dual, cudaStream_t st) {
-    // The second pass re-reads every row segment.  It only finds it in L2 if the segments in flight on the whole GPU
-    // fit there: with long segments (>= 8 KB) residency is held to 16 warps per SM -- 148 x 16 x 24 KB = 57 MB for a
-    // 12288-wide bf16 row, against 227 MB with 64 warps per SM, which L2 (126 MB) cannot hold -- by giving every
-    // 128-thread CTA a quarter of the shared memory it never touches.
-    int longest = 0;
-    for (int s = 0; s < p.num_segs; ++s) longest = p.seg_bounds[s + 1] - p.seg_bounds[s] > longest ? p.seg_bounds[s + 1] - p.seg_bounds[s] : longest;
-    const long long items = p.batch * p.M * p.num_segs;
-    if (static_cast<long long>(longest) * sizeof(T) >= 8192) {
-        constexpr int kHoldSmem = 56 * 1024;
-        static bool attr_set[2][64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 64 || !attr_set[dual ? 1 : 0][dev]) {
-            if (dual) cudaFuncSetAttribute(act_quant_dynamic_kernel<T, OUT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHoldSmem);
-            else cudaFuncSetAttribute(act_quant_dynamic_kernel<T, OUT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHoldSmem);
-            if (dev < 64) attr_set[dual ? 1 : 0][dev] = true;
-        }
-        long long ctas = (items + 3) / 4;
-        if (ctas > kNumSMs * 4) ctas = kNumSMs * 4;
-        const int grid = static_cast<int>(ctas < 1 ? 1 : ctas);
-        if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 128, kHoldSmem, st>>>(p);
-        else act_quant_dynamic_kernel<T, OUT, false><<<grid, 128, kHoldSmem, st>>>(p);
-        return;
-    }
-    const int grid = grid_for(items);
+    // Measured alternatives that were NOT faster than this two-pass kernel (161 us on 16384 x 12288 bf16, 0.57 of the
+    // copy roofline; DRAM reads are already 1.02x the input, the second pass hits L2): holding residency to 16 warps per
+    // SM (164 us), keeping the segment in the registers of a 32-256 thread group (172-203 us), parking it in shared
+    // memory between the passes (175 us, 8 warps per SM).
+    const int grid = grid_for(p.batch * p.M * p.num_segs);
     if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 256, 0, st>>>(p);
     else act_quant_dynamic_kernel<T, OUT, false><<<grid, 256, 0, st>>>(p);
 }
