@@ -119,6 +119,18 @@ int sq_quantize_act(const sq_act_quant_args* args, sq_stream_t stream);
 int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev,
                             float* sx_neg_out_dev, sq_stream_t stream);
 
+/* ---- LayerNorm + adaLN modulation + activation quantise (no counterpart in the reference) ----
+ * y = LayerNorm(x) * (1 + scale[b]) + shift[b], LayerNorm over K without affine parameters (eps inside the square
+ * root), immediately quantised like sq_quantize_act with the static per-segment scales of `args` (sx_row_stride must
+ * be 0, smooth_dev NULL).  Fuses the three torch kernels that sit between the residual stream and the q / k / v and
+ * MLP projections of a DiT block (layer_norm, modulation, quantise: each a full pass over [tokens, hidden]) into one
+ * read of x.  shift_dev / scale_dev: [batch, K] in the dtype of x, rows mod_batch_stride elements apart, or both NULL
+ * for a plain LayerNorm.  A row may be at most 4096 bytes (K <= 2048 for 16-bit inputs); longer rows return
+ * SQ_ERR_UNSUPPORTED and the caller keeps the separate kernels.
+ */
+int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev,
+                         int64_t mod_batch_stride, float eps, sq_stream_t stream);
+
 /* ---- weight quantise / pack ---------------------------------------------------------------
  * Replaces real_quantized_quantize_weights<T> (real_gemm.cu:538-638; pybind names in
  * seg_utils.h:82-120).  w is [N, K] contiguous.  scale_mode 0: one scalar `scale_scalar`

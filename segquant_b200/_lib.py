@@ -24,7 +24,7 @@ SQ_GEMM_W8A8_I8, SQ_GEMM_W8A8_F8, SQ_GEMM_W4A8 = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "sq_version", "sq_last_error", "sq_status_string", "sq_device_status",
-    "sq_quantize_act", "sq_quantize_act_dynamic", "sq_quantize_weight", "sq_unpack_int4",
+    "sq_quantize_act", "sq_quantize_act_dynamic", "sq_norm_quantize_act", "sq_quantize_weight", "sq_unpack_int4",
     "sq_gemm", "sq_gemm_num_units", "sq_seg_linear",
 )
 
@@ -122,6 +122,9 @@ def load():
     lib.sq_quantize_act.restype = ctypes.c_int
     lib.sq_quantize_act.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p]
     lib.sq_quantize_act_dynamic.restype = ctypes.c_int
+    lib.sq_norm_quantize_act.restype = ctypes.c_int
+    lib.sq_norm_quantize_act.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                         ctypes.c_float, ctypes.c_void_p]
     lib.sq_quantize_act_dynamic.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.sq_quantize_weight.restype = ctypes.c_int
     lib.sq_quantize_weight.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,

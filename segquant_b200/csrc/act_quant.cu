@@ -450,4 +450,149 @@ int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_ne
     return SQ_OK;
 }
 
+// ---- LayerNorm + adaLN modulation + static quantise, one pass -----------------------------------
+// y = LN(x) * (1 + scale[b]) + shift[b] (LayerNorm without affine parameters), then the per-segment static
+// quantisation of act_quant_kernel.  In a DiT block this is what sits between the residual stream and the q / k / v
+// and MLP projections: three torch kernels (layer_norm, the modulation, the quantise) that each read and write the
+// whole [tokens, hidden] tensor.  One warp owns a row and keeps it in registers as raw 128-bit words (at most
+// kNormWords per lane): mean, variance (two passes over the registers, like torch), normalise, modulate, quantise;
+// x is read once and only bytes are written.  No counterpart in the reference.
+constexpr int kNormWords = 8;
+
+template <typename T, int OUT, bool DUAL, bool MOD>
+__global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
+                                                        const T* __restrict__ scale, long long mod_bs, float eps) {
+    constexpr int E = Unit<T>::E;
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const long long rows = p.batch * p.M;
+    const int words = static_cast<int>(p.K / E);
+    const T* __restrict__ x = static_cast<const T*>(p.x);
+    const float inv_k = 1.0f / static_cast<float>(p.K);
+
+    for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * warps_per_cta) {
+        const long long b = row / p.M, r = row - b * p.M;
+        const T* xr = x + b * p.x_batch_stride + r * p.x_row_stride;
+        uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
+        uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
+
+        uint4 raw[kNormWords];
+#pragma unroll
+        for (int j = 0; j < kNormWords; ++j)
+            if (lane + 32 * j < words) raw[j] = __ldg(reinterpret_cast<const uint4*>(xr) + lane + 32 * j);
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kNormWords; ++j) {
+            if (lane + 32 * j < words) {
+                float v[E];
+                Unit<T>::unpack(raw[j], v);
+#pragma unroll
+                for (int i = 0; i < E; ++i) sum += v[i];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum * inv_k;
+        float sq = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kNormWords; ++j) {
+            if (lane + 32 * j < words) {
+                float v[E];
+                Unit<T>::unpack(raw[j], v);
+#pragma unroll
+                for (int i = 0; i < E; ++i) { const float d = v[i] - mean; sq = fmaf(d, d, sq); }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float rstd = 1.0f / sqrtf(sq * inv_k + eps);
+
+        // segment cursor: this lane's k only grows with j
+        int s = 0;
+        int next_bound = p.seg_bounds[1];
+        float sc = __ldg(p.sx + b * p.sx_batch_stride);
+        float scn = DUAL ? __ldg(p.sx_neg + b * p.sx_batch_stride) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < kNormWords; ++j) {
+            const int u = lane + 32 * j;
+            if (u < words) {
+                const int k = u * E;
+                float v[E];
+                Unit<T>::unpack(raw[j], v);
+                if constexpr (MOD) {
+                    float sh[E], scl[E];
+                    Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(shift + b * mod_bs) + u), sh);
+                    Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(scale + b * mod_bs) + u), scl);
+#pragma unroll
+                    for (int i = 0; i < E; ++i) v[i] = fmaf((v[i] - mean) * rstd, 1.0f + scl[i], sh[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < E; ++i) v[i] = (v[i] - mean) * rstd;
+                }
+                while (k >= next_bound) {
+                    ++s;
+                    next_bound = p.seg_bounds[s + 1];
+                    sc = __ldg(p.sx + b * p.sx_batch_stride + s * p.sx_seg_stride);
+                    if constexpr (DUAL) scn = __ldg(p.sx_neg + b * p.sx_batch_stride + s * p.sx_seg_stride);
+                }
+                quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);
+            }
+        }
+    }
+}
+
+template <typename T, int OUT>
+static void launch_norm(const ActQuantParams& p, bool dual, const void* shift, const void* scale, long long mod_bs, float eps,
+                        cudaStream_t st) {
+    const long long rows = p.batch * p.M;
+    int block = 256;
+    int grid = grid_for(rows);
+    if (rows <= static_cast<long long>(kNumSMs) * 32) {
+        block = 64;
+        grid = static_cast<int>((rows + 1) / 2 < 1 ? 1 : (rows + 1) / 2);
+    }
+    const T* sh = static_cast<const T*>(shift);
+    const T* sc = static_cast<const T*>(scale);
+    if (shift != nullptr) {
+        if (dual) norm_quant_kernel<T, OUT, true, true><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
+        else norm_quant_kernel<T, OUT, false, true><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
+    } else {
+        if (dual) norm_quant_kernel<T, OUT, true, false><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
+        else norm_quant_kernel<T, OUT, false, false><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
+    }
+}
+
+int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st) {
+    int rc = validate(a, false);
+    if (rc != SQ_OK) return rc;
+    if (a->batch * a->M * a->K == 0) return SQ_OK;
+    SQ_REQUIRE((shift == nullptr) == (scale == nullptr), SQ_ERR_INVALID_ARG, "sq_norm_quantize_act: shift and scale go together");
+    SQ_REQUIRE(a->sx_row_stride == 0 && a->smooth_dev == nullptr, SQ_ERR_UNSUPPORTED,
+               "sq_norm_quantize_act: static per-segment scales only, no smoothing vector");
+    const long long esz = a->x_dtype == SQ_F32 ? 4 : 2;
+    const long long words = a->K * esz / 16;
+    SQ_REQUIRE((a->K * esz) % 16 == 0 && words <= 32 * kNormWords, SQ_ERR_UNSUPPORTED,
+               "sq_norm_quantize_act: a row must be at most %d bytes (K = %lld)", 32 * kNormWords * 16, static_cast<long long>(a->K));
+    SQ_REQUIRE(reinterpret_cast<uintptr_t>(a->x_dev) % 16 == 0 && (a->x_row_stride * esz) % 16 == 0 && (a->x_batch_stride * esz) % 16 == 0,
+               SQ_ERR_ALIGNMENT, "sq_norm_quantize_act: x rows must be 16-byte aligned");
+    if (shift != nullptr)
+        SQ_REQUIRE(reinterpret_cast<uintptr_t>(shift) % 16 == 0 && reinterpret_cast<uintptr_t>(scale) % 16 == 0 && (mod_bs * esz) % 16 == 0,
+                   SQ_ERR_ALIGNMENT, "sq_norm_quantize_act: shift / scale rows must be 16-byte aligned");
+    ActQuantParams p;
+    fill_params(a, p);
+    const bool dual = a->xq_neg_dev != nullptr;
+#define SQ_DISPATCH(T)                                                                          \
+    do {                                                                                        \
+        if (a->out_kind == SQ_Q_INT8) launch_norm<T, SQ_Q_INT8>(p, dual, shift, scale, mod_bs, eps, st); \
+        else launch_norm<T, SQ_Q_E4M3>(p, dual, shift, scale, mod_bs, eps, st);                 \
+    } while (0)
+    if (a->x_dtype == SQ_F32) SQ_DISPATCH(float);
+    else if (a->x_dtype == SQ_F16) SQ_DISPATCH(__half);
+    else SQ_DISPATCH(__nv_bfloat16);
+#undef SQ_DISPATCH
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
+}
+
 }  // namespace sq

@@ -22,6 +22,7 @@ void clear_error() { g_err[0] = 0; }
 // implemented in act_quant.cu / weight_quant.cu / seg_gemm.cu
 int quantize_act(const sq_act_quant_args* a, cudaStream_t st);
 int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_neg_out, cudaStream_t st);
+int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st);
 int quantize_weight(const void* w, int w_dtype, long long N, long long K, int scale_mode, float scale_scalar,
                     const float* scale, int group_size, int out_kind, void* out, cudaStream_t st);
 int unpack_int4(const void* packed, void* out, long long numel, cudaStream_t st);
@@ -65,6 +66,12 @@ int sq_quantize_act(const sq_act_quant_args* args, sq_stream_t stream) {
 int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev, float* sx_neg_out_dev, sq_stream_t stream) {
     sq::clear_error();
     return sq::quantize_act_dynamic(args, sx_out_dev, sx_neg_out_dev, static_cast<cudaStream_t>(stream));
+}
+
+int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev, int64_t mod_batch_stride,
+                         float eps, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::norm_quantize_act(args, shift_dev, scale_dev, mod_batch_stride, eps, static_cast<cudaStream_t>(stream));
 }
 
 int sq_quantize_weight(const void* w_dev, int32_t w_dtype, int64_t N, int64_t K, int32_t scale_mode, float scale_scalar,

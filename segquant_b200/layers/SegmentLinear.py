@@ -177,6 +177,12 @@ class SegmentLinear(nn.Module):
         return out + self.bias_data if self.bias else out
 
 
+    def forward_quantized(self, xq, xq_neg=None, out=None, out_dtype=torch.bfloat16):
+        """The layer's GEMM + epilogue on activations the caller has already quantised with
+        `self.optimizer.input_quant_params()` (e.g. ops.norm_quantize_act); xq (B, M, K) uint8."""
+        return self.optimizer.fused_gemm(xq, xq_neg, self.bias_data if self.bias else None, out=out, out_dtype=out_dtype)
+
+
 def create_segment_linear(input_dtype: DType, weight_dtype: DType, opt: Optimum, calib: Calibrate, in_features,
                           out_features, opt_kwargs, calib_kwargs, input_quant_args, weight_quant_args, **kwargs):
     return SegmentLinear(in_features, out_features, input_quant_type=input_dtype.value,

@@ -14,8 +14,9 @@ would give it (segquant/pattern_detector.py:239-358):
   * attention output projections: S = 1 by default, or 24 K-segments of 64 (`out_proj_segments=24`,
     the reshape_to_linear pattern: heads x head_dim);
   * everything else: S = 1.
-Attention (torch SDPA) and the norms stay bf16.  Scales are calibrated once from one forward of the
-float model on the given inputs (AMax), then every layer runs the fused quantise + tcgen05 GEMM path.
+Attention (torch SDPA) stays bf16.  Scales are calibrated once from one forward of the float model on the
+given inputs (AMax), then every layer runs the fused quantise + tcgen05 GEMM path; where a LayerNorm + adaLN
+modulation feeds linears, one kernel normalises, modulates and quantises (FusedNorm below).
 """
 import math
 
@@ -57,6 +58,51 @@ def _layer_norm(x):
     return F.layer_norm(x, (x.shape[-1],), eps=1e-6)
 
 
+def _modulate(x, shift, scale):
+    """LayerNorm(x) * (1 + scale) + shift; shift / scale are (B, H) or None."""
+    n = _layer_norm(x)
+    return n if shift is None else torch.addcmul(shift.unsqueeze(1), n, 1 + scale.unsqueeze(1))
+
+
+class FusedNorm:
+    """Runs `layers` on LayerNorm(x) * (1 + scale) + shift.  Linears that were calibrated on the same tensor hold the
+    same static input scale, so the normalisation, the modulation and the quantisation are done once, in one kernel that
+    reads x once and writes bytes (ops.norm_quantize_act), and every layer's GEMM consumes those bytes.  Groups whose
+    layers do not share their quantisation parameters (or whose rows are too long for the kernel) take the unfused path;
+    the decision is made on the first call, outside any graph capture, and cached."""
+
+    MAX_ROW_BYTES = 4096
+
+    def __init__(self):
+        self.plan = {}
+
+    def _params(self, layers, x):
+        key = tuple(id(l) for l in layers)
+        if key not in self.plan:
+            self.plan[key] = None
+            try:
+                ps = [l.layer.optimizer.input_quant_params() for l in layers]
+            except RuntimeError:
+                return None
+            b0, sx0, sn0, k0 = ps[0]
+            same = all(list(b) == list(b0) and k == k0 and torch.equal(sx, sx0) and (sn is None) == (sn0 is None)
+                       and (sn is None or torch.equal(sn, sn0)) for b, sx, sn, k in ps[1:])
+            if same and x.shape[-1] * x.element_size() <= self.MAX_ROW_BYTES:
+                self.plan[key] = ps[0]
+        return self.plan[key]
+
+    def __call__(self, layers, x, shift, scale, outs=None):
+        from . import ops
+        outs = outs or [None] * len(layers)
+        p = self._params(layers, x)
+        if p is None:
+            n = _modulate(x, shift, scale)
+            return [l(n, out=o) for l, o in zip(layers, outs)]
+        bounds, sx, sx_neg, kind = p
+        xq, xq_neg = ops.norm_quantize_act(x, bounds, sx, sx_neg, out_kind=kind, shift=shift, scale=scale)
+        return [l.layer.forward_quantized(xq, xq_neg, out=o, out_dtype=x.dtype) for l, o in zip(layers, outs)]
+
+
 def _timestep_embedding(t, dim=256):
     half = dim // 2
     freqs = torch.exp(-math.log(10000.0) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
@@ -85,21 +131,19 @@ class JointBlock:
             names += ["to_add_out", "ffc0", "ffc2"]
         return [getattr(self, n) for n in names]
 
-    def forward(self, img, txt, c_act, call):
+    def forward(self, img, txt, c_act, call, norm_call):
         """c_act = SiLU(conditioning) [B, H]; call(layer, x, out=None) runs either the calibration or the quantized
-        linear, writing into `out` when given."""
+        linear, writing into `out` when given; norm_call(layers, x, shift, scale, outs) runs `layers` on the
+        normalised and modulated x."""
         B, Ti, H = img.shape
         Tt = txt.shape[1]
-        m = call(self.norm1, c_act).unsqueeze(1).chunk(6, dim=-1)            # shift, scale, gate (msa), shift, scale, gate (mlp)
-        n_img = torch.addcmul(m[0], _layer_norm(img), 1 + m[1])
-        mc = call(self.norm1_context, c_act).unsqueeze(1).chunk(2 if self.last else 6, dim=-1)
-        n_txt = torch.addcmul(mc[0], _layer_norm(txt), 1 + mc[1])
+        m = call(self.norm1, c_act).chunk(6, dim=-1)                         # shift, scale, gate (msa), shift, scale, gate (mlp)
+        mc = call(self.norm1_context, c_act).chunk(2 if self.last else 6, dim=-1)
 
         # the six projections write straight into their token range of one joint buffer per q / k / v
         qkv = torch.empty((3, B, Ti + Tt, H), dtype=img.dtype, device=img.device)
-        for j, (li, lt) in enumerate(((self.to_q, self.add_q), (self.to_k, self.add_k), (self.to_v, self.add_v))):
-            call(li, n_img, qkv[j, :, :Ti])
-            call(lt, n_txt, qkv[j, :, Ti:])
+        norm_call((self.to_q, self.to_k, self.to_v), img, m[0], m[1], [qkv[j, :, :Ti] for j in range(3)])
+        norm_call((self.add_q, self.add_k, self.add_v), txt, mc[0], mc[1], [qkv[j, :, Ti:] for j in range(3)])
 
         def heads(t):
             return t.view(B, Ti + Tt, self.heads, H // self.heads).transpose(1, 2)
@@ -107,13 +151,13 @@ class JointBlock:
         a = F.scaled_dot_product_attention(heads(qkv[0]), heads(qkv[1]), heads(qkv[2])).transpose(1, 2).reshape(B, Ti + Tt, H)
         a_img, a_txt = a[:, :Ti], a[:, Ti:]
 
-        img = torch.addcmul(img, m[2], call(self.to_out, a_img))
-        n2 = torch.addcmul(m[3], _layer_norm(img), 1 + m[4])
-        img = torch.addcmul(img, m[5], call(self.ff2, F.gelu(call(self.ff0, n2), approximate="tanh")))
+        img = torch.addcmul(img, m[2].unsqueeze(1), call(self.to_out, a_img))
+        h = norm_call((self.ff0,), img, m[3], m[4])[0]
+        img = torch.addcmul(img, m[5].unsqueeze(1), call(self.ff2, F.gelu(h, approximate="tanh")))
         if not self.last:
-            txt = torch.addcmul(txt, mc[2], call(self.to_add_out, a_txt))
-            n2c = torch.addcmul(mc[3], _layer_norm(txt), 1 + mc[4])
-            txt = torch.addcmul(txt, mc[5], call(self.ffc2, F.gelu(call(self.ffc0, n2c), approximate="tanh")))
+            txt = torch.addcmul(txt, mc[2].unsqueeze(1), call(self.to_add_out, a_txt))
+            h = norm_call((self.ffc0,), txt, mc[3], mc[4])[0]
+            txt = torch.addcmul(txt, mc[5].unsqueeze(1), call(self.ffc2, F.gelu(h, approximate="tanh")))
         return img, txt
 
 
@@ -132,6 +176,7 @@ class SyntheticMMDiT:
         self.norm_out = mk(hidden, 2 * hidden, chunks=2, dual=True)
         self.proj_out = mk(hidden, 64)
         self.calibrated = False
+        self.fused_norm = FusedNorm()      # set to None to run layer_norm / modulation / quantise as separate kernels
 
     def linears(self):
         out = [self.context_embedder, self.t_lin1, self.t_lin2, self.p_lin1, self.p_lin2]
@@ -139,7 +184,7 @@ class SyntheticMMDiT:
             out += b.linears()
         return out + [self.norm_out, self.proj_out]
 
-    def _forward(self, latents, text, pooled, timestep, call):
+    def _forward(self, latents, text, pooled, timestep, call, norm_call):
         """latents [B, Ti, H] (already patch-embedded: the patch embedder is a Conv2d, never quantised),
         text [B, Tt, 4096], pooled [B, 2048], timestep [B]."""
         temb = call(self.t_lin2, F.silu(call(self.t_lin1, _timestep_embedding(timestep).to(self.dtype))))
@@ -148,10 +193,9 @@ class SyntheticMMDiT:
         txt = call(self.context_embedder, text)
         img = latents
         for blk in self.blocks:
-            img, txt = blk.forward(img, txt, c_act, call)
-        mod = call(self.norm_out, c_act).unsqueeze(1).chunk(2, dim=-1)       # scale, shift
-        img = torch.addcmul(mod[1], _layer_norm(img), 1 + mod[0])
-        return call(self.proj_out, img)
+            img, txt = blk.forward(img, txt, c_act, call, norm_call)
+        mod = call(self.norm_out, c_act).chunk(2, dim=-1)                    # scale, shift
+        return norm_call((self.proj_out,), img, mod[1], mod[0])[0]
 
     def calibrate(self, latents, text, pooled, timestep):
         """One forward of the float model; every linear records its input range and is then quantized."""
@@ -162,7 +206,10 @@ class SyntheticMMDiT:
                     out.copy_(y)
                     return out
                 return y
-            y = self._forward(latents, text, pooled, timestep, calib)
+            def calib_norm(layers, x, shift, scale, outs=None):
+                n = _modulate(x, shift, scale)
+                return [calib(l, n, o) for l, o in zip(layers, outs or [None] * len(layers))]
+            y = self._forward(latents, text, pooled, timestep, calib, calib_norm)
             for lin in self.linears():
                 lin.finish()
         self.calibrated = True
@@ -172,7 +219,11 @@ class SyntheticMMDiT:
         if not self.calibrated:
             raise RuntimeError("call calibrate() once before running the quantized model")
         with torch.no_grad():
-            return self._forward(latents, text, pooled, timestep, lambda layer, x, out=None: layer(x, out=out))
+            def unfused(layers, x, shift, scale, outs=None):
+                n = _modulate(x, shift, scale)
+                return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))]
+            return self._forward(latents, text, pooled, timestep, lambda layer, x, out=None: layer(x, out=out),
+                                 self.fused_norm or unfused)
 
     def linear_ops(self, batch):
         """Useful operations 2*M*N*K of one step, summed over every quantized linear."""

@@ -106,6 +106,48 @@ def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=Fal
     return xq, xqn
 
 
+def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=None, scale=None, eps=1e-6):
+    """LayerNorm(x) * (1 + scale) + shift, quantised with the static per-segment scales, in one pass over x.
+
+    x: (B, T, K) with contiguous rows; shift / scale: (B, K) in x's dtype (or both None for a plain LayerNorm);
+    sx (and sx_neg for DualScale): (S,) float32 shared by all batches.  Returns (xq, xq_neg) uint8 (B, T, K)."""
+    global launch_count
+    _need_cuda(x, sx, sx_neg, shift, scale)
+    if x.dim() != 3 or x.stride(-1) != 1:
+        raise ValueError("norm_quantize_act needs a (B, T, K) tensor with contiguous rows")
+    B, M, K = x.shape
+    dual = sx_neg is not None
+    xq = torch.empty((B, M, K), dtype=torch.uint8, device=x.device)
+    xqn = torch.empty((B, M, K), dtype=torch.uint8, device=x.device) if dual else None
+    if x.numel() == 0:
+        return xq, xqn
+    a = L.ActQuantArgs()
+    a.x_dev, a.x_dtype, a.out_kind = x.data_ptr(), _dt(x), out_kind
+    a.batch, a.M, a.K = B, M, K
+    a.x_batch_stride, a.x_row_stride = (x.stride(0) if B > 1 else 0), x.stride(1)
+    a.num_segs = len(bounds) - 1
+    L.set_bounds(a.seg_bounds, bounds)
+    a.sx_dev = sx.data_ptr()
+    a.sx_neg_dev = sx_neg.data_ptr() if dual else None
+    a.sx_batch_stride, a.sx_seg_stride, a.sx_row_stride = 0, 1, 0
+    a.xq_dev = xq.data_ptr()
+    a.xq_neg_dev = xqn.data_ptr() if dual else None
+    a.xq_batch_stride, a.xq_row_stride = M * K, K
+    mod_bs = 0
+    if shift is not None:
+        if shift.dtype != x.dtype or scale.dtype != x.dtype or shift.shape != (B, K) or scale.shape != (B, K):
+            raise ValueError("shift / scale must be (B, K) tensors of x's dtype")
+        if shift.stride(-1) != 1 or scale.stride(-1) != 1 or (B > 1 and shift.stride(0) != scale.stride(0)):
+            shift, scale = shift.contiguous(), scale.contiguous()     # views with one common row stride are read in place
+        mod_bs = shift.stride(0) if B > 1 else 0
+    with torch.cuda.device(x.device):
+        L.check(L.load().sq_norm_quantize_act(ctypes.byref(a), shift.data_ptr() if shift is not None else None,
+                                              scale.data_ptr() if scale is not None else None, mod_bs, float(eps), _stream(x)),
+                "sq_norm_quantize_act")
+    launch_count += 1
+    return xq, xqn
+
+
 def quantize_act_dynamic(x, bounds, out_kind=L.SQ_Q_INT8, dual=False):
     """Per-token dynamic scales + quantise in one launch.  x (M, K).  Returns
     (xq, xq_neg, sx, sx_neg) with scales of shape (S, M)."""

@@ -128,6 +128,33 @@ class BaseOptimizer:
                               dynamic=bool(iq.dynamic), group_size=f["group"], sw_strides=f["sw_strides"], bias=bias, out=out,
                               peer_outputs=peer_outputs)
 
+    def input_quant_params(self):
+        """(bounds, sx, sx_neg, activation kind) of the fused forward's static activation quantisation, for callers that
+        quantise the input themselves (e.g. fused with a preceding normalisation) and then call fused_gemm()."""
+        if self._fused is None:
+            self._build_fused()
+        f = self._fused
+        if "bounds" not in f or bool(self._input_quantizer().dynamic):
+            raise RuntimeError("this layer's activations are not quantised with static per-segment scales")
+        return f["bounds"], f["sx"], f["sx_neg"], ops.KERNELS[self.kernel_type][1]
+
+    def fused_gemm(self, xq, xq_neg=None, bias=None, out=None, out_dtype=torch.bfloat16):
+        """GEMM + epilogue of the fused forward on activations that are already quantised: xq (B, M, K) uint8."""
+        if self._fused is None:
+            self._build_fused()
+        f = self._fused
+        kind = ops.KERNELS[self.kernel_type][0]
+        if out is not None:
+            ops.gemm(kind, xq, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"], xq_neg=xq_neg, sx_neg=f["sx_neg"], group_size=f["group"],
+                     sw_strides=f["sw_strides"], bias=bias, out_dtype=out.dtype, out=out, y_strides=(out.stride(0), out.stride(1)),
+                     sx_batch_stride=0)
+            return out
+        B, M, K = xq.shape
+        y = ops.gemm(kind, xq.view(1, B * M, K), f["wq"], f["N"], f["bounds"], f["sx"], f["sw"],
+                     xq_neg=None if xq_neg is None else xq_neg.view(1, B * M, K), sx_neg=f["sx_neg"], group_size=f["group"],
+                     sw_strides=f["sw_strides"], bias=bias, out_dtype=out_dtype)
+        return y.view(B, M, f["N"])
+
     # ---- housekeeping ------------------------------------------------------------------------------
     def _calibrate_weights(self, i_view, w_view):
         for cal, w_chunk, x_chunk in zip(self.weight_calibrators, w_view, i_view):

@@ -43,3 +43,82 @@ def test_small_step_close_to_calibration_pass():
     assert cos > 0.99
     from segquant_b200 import ops
     assert ops.device_status() == 0
+
+
+def _ref_norm_quant(x, shift, scale, bounds, sx, sx_neg, kind):
+    """fp32 restatement of the fused kernel: LayerNorm (eps 1e-6, biased variance), modulation, static quantise."""
+    from segquant_b200 import ops
+    xf = x.float()
+    mean = xf.mean(-1, keepdim=True)
+    var = ((xf - mean) ** 2).mean(-1, keepdim=True)
+    n = (xf - mean) / torch.sqrt(var + 1e-6)
+    if shift is not None:
+        n = n * (1 + scale.float().unsqueeze(1)) + shift.float().unsqueeze(1)
+    B, T, K = x.shape
+    q, qn = ops.quantize_act(n.reshape(B * T, K).contiguous(), bounds, sx, sx_neg, out_kind=kind)
+    return q.view(B, T, K), None if qn is None else qn.view(B, T, K)
+
+
+def _as_values(q, kind):
+    from segquant_b200 import _lib as L
+    return q.view(torch.int8).float() if kind == L.SQ_Q_INT8 else q.view(torch.float8_e4m3fn).float()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("kind_name", ["int8", "e4m3"])
+@pytest.mark.parametrize("dual,mod,segs", [(False, True, 1), (True, True, 3), (False, False, 2)])
+def test_norm_quantize_act_matches_unfused(dtype, kind_name, dual, mod, segs):
+    from segquant_b200 import _lib as L, ops
+    kind = L.SQ_Q_INT8 if kind_name == "int8" else L.SQ_Q_E4M3
+    torch.manual_seed(11)
+    B, T, K = 2, 77, 1024 if dtype == torch.float32 else 1536
+    x = (torch.randn(B, T, K, device="cuda") * 3 + 0.5).to(dtype)
+    modt = (torch.randn(B, 6 * K, device="cuda") * 0.3).to(dtype)          # shift / scale are strided views, as in a block
+    shift, scale = (modt[:, :K], modt[:, K:2 * K]) if mod else (None, None)
+    bounds = [0, K] if segs == 1 else ([0, K // 2, K] if segs == 2 else [0, 256, 768, K])
+    qmax = 127.0 if kind == L.SQ_Q_INT8 else 448.0
+    sx = (torch.rand(segs, device="cuda") * 2 + 3) / qmax
+    sxn = (torch.rand(segs, device="cuda") * 2 + 2) / qmax if dual else None
+    q, qn = ops.norm_quantize_act(x, bounds, sx, sxn, out_kind=kind, shift=shift, scale=scale)
+    rq, rqn = _ref_norm_quant(x, shift, scale, bounds, sx, sxn, kind)
+    for got, want in ((q, rq), (qn, rqn)):
+        if want is None:
+            assert got is None
+            continue
+        # both sides round the same fp32 value up to the last ulp of the normalisation, so a value that sits on a
+        # rounding boundary may land on the neighbouring code: allow that for a small fraction, and nothing larger
+        diff = got != want
+        assert diff.float().mean() < 2e-3
+        g, w = _as_values(got, kind)[diff], _as_values(want, kind)[diff]
+        if kind == L.SQ_Q_INT8:
+            assert torch.all((g - w).abs() <= 1)
+        else:
+            assert torch.all((g - w).abs() <= 0.126 * torch.maximum(g.abs(), w.abs()) + 2 ** -9)
+    assert ops.device_status() == 0
+
+
+def test_norm_quantize_act_rejects_long_rows():
+    from segquant_b200 import ops
+    x = torch.randn(1, 4, 4096, device="cuda", dtype=torch.bfloat16)
+    sx = torch.ones(1, device="cuda")
+    with pytest.raises(Exception):
+        ops.norm_quantize_act(x, [0, 4096], sx)
+
+
+def test_fused_norm_step_matches_unfused_step():
+    """The step with one normalise + modulate + quantise kernel per norm against the same model running torch's
+    layer_norm and modulation in bf16 followed by the quantise kernel: same weights and scales, so the only
+    difference is that the fused kernel does not round the normalised tensor to bf16 before quantising."""
+    from segquant_b200.mmdit import SyntheticMMDiT, synthetic_inputs
+    model = SyntheticMMDiT("cuda", blocks=2, hidden=256, heads=4, img_tokens=256, txt_tokens=40, seed=0)
+    inp = synthetic_inputs(2, "cuda", img_tokens=256, txt_tokens=40, hidden=256, seed=1)
+    model.calibrate(*inp)
+    fused = model(*inp).float()
+    assert any(v is not None for v in model.fused_norm.plan.values())       # the fused kernel really ran
+    keep, model.fused_norm = model.fused_norm, None
+    plain = model(*inp).float()
+    model.fused_norm = keep
+    cos = torch.nn.functional.cosine_similarity(fused.flatten(), plain.flatten(), dim=0)
+    assert cos > 0.999
+    from segquant_b200 import ops
+    assert ops.device_status() == 0
