@@ -606,7 +606,8 @@ def run_sweep(args):
 
 def run_kernels(args):
     """The HBM-bound kernels alone on [rows, 12288] tensors (larger than L2): activation quantise (bf16 / fp32, single,
-    DualScale, dynamic per-token), weight quantise (int8, packed int4 with group scales) and int4 unpack.
+    DualScale, dynamic per-token), weight quantise (int8, packed int4 with group scales), int4 unpack, and the fused
+    LayerNorm + modulation + quantise on the same bytes seen as rows of 1536.
     GB/s = algorithmic bytes / mean CUDA-event time; frac = GB/s / measured copy bandwidth."""
     from segquant_b200 import _lib as L
     from segquant_b200 import ops
@@ -631,15 +632,23 @@ def run_kernels(args):
     sw_row = (127.0 / x16.float().abs().amax(-1)).contiguous()
     sw_grp = (7.0 / x16.float().view(R, K // 128, 128).abs().amax(-1)).contiguous()
     ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128)
+    xn = x16.view(1, R * K // 1536, 1536)
+    mod = (torch.randn(1, 2 * 1536, generator=g) * 0.3).to(torch.bfloat16).to(dev)
     cases = [
         ("act_quant bf16 -> int8, 4 segments", lambda: ops.quantize_act(x16, bounds, sx, None, L.SQ_Q_INT8), R * K * 3),
         ("act_quant bf16 -> e4m3 DualScale", lambda: ops.quantize_act(x16, bounds, sx, sxn, L.SQ_Q_E4M3), R * K * 4),
+        ("act_quant GELU(bf16) -> int8 DualScale", lambda: ops.quantize_act(x16, bounds, sx, sxn, L.SQ_Q_INT8, pre_act="gelu_tanh"), R * K * 4),
         ("act_quant fp32 -> int8, 4 segments", lambda: ops.quantize_act(x32, bounds, sx, None, L.SQ_Q_INT8), R * K * 5),
         ("act_quant_dynamic bf16 -> int8 per token", lambda: ops.quantize_act_dynamic(x16, [0, K], L.SQ_Q_INT8), R * K * 3 + R * 4),
         ("weight_quant bf16 -> int8 per row", lambda: ops.quantize_weight(x16, wq8, sw_row, L.SQ_Q_INT8), R * K * 3),
         ("weight_quant bf16 -> packed int4, groups of 128", lambda: ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128),
          R * K * 2.5 + R * K // 128 * 4),
         ("unpack_int4", lambda: ops.unpack_int4(wq4), R * K * 1.5),
+        # the same bytes seen as rows of 1536 (a DiT hidden size): LayerNorm + modulation + quantise in one pass
+        ("norm_quant bf16 rows of 1536 -> int8, modulated", lambda: ops.norm_quantize_act(xn, [0, 1536], sx[:1], None, L.SQ_Q_INT8, shift=mod[:, :1536], scale=mod[:, 1536:]),
+         R * K * 3),
+        ("norm_quant bf16 rows of 1536 -> e4m3 DualScale, modulated",
+         lambda: ops.norm_quantize_act(xn, [0, 1536], sx[:1], sxn[:1], L.SQ_Q_E4M3, shift=mod[:, :1536], scale=mod[:, 1536:]), R * K * 4),
     ]
     rows = []
     for name, fn, nbytes in cases:

@@ -88,6 +88,10 @@ int64_t sq_device_status(void);
  * If xq_neg_dev != NULL the DualScale rule applies: x >= 0 goes to xq (scaled by sx), x < 0 goes
  * to xq_neg (scaled by sx_neg), the other side gets 0.
  */
+#define SQ_ACT_NONE 0
+#define SQ_ACT_GELU_TANH 1      /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) */
+#define SQ_ACT_SILU 2           /* x / (1 + exp(-x)) */
+
 typedef struct sq_act_quant_args {
     const void* x_dev;
     int32_t x_dtype;           /* SQ_F32 / SQ_F16 / SQ_BF16 */
@@ -104,6 +108,10 @@ typedef struct sq_act_quant_args {
     void* xq_dev;
     void* xq_neg_dev;          /* NULL unless DualScale */
     int64_t xq_batch_stride, xq_row_stride;      /* bytes */
+    int32_t pre_act;           /* SQ_ACT_*: activation applied to x (in fp32) before it is scaled; static scales
+                                  only, not together with smooth_dev.  No counterpart in the reference, where the
+                                  activation is a separate torch op in front of the layer.                        */
+    int32_t reserved0;         /* must be 0 */
 } sq_act_quant_args;
 
 int sq_quantize_act(const sq_act_quant_args* args, sq_stream_t stream);

@@ -20,6 +20,7 @@ SQ_ERR_TOO_LARGE = -6
 
 SQ_F32, SQ_F16, SQ_BF16 = 0, 1, 2
 SQ_Q_INT8, SQ_Q_E4M3, SQ_Q_INT4 = 0, 1, 2
+SQ_ACT_NONE, SQ_ACT_GELU_TANH, SQ_ACT_SILU = 0, 1, 2
 SQ_GEMM_W8A8_I8, SQ_GEMM_W8A8_F8, SQ_GEMM_W4A8 = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
@@ -46,6 +47,7 @@ class ActQuantArgs(ctypes.Structure):
         ("xq_dev", ctypes.c_void_p),
         ("xq_neg_dev", ctypes.c_void_p),
         ("xq_batch_stride", ctypes.c_int64), ("xq_row_stride", ctypes.c_int64),
+        ("pre_act", ctypes.c_int32), ("reserved0", ctypes.c_int32),
     ]
 
 

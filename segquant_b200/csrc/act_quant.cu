@@ -28,6 +28,7 @@ struct ActQuantParams {
     long long xq_batch_stride, xq_row_stride;
     int num_segs;
     int uniform_seg;  // >0: every segment has this length
+    int pre_act;      // SQ_ACT_*: activation applied to x before scaling (static kernel only)
     int seg_bounds[SQ_MAX_SEGS + 1];
 };
 
@@ -119,6 +120,28 @@ struct Unit<__nv_bfloat16> {
     }
 };
 
+// Activation functions fused in front of the quantiser (the layer after a GELU / SiLU is where the reference uses
+// DualScale: segquant/pattern_detector.py:239-358).  Evaluated in fp32 with the hardware tanh / exp2 / reciprocal
+// approximations (relative error about 2^-11, a quarter of the bf16 rounding the separate torch kernel applies to
+// the same value before it is quantised).
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <int PRE>
+__device__ __forceinline__ float pre_activation(float x) {
+    if constexpr (PRE == SQ_ACT_GELU_TANH) {
+        const float inner = x * fmaf(x * x, 0.044715f * 0.7978845608028654f, 0.7978845608028654f);
+        const float hx = 0.5f * x;
+        return fmaf(hx, tanh_approx(inner), hx);
+    } else if constexpr (PRE == SQ_ACT_SILU) {
+        return x * __frcp_rn(1.0f + exp2f(-1.4426950408889634f * x));
+    } else {
+        return x;
+    }
+}
+
 template <int OUT, bool DUAL, int E>
 __device__ __forceinline__ void quant_store(const float (&x)[E], float sp, float sn, uint8_t* q, uint8_t* qn) {
     uint32_t wp[E / 4], wn[E / 4];
@@ -148,7 +171,9 @@ __device__ __forceinline__ void quant_store(const float (&x)[E], float sp, float
     }
 }
 
-template <typename T, int OUT, bool DUAL, bool SMOOTH>
+constexpr int kPreSmooth = -1;   // PRE: 0 nothing, kPreSmooth = divide by the smoothing vector, SQ_ACT_* = that activation
+
+template <typename T, int OUT, bool DUAL, int PRE>
 __global__ void __launch_bounds__(256, 4) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
     constexpr int E = Unit<T>::E;
     constexpr int U = 8;
@@ -194,9 +219,12 @@ __global__ void __launch_bounds__(256, 4) act_quant_kernel(const __grid_constant
                     sc = __ldg(sxr + s * p.sx_seg_stride);
                     if constexpr (DUAL) scn = __ldg(sxnr + s * p.sx_seg_stride);
                 }
-                if constexpr (SMOOTH) {
+                if constexpr (PRE == kPreSmooth) {
 #pragma unroll
                     for (int i = 0; i < E; ++i) v[i] = v[i] / __ldg(p.smooth + k + i);
+                } else if constexpr (PRE != 0) {
+#pragma unroll
+                    for (int i = 0; i < E; ++i) v[i] = pre_activation<PRE>(v[i]);
                 }
                 quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);
             }
@@ -321,6 +349,10 @@ static int validate(const sq_act_quant_args* a, bool dynamic) {
                "sq_quantize_act: activations quantise to int8 or e4m3 only (got kind %d)", a->out_kind);
     SQ_REQUIRE(a->num_segs >= 1 && a->num_segs <= SQ_MAX_SEGS, SQ_ERR_INVALID_ARG,
                "sq_quantize_act: num_segs %d outside [1, %d]", a->num_segs, SQ_MAX_SEGS);
+    SQ_REQUIRE(a->pre_act == SQ_ACT_NONE || a->pre_act == SQ_ACT_GELU_TANH || a->pre_act == SQ_ACT_SILU, SQ_ERR_INVALID_ARG,
+               "sq_quantize_act: unknown pre_act %d", a->pre_act);
+    SQ_REQUIRE(a->pre_act == SQ_ACT_NONE || (!dynamic && a->smooth_dev == nullptr), SQ_ERR_UNSUPPORTED,
+               "sq_quantize_act: pre_act needs static scales and no smoothing vector");
     SQ_REQUIRE(a->K % 16 == 0, SQ_ERR_ALIGNMENT, "sq_quantize_act: K (%lld) must be divisible by 16",
                static_cast<long long>(a->K));
     SQ_REQUIRE(a->K < (1ll << 30), SQ_ERR_TOO_LARGE, "sq_quantize_act: K too large");
@@ -359,6 +391,7 @@ static void fill_params(const sq_act_quant_args* a, ActQuantParams& p) {
     p.sx_batch_stride = a->sx_batch_stride; p.sx_seg_stride = a->sx_seg_stride; p.sx_row_stride = a->sx_row_stride;
     p.xq_batch_stride = a->xq_batch_stride; p.xq_row_stride = a->xq_row_stride;
     p.num_segs = a->num_segs;
+    p.pre_act = a->pre_act;
     for (int s = 0; s <= SQ_MAX_SEGS; ++s) p.seg_bounds[s] = s <= a->num_segs ? a->seg_bounds[s] : 0;
     int len = a->seg_bounds[1] - a->seg_bounds[0];
     bool uniform = len > 0;
@@ -385,13 +418,16 @@ static void launch_static(const ActQuantParams& p, bool dual, bool smooth, cudaS
         block = 64;
         grid = static_cast<int>((rows + 1) / 2 < 1 ? 1 : (rows + 1) / 2);
     }
-    if (dual) {
-        if (smooth) act_quant_kernel<T, OUT, true, true><<<grid, block, 0, st>>>(p);
-        else act_quant_kernel<T, OUT, true, false><<<grid, block, 0, st>>>(p);
-    } else {
-        if (smooth) act_quant_kernel<T, OUT, false, true><<<grid, block, 0, st>>>(p);
-        else act_quant_kernel<T, OUT, false, false><<<grid, block, 0, st>>>(p);
-    }
+#define SQ_STATIC(PRE)                                                                     \
+    do {                                                                                   \
+        if (dual) act_quant_kernel<T, OUT, true, PRE><<<grid, block, 0, st>>>(p);           \
+        else act_quant_kernel<T, OUT, false, PRE><<<grid, block, 0, st>>>(p);               \
+    } while (0)
+    if (smooth) SQ_STATIC(kPreSmooth);
+    else if (p.pre_act == SQ_ACT_GELU_TANH) SQ_STATIC(SQ_ACT_GELU_TANH);
+    else if (p.pre_act == SQ_ACT_SILU) SQ_STATIC(SQ_ACT_SILU);
+    else SQ_STATIC(0);
+#undef SQ_STATIC
 }
 
 template <typename T, int OUT>
@@ -459,9 +495,12 @@ int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_ne
 // x is read once and only bytes are written.  No counterpart in the reference.
 constexpr int kNormWords = 8;
 
-template <typename T, int OUT, bool DUAL, bool MOD>
-__global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
-                                                        const T* __restrict__ scale, long long mod_bs, float eps) {
+// NW = 128-bit words per lane the row needs (4, 6 or 8), a compile-time bound so that short rows do not pay for the
+// registers of long ones: with at most 64 registers a thread, four 256-thread CTAs stay resident per SM, and it is the
+// number of rows in flight per SM that decides how much of the HBM bandwidth a load -> reduce -> store chain reaches.
+template <typename T, int OUT, bool DUAL, int NW>
+__global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
+                                                           const T* __restrict__ scale, long long mod_bs, float eps) {
     constexpr int E = Unit<T>::E;
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
@@ -469,6 +508,7 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__
     const int words = static_cast<int>(p.K / E);
     const T* __restrict__ x = static_cast<const T*>(p.x);
     const float inv_k = 1.0f / static_cast<float>(p.K);
+    const bool mod = shift != nullptr;
 
     for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < rows;
          row += static_cast<long long>(gridDim.x) * warps_per_cta) {
@@ -477,13 +517,13 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__
         uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
 
-        uint4 raw[kNormWords];
+        uint4 raw[NW];
 #pragma unroll
-        for (int j = 0; j < kNormWords; ++j)
+        for (int j = 0; j < NW; ++j)
             if (lane + 32 * j < words) raw[j] = __ldg(reinterpret_cast<const uint4*>(xr) + lane + 32 * j);
         float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kNormWords; ++j) {
+        for (int j = 0; j < NW; ++j) {
             if (lane + 32 * j < words) {
                 float v[E];
                 Unit<T>::unpack(raw[j], v);
@@ -496,7 +536,7 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__
         const float mean = sum * inv_k;
         float sq = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kNormWords; ++j) {
+        for (int j = 0; j < NW; ++j) {
             if (lane + 32 * j < words) {
                 float v[E];
                 Unit<T>::unpack(raw[j], v);
@@ -514,13 +554,13 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const __grid_constant__
         float sc = __ldg(p.sx + b * p.sx_batch_stride);
         float scn = DUAL ? __ldg(p.sx_neg + b * p.sx_batch_stride) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < kNormWords; ++j) {
+        for (int j = 0; j < NW; ++j) {
             const int u = lane + 32 * j;
             if (u < words) {
                 const int k = u * E;
                 float v[E];
                 Unit<T>::unpack(raw[j], v);
-                if constexpr (MOD) {
+                if (mod) {
                     float sh[E], scl[E];
                     Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(shift + b * mod_bs) + u), sh);
                     Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(scale + b * mod_bs) + u), scl);
@@ -554,13 +594,16 @@ static void launch_norm(const ActQuantParams& p, bool dual, const void* shift, c
     }
     const T* sh = static_cast<const T*>(shift);
     const T* sc = static_cast<const T*>(scale);
-    if (shift != nullptr) {
-        if (dual) norm_quant_kernel<T, OUT, true, true><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
-        else norm_quant_kernel<T, OUT, false, true><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
-    } else {
-        if (dual) norm_quant_kernel<T, OUT, true, false><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
-        else norm_quant_kernel<T, OUT, false, false><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);
-    }
+    const long long per_lane = (p.K / Unit<T>::E + 31) / 32;
+#define SQ_NORM(NW)                                                                                \
+    do {                                                                                           \
+        if (dual) norm_quant_kernel<T, OUT, true, NW><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);  \
+        else norm_quant_kernel<T, OUT, false, NW><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);      \
+    } while (0)
+    if (per_lane <= 4) SQ_NORM(4);
+    else if (per_lane <= 6) SQ_NORM(6);
+    else SQ_NORM(kNormWords);
+#undef SQ_NORM
 }
 
 int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st) {
@@ -568,8 +611,8 @@ int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void*
     if (rc != SQ_OK) return rc;
     if (a->batch * a->M * a->K == 0) return SQ_OK;
     SQ_REQUIRE((shift == nullptr) == (scale == nullptr), SQ_ERR_INVALID_ARG, "sq_norm_quantize_act: shift and scale go together");
-    SQ_REQUIRE(a->sx_row_stride == 0 && a->smooth_dev == nullptr, SQ_ERR_UNSUPPORTED,
-               "sq_norm_quantize_act: static per-segment scales only, no smoothing vector");
+    SQ_REQUIRE(a->sx_row_stride == 0 && a->smooth_dev == nullptr && a->pre_act == SQ_ACT_NONE, SQ_ERR_UNSUPPORTED,
+               "sq_norm_quantize_act: static per-segment scales only, no smoothing vector, no pre_act");
     const long long esz = a->x_dtype == SQ_F32 ? 4 : 2;
     const long long words = a->K * esz / 16;
     SQ_REQUIRE((a->K * esz) % 16 == 0 && words <= 32 * kNormWords, SQ_ERR_UNSUPPORTED,

@@ -50,8 +50,27 @@ class QLinear:
         self.layer.finish_calibrate()
         self.w = None   # the float weight is no longer needed
 
-    def __call__(self, x, out=None):
-        return self.layer(x, out=out)
+    fuse_activation = True     # class-wide switch: False runs the activation in front of a layer as its own torch kernel
+
+    def __call__(self, x, out=None, pre_act=None):
+        """pre_act ("gelu_tanh" / "silu"): the layer's input is pre_act(x); the quantise kernel evaluates it on the fly."""
+        if pre_act is None:
+            return self.layer(x, out=out)
+        if self.fuse_activation:
+            try:
+                bounds, sx, sx_neg, kind = self.layer.optimizer.input_quant_params()
+            except RuntimeError:
+                bounds = None
+            if bounds is not None:
+                from . import ops
+                x3 = x if x.dim() == 3 else x.reshape(1, -1, x.shape[-1])
+                xq, xq_neg = ops.quantize_act(x3, bounds, sx, sx_neg, kind, shared_scales=True, pre_act=pre_act)
+                y = self.layer.forward_quantized(xq, xq_neg, out=out, out_dtype=x.dtype)
+                return y if out is not None else y.reshape(*x.shape[:-1], self.out_f)
+        return self.layer(_ACTS[pre_act](x), out=out)
+
+
+_ACTS = {"gelu_tanh": lambda t: F.gelu(t, approximate="tanh"), "silu": F.silu}
 
 
 def _layer_norm(x):
@@ -132,9 +151,9 @@ class JointBlock:
         return [getattr(self, n) for n in names]
 
     def forward(self, img, txt, c_act, call, norm_call):
-        """c_act = SiLU(conditioning) [B, H]; call(layer, x, out=None) runs either the calibration or the quantized
-        linear, writing into `out` when given; norm_call(layers, x, shift, scale, outs) runs `layers` on the
-        normalised and modulated x."""
+        """c_act = SiLU(conditioning) [B, H]; call(layer, x, out=None, pre_act=None) runs either the calibration or the
+        quantized linear on pre_act(x), writing into `out` when given; norm_call(layers, x, shift, scale, outs) runs
+        `layers` on the normalised and modulated x."""
         B, Ti, H = img.shape
         Tt = txt.shape[1]
         m = call(self.norm1, c_act).chunk(6, dim=-1)                         # shift, scale, gate (msa), shift, scale, gate (mlp)
@@ -153,11 +172,11 @@ class JointBlock:
 
         img = torch.addcmul(img, m[2].unsqueeze(1), call(self.to_out, a_img))
         h = norm_call((self.ff0,), img, m[3], m[4])[0]
-        img = torch.addcmul(img, m[5].unsqueeze(1), call(self.ff2, F.gelu(h, approximate="tanh")))
+        img = torch.addcmul(img, m[5].unsqueeze(1), call(self.ff2, h, pre_act="gelu_tanh"))
         if not self.last:
             txt = torch.addcmul(txt, mc[2].unsqueeze(1), call(self.to_add_out, a_txt))
             h = norm_call((self.ffc0,), txt, mc[3], mc[4])[0]
-            txt = torch.addcmul(txt, mc[5].unsqueeze(1), call(self.ffc2, F.gelu(h, approximate="tanh")))
+            txt = torch.addcmul(txt, mc[5].unsqueeze(1), call(self.ffc2, h, pre_act="gelu_tanh"))
         return img, txt
 
 
@@ -187,8 +206,8 @@ class SyntheticMMDiT:
     def _forward(self, latents, text, pooled, timestep, call, norm_call):
         """latents [B, Ti, H] (already patch-embedded: the patch embedder is a Conv2d, never quantised),
         text [B, Tt, 4096], pooled [B, 2048], timestep [B]."""
-        temb = call(self.t_lin2, F.silu(call(self.t_lin1, _timestep_embedding(timestep).to(self.dtype))))
-        pemb = call(self.p_lin2, F.silu(call(self.p_lin1, pooled)))
+        temb = call(self.t_lin2, call(self.t_lin1, _timestep_embedding(timestep).to(self.dtype)), pre_act="silu")
+        pemb = call(self.p_lin2, call(self.p_lin1, pooled), pre_act="silu")
         c_act = F.silu(temb + pemb)
         txt = call(self.context_embedder, text)
         img = latents
@@ -200,8 +219,8 @@ class SyntheticMMDiT:
     def calibrate(self, latents, text, pooled, timestep):
         """One forward of the float model; every linear records its input range and is then quantized."""
         with torch.no_grad():
-            def calib(layer, x, out=None):
-                y = layer.calibrate_forward(x)
+            def calib(layer, x, out=None, pre_act=None):
+                y = layer.calibrate_forward(x if pre_act is None else _ACTS[pre_act](x))
                 if out is not None:
                     out.copy_(y)
                     return out
@@ -222,7 +241,8 @@ class SyntheticMMDiT:
             def unfused(layers, x, shift, scale, outs=None):
                 n = _modulate(x, shift, scale)
                 return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))]
-            return self._forward(latents, text, pooled, timestep, lambda layer, x, out=None: layer(x, out=out),
+            return self._forward(latents, text, pooled, timestep,
+                                 lambda layer, x, out=None, pre_act=None: layer(x, out=out, pre_act=pre_act),
                                  self.fused_norm or unfused)
 
     def linear_ops(self, batch):

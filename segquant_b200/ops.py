@@ -60,15 +60,21 @@ def uniform_bounds(K, segments):
 # ---------------------------------------------------------------------------------------------
 # activation quantise
 # ---------------------------------------------------------------------------------------------
+PRE_ACTS = {None: L.SQ_ACT_NONE, "gelu_tanh": L.SQ_ACT_GELU_TANH, "silu": L.SQ_ACT_SILU}
+
+
 def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=False, smooth=None,
-                 out=None, out_neg=None, shared_scales=False):
+                 out=None, out_neg=None, shared_scales=False, pre_act=None):
     """x: (B, M, K) view (any batch / row stride, K contiguous) or (M, K).
 
     sx: (B*S,) or (B*S*M,) float32 in (batch, segment[, row]) order, or (S,) used by every batch
     when shared_scales is set.  Returns (xq, xq_neg) uint8 tensors of shape (B, M, K) (contiguous).
-    `bounds` cuts K into the S segments."""
+    `bounds` cuts K into the S segments.  pre_act ("gelu_tanh" / "silu") applies that activation to x, in fp32,
+    inside the kernel, so the activation in front of a layer costs no pass over memory of its own."""
     global launch_count
     _need_cuda(x, sx, sx_neg)
+    if pre_act not in PRE_ACTS:
+        raise ValueError(f"pre_act must be one of {list(PRE_ACTS)}")
     if x.dim() == 2:
         x = x.unsqueeze(0)
     if x.stride(-1) != 1:
@@ -97,6 +103,7 @@ def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=Fal
     if shared_scales:
         a.sx_batch_stride = 0
     a.smooth_dev = smooth.data_ptr() if smooth is not None else None
+    a.pre_act = PRE_ACTS[pre_act]
     a.xq_dev = xq.data_ptr()
     a.xq_neg_dev = xqn.data_ptr() if dual else None
     a.xq_batch_stride, a.xq_row_stride = M * K, K

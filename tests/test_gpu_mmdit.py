@@ -105,19 +105,61 @@ def test_norm_quantize_act_rejects_long_rows():
         ops.norm_quantize_act(x, [0, 4096], sx)
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("kind_name,dual", [("int8", True), ("e4m3", True), ("int8", False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quantize_act_with_fused_activation(act, kind_name, dual, dtype):
+    """quantize_act(pre_act=...) against the activation evaluated by torch in fp32 followed by the plain quantise
+    kernel: the hardware tanh / exp2 approximations move a value by about 2^-11 of itself, so a small fraction of
+    codes may land on the neighbouring step, none further."""
+    from segquant_b200 import _lib as L, ops
+    kind = L.SQ_Q_INT8 if kind_name == "int8" else L.SQ_Q_E4M3
+    torch.manual_seed(5)
+    B, T, K = 2, 130, 1024
+    x = (torch.randn(B, T, K, device="cuda") * 2.5).to(dtype)
+    fn = (lambda t: torch.nn.functional.gelu(t, approximate="tanh")) if act == "gelu_tanh" else torch.nn.functional.silu
+    y = fn(x.float())
+    qmax = 127.0 if kind == L.SQ_Q_INT8 else 448.0
+    bounds = [0, 512, K]
+    sx = qmax / torch.stack([y[..., :512].max(), y[..., 512:].max()])
+    sxn = (qmax / torch.stack([y[..., :512].min().abs(), y[..., 512:].min().abs()])) if dual else None
+    q, qn = ops.quantize_act(x, bounds, sx, sxn, kind, shared_scales=True, pre_act=act)
+    rq, rqn = ops.quantize_act(y, bounds, sx, sxn, kind, shared_scales=True)
+    for got, want in ((q, rq), (qn, rqn)):
+        if want is None:
+            assert got is None
+            continue
+        diff = got != want
+        assert diff.float().mean() < 0.03
+        g, w = _as_values(got, kind)[diff], _as_values(want, kind)[diff]
+        if kind == L.SQ_Q_INT8:
+            assert torch.all((g - w).abs() <= 1)
+        else:
+            assert torch.all((g - w).abs() <= 0.126 * torch.maximum(g.abs(), w.abs()) + 2 ** -9)
+    with pytest.raises(Exception):      # a fused activation cannot be combined with the smoothing vector
+        ops.quantize_act(x, bounds, sx, sxn, kind, shared_scales=True, pre_act=act, smooth=torch.ones(K, device="cuda"))
+    assert ops.device_status() == 0
+
+
 def test_fused_norm_step_matches_unfused_step():
-    """The step with one normalise + modulate + quantise kernel per norm against the same model running torch's
-    layer_norm and modulation in bf16 followed by the quantise kernel: same weights and scales, so the only
-    difference is that the fused kernel does not round the normalised tensor to bf16 before quantising."""
+    """The step with one normalise + modulate + quantise kernel per norm and the GELU / SiLU evaluated inside the
+    quantise kernel, against the same model running torch's layer_norm, modulation and activations in bf16 followed
+    by the plain quantise kernel: same weights and scales, so the only difference is that the fused kernels do not
+    round the intermediate tensor to bf16 before quantising."""
     from segquant_b200.mmdit import SyntheticMMDiT, synthetic_inputs
     model = SyntheticMMDiT("cuda", blocks=2, hidden=256, heads=4, img_tokens=256, txt_tokens=40, seed=0)
     inp = synthetic_inputs(2, "cuda", img_tokens=256, txt_tokens=40, hidden=256, seed=1)
     model.calibrate(*inp)
     fused = model(*inp).float()
     assert any(v is not None for v in model.fused_norm.plan.values())       # the fused kernel really ran
+    from segquant_b200.mmdit import QLinear
     keep, model.fused_norm = model.fused_norm, None
-    plain = model(*inp).float()
-    model.fused_norm = keep
+    QLinear.fuse_activation = False
+    try:
+        plain = model(*inp).float()
+    finally:
+        model.fused_norm = keep
+        QLinear.fuse_activation = True
     cos = torch.nn.functional.cosine_similarity(fused.flatten(), plain.flatten(), dim=0)
     assert cos > 0.999
     from segquant_b200 import ops
