@@ -491,8 +491,18 @@ int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_ne
 // quantisation of act_quant_kernel.  In a DiT block this is what sits between the residual stream and the q / k / v
 // and MLP projections: three torch kernels (layer_norm, the modulation, the quantise) that each read and write the
 // whole [tokens, hidden] tensor.  One warp owns a row and keeps it in registers as raw 128-bit words (at most
-// kNormWords per lane): mean, variance (two passes over the registers, like torch), normalise, modulate, quantise;
-// x is read once and only bytes are written.  No counterpart in the reference.
+// kNormWords per lane); x is read once and only bytes are written.  No counterpart in the reference.
+//
+// Rows this short make the kernel instruction-bound before it is HBM-bound (at 6.5 TB/s and 3 bytes per element the
+// SMs have about a dozen issue slots per element), so the arithmetic is trimmed to fit:
+//  * statistics in ONE pass over the registers, as sums of d = x - pivot and d * d, pivot = mean of 32 samples of the
+//    row (one per lane): var = E[d^2] - E[d]^2 loses nothing to cancellation because |pivot - mean| is a fraction
+//    of the standard deviation;
+//  * the per-column factors do not depend on the row: each CTA keeps a = (1 + scale) and c = shift of its batch in
+//    shared memory as fp32 (for the single-scale case already multiplied by the segment's quantisation scale), and a
+//    CTA's rows never straddle two batches, so a row costs two shared loads per four elements instead of two global
+//    loads, two unpacks and an add;
+//  * all fp32 arithmetic on pairs (fma.rn.f32x2).
 constexpr int kNormWords = 8;
 
 // NW = 128-bit words per lane the row needs (4, 6 or 8), a compile-time bound so that short rows do not pay for the
@@ -500,19 +510,44 @@ constexpr int kNormWords = 8;
 // number of rows in flight per SM that decides how much of the HBM bandwidth a load -> reduce -> store chain reaches.
 template <typename T, int OUT, bool DUAL, int NW>
 __global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
-                                                           const T* __restrict__ scale, long long mod_bs, float eps) {
+                                                                          const T* __restrict__ scale, long long mod_bs, float eps) {
     constexpr int E = Unit<T>::E;
-    const int lane = threadIdx.x & 31;
-    const int warps_per_cta = blockDim.x >> 5;
-    const long long rows = p.batch * p.M;
+    constexpr int H = E / 4;                       // float4 pieces per 128-bit word of x
+    constexpr int kMaxWords = 32 * kNormWords;
+    __shared__ float4 tab_a[H][kMaxWords];         // (1 + scale[k]) [* sx[seg(k)] unless DUAL]; lane stride 16 bytes
+    __shared__ float4 tab_c[H][kMaxWords];         // shift[k] [* sx[seg(k)] unless DUAL]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wpc = blockDim.x >> 5;
     const int words = static_cast<int>(p.K / E);
     const T* __restrict__ x = static_cast<const T*>(p.x);
     const float inv_k = 1.0f / static_cast<float>(p.K);
-    const bool mod = shift != nullptr;
+    const float inv_samples = 1.0f / static_cast<float>(words < 32 ? words : 32);
 
-    for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < rows;
-         row += static_cast<long long>(gridDim.x) * warps_per_cta) {
-        const long long b = row / p.M, r = row - b * p.M;
+    // work item = wpc consecutive rows of ONE batch, so the table in shared memory serves every warp of the CTA
+    const long long blocks_per_batch = (p.M + wpc - 1) / wpc;
+    const long long nblk = p.batch * blocks_per_batch;
+    long long tab_batch = -1;
+    for (long long item = blockIdx.x; item < nblk; item += gridDim.x) {
+        const long long b = item / blocks_per_batch;
+        const long long r = (item - b * blocks_per_batch) * wpc + warp;
+        if (b != tab_batch) {                      // uniform over the CTA
+            __syncthreads();
+            for (int k = threadIdx.x * 4; k < p.K; k += blockDim.x * 4) {      // segment bounds are multiples of 16
+                const float f = DUAL ? 1.0f : __ldg(p.sx + b * p.sx_batch_stride + find_segment(p, k) * p.sx_seg_stride);
+                float a[4], c[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    a[i] = shift != nullptr ? (1.0f + to_float<T>(scale[b * mod_bs + k + i])) * f : f;
+                    c[i] = shift != nullptr ? to_float<T>(shift[b * mod_bs + k + i]) * f : 0.0f;
+                }
+                tab_a[(k % E) / 4][k / E] = make_float4(a[0], a[1], a[2], a[3]);
+                tab_c[(k % E) / 4][k / E] = make_float4(c[0], c[1], c[2], c[3]);
+            }
+            tab_batch = b;
+            __syncthreads();
+        }
+        if (r >= p.M) continue;                    // warp-uniform; every warp still runs every iteration of the loop
+
         const T* xr = x + b * p.x_batch_stride + r * p.x_row_stride;
         uint8_t* qr = p.xq + b * p.xq_batch_stride + r * p.xq_row_stride;
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
@@ -521,38 +556,51 @@ __global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const 
 #pragma unroll
         for (int j = 0; j < NW; ++j)
             if (lane + 32 * j < words) raw[j] = __ldg(reinterpret_cast<const uint4*>(xr) + lane + 32 * j);
-        float sum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NW; ++j) {
-            if (lane + 32 * j < words) {
-                float v[E];
-                Unit<T>::unpack(raw[j], v);
-#pragma unroll
-                for (int i = 0; i < E; ++i) sum += v[i];
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float mean = sum * inv_k;
-        float sq = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NW; ++j) {
-            if (lane + 32 * j < words) {
-                float v[E];
-                Unit<T>::unpack(raw[j], v);
-#pragma unroll
-                for (int i = 0; i < E; ++i) { const float d = v[i] - mean; sq = fmaf(d, d, sq); }
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        const float rstd = 1.0f / sqrtf(sq * inv_k + eps);
 
-        // segment cursor: this lane's k only grows with j
+        float pivot = 0.0f;
+        if (lane < words) {
+            float v[E];
+            Unit<T>::unpack(raw[0], v);
+            pivot = v[0];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pivot += __shfl_xor_sync(0xffffffffu, pivot, o);
+        pivot *= inv_samples;
+
+        const float2 neg_pivot = make_float2(-pivot, -pivot);
+        float2 s1 = make_float2(0.0f, 0.0f), s2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < NW; ++j) {
+            if (lane + 32 * j < words) {
+                float v[E];
+                Unit<T>::unpack(raw[j], v);
+#pragma unroll
+                for (int i = 0; i < E; i += 2) {
+                    const float2 d = __fadd2_rn(make_float2(v[i], v[i + 1]), neg_pivot);
+                    s1 = __fadd2_rn(s1, d);
+                    s2 = __ffma2_rn(d, d, s2);
+                }
+            }
+        }
+        float sum = s1.x + s1.y, sq = s2.x + s2.y;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        }
+        const float md = sum * inv_k;              // mean - pivot
+        const float rstd = 1.0f / sqrtf(fmaxf(sq * inv_k - md * md, 0.0f) + eps);
+        const float nmr = -(pivot + md) * rstd;
+        const float2 rstd2 = make_float2(rstd, rstd), nmr2 = make_float2(nmr, nmr);
+
+        // DualScale: the quantisation scale depends on the sign, so it is applied per element; this lane's k only grows
         int s = 0;
         int next_bound = p.seg_bounds[1];
-        float sc = __ldg(p.sx + b * p.sx_batch_stride);
-        float scn = DUAL ? __ldg(p.sx_neg + b * p.sx_batch_stride) : 0.0f;
+        float sc = 1.0f, scn = 0.0f;
+        if constexpr (DUAL) {
+            sc = __ldg(p.sx + b * p.sx_batch_stride);
+            scn = __ldg(p.sx_neg + b * p.sx_batch_stride);
+        }
 #pragma unroll
         for (int j = 0; j < NW; ++j) {
             const int u = lane + 32 * j;
@@ -560,23 +608,24 @@ __global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const 
                 const int k = u * E;
                 float v[E];
                 Unit<T>::unpack(raw[j], v);
-                if (mod) {
-                    float sh[E], scl[E];
-                    Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(shift + b * mod_bs) + u), sh);
-                    Unit<T>::unpack(__ldg(reinterpret_cast<const uint4*>(scale + b * mod_bs) + u), scl);
 #pragma unroll
-                    for (int i = 0; i < E; ++i) v[i] = fmaf((v[i] - mean) * rstd, 1.0f + scl[i], sh[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < E; ++i) v[i] = (v[i] - mean) * rstd;
+                for (int h = 0; h < H; ++h) {
+                    const float4 a = tab_a[h][u], c = tab_c[h][u];
+                    const float2 n0 = __ffma2_rn(make_float2(v[4 * h], v[4 * h + 1]), rstd2, nmr2);
+                    const float2 n1 = __ffma2_rn(make_float2(v[4 * h + 2], v[4 * h + 3]), rstd2, nmr2);
+                    const float2 o0 = __ffma2_rn(n0, make_float2(a.x, a.y), make_float2(c.x, c.y));
+                    const float2 o1 = __ffma2_rn(n1, make_float2(a.z, a.w), make_float2(c.z, c.w));
+                    v[4 * h] = o0.x; v[4 * h + 1] = o0.y; v[4 * h + 2] = o1.x; v[4 * h + 3] = o1.y;
                 }
-                while (k >= next_bound) {
-                    ++s;
-                    next_bound = p.seg_bounds[s + 1];
-                    sc = __ldg(p.sx + b * p.sx_batch_stride + s * p.sx_seg_stride);
-                    if constexpr (DUAL) scn = __ldg(p.sx_neg + b * p.sx_batch_stride + s * p.sx_seg_stride);
+                if constexpr (DUAL) {
+                    while (k >= next_bound) {
+                        ++s;
+                        next_bound = p.seg_bounds[s + 1];
+                        sc = __ldg(p.sx + b * p.sx_batch_stride + s * p.sx_seg_stride);
+                        scn = __ldg(p.sx_neg + b * p.sx_batch_stride + s * p.sx_seg_stride);
+                    }
                 }
-                quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);
+                quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);   // single scale: sc == 1, folded into the table
             }
         }
     }
