@@ -121,25 +121,36 @@ struct Unit<__nv_bfloat16> {
 };
 
 // Activation functions fused in front of the quantiser (the layer after a GELU / SiLU is where the reference uses
-// DualScale: segquant/pattern_detector.py:239-358).  Evaluated in fp32 with the hardware tanh / exp2 / reciprocal
-// approximations (relative error about 2^-11, a quarter of the bf16 rounding the separate torch kernel applies to
-// the same value before it is quantised).
-__device__ __forceinline__ float tanh_approx(float x) {
+// DualScale: segquant/pattern_detector.py:239-358).  Both are written as x * sigmoid(g(x)) = x / (1 + 2^(-log2(e) g(x))):
+// tanh-GELU has g = 2 sqrt(2/pi) (x + 0.044715 x^3) since 0.5 (1 + tanh(u)) = sigmoid(2u), SiLU has g = x.  That form
+// keeps the RELATIVE error small on the negative tail, where 0.5 x (1 + tanh(u)) cancels and where DualScale spends its
+// second scale; ex2.approx / rcp.approx are good to 2^-22, far below the bf16 rounding the separate torch kernel
+// applies.  Evaluated on pairs (f32x2) because the kernel is issue-bound once an activation is added.
+__device__ __forceinline__ float ex2_approx(float x) {
     float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 template <int PRE>
-__device__ __forceinline__ float pre_activation(float x) {
+__device__ __forceinline__ void pre_activation2(float& a, float& b) {
+    const float2 x = make_float2(a, b);
+    float2 arg;                                    // -log2(e) * g(x)
     if constexpr (PRE == SQ_ACT_GELU_TANH) {
-        const float inner = x * fmaf(x * x, 0.044715f * 0.7978845608028654f, 0.7978845608028654f);
-        const float hx = 0.5f * x;
-        return fmaf(hx, tanh_approx(inner), hx);
-    } else if constexpr (PRE == SQ_ACT_SILU) {
-        return x * __frcp_rn(1.0f + exp2f(-1.4426950408889634f * x));
+        constexpr float c0 = -2.0f * 1.4426950408889634f * 0.7978845608028654f;
+        constexpr float c1 = c0 * 0.044715f;
+        arg = __fmul2_rn(x, __ffma2_rn(__fmul2_rn(x, x), make_float2(c1, c1), make_float2(c0, c0)));
     } else {
-        return x;
+        arg = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
     }
+    const float2 den = __fadd2_rn(make_float2(ex2_approx(arg.x), ex2_approx(arg.y)), make_float2(1.0f, 1.0f));
+    const float2 r = __fmul2_rn(x, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+    a = r.x;
+    b = r.y;
 }
 
 template <int OUT, bool DUAL, int E>
@@ -224,7 +235,7 @@ __global__ void __launch_bounds__(256, 4) act_quant_kernel(const __grid_constant
                     for (int i = 0; i < E; ++i) v[i] = v[i] / __ldg(p.smooth + k + i);
                 } else if constexpr (PRE != 0) {
 #pragma unroll
-                    for (int i = 0; i < E; ++i) v[i] = pre_activation<PRE>(v[i]);
+                    for (int i = 0; i < E; i += 2) pre_activation2<PRE>(v[i], v[i + 1]);
                 }
                 quant_store<OUT, DUAL, E>(v, sc, scn, qr + k, DUAL ? qnr + k : nullptr);
             }

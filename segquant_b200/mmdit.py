@@ -262,7 +262,7 @@ class SyntheticMMDiT:
 
 
 class GraphedStep:
-    """The quantized denoise step captured once into a CUDA graph and replayed: a step is ~2000 small
+    """The quantized denoise step captured once into a CUDA graph and replayed: a step is well over a thousand small
     launches (two per linear plus the bf16 glue), so launch overhead dominates when they are issued one by
     one from Python.  Inputs are copied into static buffers; the output tensor is reused by every replay."""
 

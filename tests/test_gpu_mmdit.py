@@ -110,8 +110,8 @@ def test_norm_quantize_act_rejects_long_rows():
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_quantize_act_with_fused_activation(act, kind_name, dual, dtype):
     """quantize_act(pre_act=...) against the activation evaluated by torch in fp32 followed by the plain quantise
-    kernel: the hardware tanh / exp2 approximations move a value by about 2^-11 of itself, so a small fraction of
-    codes may land on the neighbouring step, none further."""
+    kernel: the hardware exp2 / reciprocal approximations move a value by about 2^-22 of itself, so a very small
+    fraction of codes may land on the neighbouring step, none further."""
     from segquant_b200 import _lib as L, ops
     kind = L.SQ_Q_INT8 if kind_name == "int8" else L.SQ_Q_E4M3
     torch.manual_seed(5)
@@ -129,9 +129,10 @@ def test_quantize_act_with_fused_activation(act, kind_name, dual, dtype):
         if want is None:
             assert got is None
             continue
-        diff = got != want
-        assert diff.float().mean() < 0.03
-        g, w = _as_values(got, kind)[diff], _as_values(want, kind)[diff]
+        gv, wv = _as_values(got, kind), _as_values(want, kind)
+        diff = gv != wv                                  # by value: an e4m3 -0 (a tiny negative input) equals +0
+        assert diff.float().mean() < 0.005
+        g, w = gv[diff], wv[diff]
         if kind == L.SQ_Q_INT8:
             assert torch.all((g - w).abs() <= 1)
         else:
