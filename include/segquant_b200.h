@@ -139,6 +139,28 @@ int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev,
 int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev,
                          int64_t mod_batch_stride, float eps, sq_stream_t stream);
 
+/* ---- gated residual add (no counterpart in the reference) ---------------------------------------
+ * out[b, r, :] = x[b, r, :] + gate[b, :] * y[b, r, :] on 16-bit tensors: the residual-stream update of a DiT block
+ * (y = output of a quantised linear, gate = a chunk of the adaLN modulation).  Bit-identical to torch.addcmul; exists
+ * because torch runs a gate broadcast over the tokens through its strided-iterator kernel at a fraction of the copy
+ * bandwidth.  out may alias x.  K and all strides (elements) are multiples of 8, pointers 16-byte aligned.
+ */
+typedef struct sq_gated_residual_args {
+    const void* x_dev;
+    const void* gate_dev;
+    const void* y_dev;
+    void* out_dev;
+    int32_t dtype;             /* SQ_F16 / SQ_BF16 */
+    int32_t reserved0;
+    int64_t batch, M, K;
+    int64_t x_batch_stride, x_row_stride;
+    int64_t y_batch_stride, y_row_stride;
+    int64_t out_batch_stride, out_row_stride;
+    int64_t gate_batch_stride;
+} sq_gated_residual_args;
+
+int sq_gated_residual(const sq_gated_residual_args* args, sq_stream_t stream);
+
 /* ---- weight quantise / pack ---------------------------------------------------------------
  * Replaces real_quantized_quantize_weights<T> (real_gemm.cu:538-638; pybind names in
  * seg_utils.h:82-120).  w is [N, K] contiguous.  scale_mode 0: one scalar `scale_scalar`

@@ -23,6 +23,7 @@ void clear_error() { g_err[0] = 0; }
 int quantize_act(const sq_act_quant_args* a, cudaStream_t st);
 int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_neg_out, cudaStream_t st);
 int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st);
+int gated_residual(const sq_gated_residual_args* a, cudaStream_t st);
 int quantize_weight(const void* w, int w_dtype, long long N, long long K, int scale_mode, float scale_scalar,
                     const float* scale, int group_size, int out_kind, void* out, cudaStream_t st);
 int unpack_int4(const void* packed, void* out, long long numel, cudaStream_t st);
@@ -72,6 +73,11 @@ int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, c
                          float eps, sq_stream_t stream) {
     sq::clear_error();
     return sq::norm_quantize_act(args, shift_dev, scale_dev, mod_batch_stride, eps, static_cast<cudaStream_t>(stream));
+}
+
+int sq_gated_residual(const sq_gated_residual_args* args, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::gated_residual(args, static_cast<cudaStream_t>(stream));
 }
 
 int sq_quantize_weight(const void* w_dev, int32_t w_dtype, int64_t N, int64_t K, int32_t scale_mode, float scale_scalar,

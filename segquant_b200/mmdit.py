@@ -83,6 +83,15 @@ def _modulate(x, shift, scale):
     return n if shift is None else torch.addcmul(shift.unsqueeze(1), n, 1 + scale.unsqueeze(1))
 
 
+def _gated_add(x, gate, y):
+    """x + gate[:, None, :] * y, the residual-stream update; on the GPU one vectorised kernel of this library (bit-identical
+    to torch.addcmul, which takes a slow strided path for the broadcast gate)."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.stride(-1) == 1 and y.stride(-1) == 1:
+        from . import ops
+        return ops.gated_residual(x, gate, y)
+    return torch.addcmul(x, gate.unsqueeze(1), y)
+
+
 class FusedNorm:
     """Runs `layers` on LayerNorm(x) * (1 + scale) + shift.  Linears that were calibrated on the same tensor hold the
     same static input scale, so the normalisation, the modulation and the quantisation are done once, in one kernel that
@@ -170,13 +179,13 @@ class JointBlock:
         a = F.scaled_dot_product_attention(heads(qkv[0]), heads(qkv[1]), heads(qkv[2])).transpose(1, 2).reshape(B, Ti + Tt, H)
         a_img, a_txt = a[:, :Ti], a[:, Ti:]
 
-        img = torch.addcmul(img, m[2].unsqueeze(1), call(self.to_out, a_img))
+        img = _gated_add(img, m[2], call(self.to_out, a_img))
         h = norm_call((self.ff0,), img, m[3], m[4])[0]
-        img = torch.addcmul(img, m[5].unsqueeze(1), call(self.ff2, h, pre_act="gelu_tanh"))
+        img = _gated_add(img, m[5], call(self.ff2, h, pre_act="gelu_tanh"))
         if not self.last:
-            txt = torch.addcmul(txt, mc[2].unsqueeze(1), call(self.to_add_out, a_txt))
+            txt = _gated_add(txt, mc[2], call(self.to_add_out, a_txt))
             h = norm_call((self.ffc0,), txt, mc[3], mc[4])[0]
-            txt = torch.addcmul(txt, mc[5].unsqueeze(1), call(self.ffc2, h, pre_act="gelu_tanh"))
+            txt = _gated_add(txt, mc[5], call(self.ffc2, h, pre_act="gelu_tanh"))
         return img, txt
 
 

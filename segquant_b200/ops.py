@@ -155,6 +155,35 @@ def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=No
     return xq, xqn
 
 
+def gated_residual(x, gate, y, out=None):
+    """x + gate.unsqueeze(1) * y for 16-bit (B, T, K) tensors x, y (contiguous rows) and a (B, K) gate, bit-identical to
+    torch.addcmul; `out` may be x itself."""
+    global launch_count
+    _need_cuda(x, gate, y)
+    if x.dim() != 3 or y.shape != x.shape or gate.shape != (x.shape[0], x.shape[2]) or x.stride(-1) != 1 or y.stride(-1) != 1:
+        raise ValueError("gated_residual needs (B, T, K) tensors x, y with contiguous rows and a (B, K) gate")
+    if not (x.dtype == y.dtype == gate.dtype) or x.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("gated_residual: x, gate and y must share a 16-bit dtype")
+    if gate.stride(-1) != 1:
+        gate = gate.contiguous()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device) if out is None else out
+    if x.numel() == 0:
+        return out
+    B, M, K = x.shape
+    a = L.GatedResidualArgs()
+    a.x_dev, a.gate_dev, a.y_dev, a.out_dev = x.data_ptr(), gate.data_ptr(), y.data_ptr(), out.data_ptr()
+    a.dtype = _dt(x)
+    a.batch, a.M, a.K = B, M, K
+    a.x_batch_stride, a.x_row_stride = (x.stride(0) if B > 1 else 0), x.stride(1)
+    a.y_batch_stride, a.y_row_stride = (y.stride(0) if B > 1 else 0), y.stride(1)
+    a.out_batch_stride, a.out_row_stride = (out.stride(0) if B > 1 else 0), out.stride(1)
+    a.gate_batch_stride = gate.stride(0) if B > 1 else 0
+    with torch.cuda.device(x.device):
+        L.check(L.load().sq_gated_residual(ctypes.byref(a), _stream(x)), "sq_gated_residual")
+    launch_count += 1
+    return out
+
+
 def quantize_act_dynamic(x, bounds, out_kind=L.SQ_Q_INT8, dual=False):
     """Per-token dynamic scales + quantise in one launch.  x (M, K).  Returns
     (xq, xq_neg, sx, sx_neg) with scales of shape (S, M)."""

@@ -39,12 +39,16 @@ def test_struct_layout_matches_header(tmp_path):
     """Compile a tiny C program against the header and compare sizeof / offsetof with ctypes."""
     fields_a = [f[0] for f in L.ActQuantArgs._fields_]
     fields_g = [f[0] for f in L.GemmArgs._fields_]
+    fields_r = [f[0] for f in L.GatedResidualArgs._fields_]
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){",
              'printf("A %zu\\n", sizeof(sq_act_quant_args));', 'printf("G %zu\\n", sizeof(sq_gemm_args));']
     for f in fields_a:
         lines.append(f'printf("A.{f} %zu\\n", offsetof(sq_act_quant_args, {f}));')
     for f in fields_g:
         lines.append(f'printf("G.{f} %zu\\n", offsetof(sq_gemm_args, {f}));')
+    lines.append('printf("R %zu\\n", sizeof(sq_gated_residual_args));')
+    for f in fields_r:
+        lines.append(f'printf("R.{f} %zu\\n", offsetof(sq_gated_residual_args, {f}));')
     lines.append("return 0;}")
     src = tmp_path / "layout.c"
     src.write_text("\n".join(lines))
@@ -54,6 +58,9 @@ def test_struct_layout_matches_header(tmp_path):
     got = dict(l.split() for l in out if l)
     assert int(got["A"]) == ctypes.sizeof(L.ActQuantArgs)
     assert int(got["G"]) == ctypes.sizeof(L.GemmArgs)
+    assert int(got["R"]) == ctypes.sizeof(L.GatedResidualArgs)
+    for f in fields_r:
+        assert int(got[f"R.{f}"]) == getattr(L.GatedResidualArgs, f).offset, f
     for f in fields_a:
         assert int(got[f"A.{f}"]) == getattr(L.ActQuantArgs, f).offset, f
     for f in fields_g:
@@ -64,6 +71,13 @@ def test_argument_errors_are_status_codes(native_lib):
     assert native_lib.sq_gemm(None, None) == L.SQ_ERR_INVALID_ARG
     assert b"NULL" in native_lib.sq_last_error()
     assert native_lib.sq_quantize_act(None, None) == L.SQ_ERR_INVALID_ARG
+    assert native_lib.sq_gated_residual(None, None) == L.SQ_ERR_INVALID_ARG
+    r = L.GatedResidualArgs()
+    r.batch, r.M, r.K, r.dtype = 1, 4, 20, L.SQ_BF16
+    r.x_dev = r.gate_dev = r.y_dev = r.out_dev = 256
+    assert native_lib.sq_gated_residual(ctypes.byref(r), None) == L.SQ_ERR_ALIGNMENT      # K not a multiple of 8
+    r.K, r.dtype = 16, L.SQ_F32
+    assert native_lib.sq_gated_residual(ctypes.byref(r), None) == L.SQ_ERR_UNSUPPORTED    # 16-bit tensors only
     a = L.GemmArgs()
     a.kind = 99
     assert native_lib.sq_gemm(ctypes.byref(a), None) == L.SQ_ERR_INVALID_ARG

@@ -165,3 +165,23 @@ def test_fused_norm_step_matches_unfused_step():
     assert cos > 0.999
     from segquant_b200 import ops
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gated_residual_is_bit_identical_to_addcmul(dtype):
+    from segquant_b200 import ops
+    torch.manual_seed(2)
+    B, T, K = 2, 333, 1536
+    x = torch.randn(B, T, K, device="cuda").to(dtype)
+    y = (torch.randn(B, T + 5, K, device="cuda") * 3).to(dtype)[:, 5:]          # a token slice: batch stride != T * K
+    mod = torch.randn(B, 6 * K, device="cuda").to(dtype)
+    gate = mod[:, 2 * K:3 * K]                                                  # a chunk of the modulation, read in place
+    want = torch.addcmul(x, gate.unsqueeze(1), y)
+    got = ops.gated_residual(x, gate, y)
+    assert torch.equal(got, want)
+    xc = x.clone()
+    ops.gated_residual(xc, gate, y, out=xc)                                     # in place
+    assert torch.equal(xc, want)
+    with pytest.raises(Exception):
+        ops.gated_residual(x[..., :20], gate[:, :20], y[..., :20])
+    assert ops.device_status() == 0
