@@ -607,7 +607,7 @@ def run_sweep(args):
 def run_kernels(args):
     """The HBM-bound kernels alone on [rows, 12288] tensors (larger than L2): activation quantise (bf16 / fp32, single,
     DualScale, dynamic per-token), weight quantise (int8, packed int4 with group scales), int4 unpack, and the fused
-    LayerNorm + modulation + quantise on the same bytes seen as rows of 1536.
+    LayerNorm + modulation + quantise and the gated residual add on the same bytes seen as rows of 1536.
     GB/s = algorithmic bytes / mean CUDA-event time; frac = GB/s / measured copy bandwidth."""
     from segquant_b200 import _lib as L
     from segquant_b200 import ops
@@ -633,6 +633,7 @@ def run_kernels(args):
     sw_grp = (7.0 / x16.float().view(R, K // 128, 128).abs().amax(-1)).contiguous()
     ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128)
     xn = x16.view(1, R * K // 1536, 1536)
+    yn, on = torch.randn_like(xn), torch.empty_like(xn)
     mod = (torch.randn(1, 2 * 1536, generator=g) * 0.3).to(torch.bfloat16).to(dev)
     cases = [
         ("act_quant bf16 -> int8, 4 segments", lambda: ops.quantize_act(x16, bounds, sx, None, L.SQ_Q_INT8), R * K * 3),
@@ -644,6 +645,7 @@ def run_kernels(args):
         ("weight_quant bf16 -> packed int4, groups of 128", lambda: ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128),
          R * K * 2.5 + R * K // 128 * 4),
         ("unpack_int4", lambda: ops.unpack_int4(wq4), R * K * 1.5),
+        ("gated_residual bf16 rows of 1536 (x + gate * y)", lambda: ops.gated_residual(xn, mod[:, :1536], yn, out=on), R * K * 6),
         # the same bytes seen as rows of 1536 (a DiT hidden size): LayerNorm + modulation + quantise in one pass
         ("norm_quant bf16 rows of 1536 -> int8, modulated", lambda: ops.norm_quantize_act(xn, [0, 1536], sx[:1], None, L.SQ_Q_INT8, shift=mod[:, :1536], scale=mod[:, 1536:]),
          R * K * 3),
