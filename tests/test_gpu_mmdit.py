@@ -153,6 +153,11 @@ def test_fused_norm_step_matches_unfused_step():
     model.calibrate(*inp)
     fused = model(*inp).float()
     assert any(v is not None for v in model.fused_norm.plan.values())       # the fused kernel really ran
+    assert any(isinstance(k, tuple) and k and k[0] == "merged" and v is not None for k, v in model.fused_norm.plan.items())
+    model.fused_norm.merge_gemms = False        # q / k / v as three GEMMs instead of one: integer accumulation, same epilogue
+    separate = model(*inp).float()
+    model.fused_norm.merge_gemms = True
+    assert torch.equal(fused, separate)
     from segquant_b200.mmdit import QLinear
     keep, model.fused_norm = model.fused_norm, None
     QLinear.fuse_activation = False
