@@ -16,7 +16,9 @@ would give it (segquant/pattern_detector.py:239-358):
   * everything else: S = 1.
 Attention (torch SDPA) stays bf16.  Scales are calibrated once from one forward of the float model on the
 given inputs (AMax), then every layer runs the fused quantise + tcgen05 GEMM path; where a LayerNorm + adaLN
-modulation feeds linears, one kernel normalises, modulates and quantises (FusedNorm below).
+modulation feeds linears, one kernel normalises, modulates and quantises (FusedNorm below), q / k / v of a stream
+run as one GEMM on those bytes, the GELU in front of the MLP down-projection is evaluated inside its quantise kernel,
+and the gated residual updates use this library's vectorised kernel.
 """
 import math
 
