@@ -139,6 +139,24 @@ int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev,
 int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev,
                          int64_t mod_batch_stride, float eps, sq_stream_t stream);
 
+/* The same with the gated residual update of the stream in front: x' = x + gate[b] * y (arithmetic and rounding of
+ * sq_gated_residual / torch.addcmul) is written to x_out_dev and normalised from registers, so the update costs no
+ * pass over [tokens, hidden] of its own.  y / x_out: [batch, M, K] in the dtype of x, gate: [batch, K]; strides in
+ * elements, 16-byte aligned; x_out must not alias x.  residual == NULL is sq_norm_quantize_act.
+ */
+typedef struct sq_norm_residual {
+    const void* y_dev;
+    const void* gate_dev;
+    void* x_out_dev;
+    int64_t y_batch_stride, y_row_stride;
+    int64_t gate_batch_stride;
+    int64_t x_out_batch_stride, x_out_row_stride;
+} sq_norm_residual;
+
+int sq_residual_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev,
+                                  int64_t mod_batch_stride, float eps, const sq_norm_residual* residual,
+                                  sq_stream_t stream);
+
 /* ---- gated residual add (no counterpart in the reference) ---------------------------------------
  * out[b, r, :] = x[b, r, :] + gate[b, :] * y[b, r, :] on 16-bit tensors: the residual-stream update of a DiT block
  * (y = output of a quantised linear, gate = a chunk of the adaLN modulation).  Bit-identical to torch.addcmul; exists

@@ -25,7 +25,7 @@ SQ_GEMM_W8A8_I8, SQ_GEMM_W8A8_F8, SQ_GEMM_W4A8 = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "sq_version", "sq_last_error", "sq_status_string", "sq_device_status",
-    "sq_quantize_act", "sq_quantize_act_dynamic", "sq_norm_quantize_act", "sq_gated_residual", "sq_quantize_weight", "sq_unpack_int4",
+    "sq_quantize_act", "sq_quantize_act_dynamic", "sq_norm_quantize_act", "sq_residual_norm_quantize_act", "sq_gated_residual", "sq_quantize_weight", "sq_unpack_int4",
     "sq_gemm", "sq_gemm_num_units", "sq_seg_linear",
 )
 
@@ -48,6 +48,16 @@ class ActQuantArgs(ctypes.Structure):
         ("xq_neg_dev", ctypes.c_void_p),
         ("xq_batch_stride", ctypes.c_int64), ("xq_row_stride", ctypes.c_int64),
         ("pre_act", ctypes.c_int32), ("reserved0", ctypes.c_int32),
+    ]
+
+
+class NormResidual(ctypes.Structure):
+    """struct sq_norm_residual"""
+    _fields_ = [
+        ("y_dev", ctypes.c_void_p), ("gate_dev", ctypes.c_void_p), ("x_out_dev", ctypes.c_void_p),
+        ("y_batch_stride", ctypes.c_int64), ("y_row_stride", ctypes.c_int64),
+        ("gate_batch_stride", ctypes.c_int64),
+        ("x_out_batch_stride", ctypes.c_int64), ("x_out_row_stride", ctypes.c_int64),
     ]
 
 
@@ -137,6 +147,9 @@ def load():
     lib.sq_quantize_act.restype = ctypes.c_int
     lib.sq_quantize_act.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p]
     lib.sq_quantize_act_dynamic.restype = ctypes.c_int
+    lib.sq_residual_norm_quantize_act.restype = ctypes.c_int
+    lib.sq_residual_norm_quantize_act.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                                  ctypes.c_float, ctypes.POINTER(NormResidual), ctypes.c_void_p]
     lib.sq_gated_residual.restype = ctypes.c_int
     lib.sq_gated_residual.argtypes = [ctypes.POINTER(GatedResidualArgs), ctypes.c_void_p]
     lib.sq_norm_quantize_act.restype = ctypes.c_int

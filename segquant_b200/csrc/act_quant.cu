@@ -100,6 +100,9 @@ struct Unit<float> {
     __device__ static __forceinline__ void unpack(const uint4& t, float (&v)[4]) {
         v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y); v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
     }
+    __device__ static __forceinline__ uint4 pack(const float (&v)[4]) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
 };
 template <>
 struct Unit<__half> {
@@ -109,6 +112,12 @@ struct Unit<__half> {
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
     }
+    __device__ static __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]); w[j] = *reinterpret_cast<const uint32_t*>(&h); }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
 };
 template <>
 struct Unit<__nv_bfloat16> {
@@ -117,6 +126,12 @@ struct Unit<__nv_bfloat16> {
         const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+    }
+    __device__ static __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]); w[j] = *reinterpret_cast<const uint32_t*>(&h); }
+        return make_uint4(w[0], w[1], w[2], w[3]);
     }
 };
 
@@ -519,9 +534,19 @@ constexpr int kNormWords = 8;
 // NW = 128-bit words per lane the row needs (4, 6 or 8), a compile-time bound so that short rows do not pay for the
 // registers of long ones: with at most 64 registers a thread, four 256-thread CTAs stay resident per SM, and it is the
 // number of rows in flight per SM that decides how much of the HBM bandwidth a load -> reduce -> store chain reaches.
-template <typename T, int OUT, bool DUAL, int NW>
-__global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
-                                                                          const T* __restrict__ scale, long long mod_bs, float eps) {
+// Optional gated residual in front of the normalisation: x' = x + gate[b] * y (the update of the residual stream by the
+// previous linear's output, arithmetic and rounding of torch.addcmul), written to x_out and normalised from registers.
+struct NormResidual {
+    const void* y;       // nullptr: no residual
+    const void* gate;
+    void* x_out;         // must not alias x
+    long long y_bs, y_rs, g_bs, o_bs, o_rs;   // elements
+};
+
+template <typename T, int OUT, bool DUAL, int NW, bool RES>
+__global__ void __launch_bounds__(256, (NW <= 6 && !RES) ? 4 : 3) norm_quant_kernel(const __grid_constant__ ActQuantParams p, const T* __restrict__ shift,
+                                                                                    const T* __restrict__ scale, long long mod_bs, float eps,
+                                                                                    const __grid_constant__ NormResidual res) {
     constexpr int E = Unit<T>::E;
     constexpr int H = E / 4;                       // float4 pieces per 128-bit word of x
     constexpr int kMaxWords = 32 * kNormWords;
@@ -567,6 +592,25 @@ __global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const 
 #pragma unroll
         for (int j = 0; j < NW; ++j)
             if (lane + 32 * j < words) raw[j] = __ldg(reinterpret_cast<const uint4*>(xr) + lane + 32 * j);
+        if constexpr (RES) {
+            const uint4* yr = reinterpret_cast<const uint4*>(static_cast<const T*>(res.y) + b * res.y_bs + r * res.y_rs);
+            const uint4* gr = reinterpret_cast<const uint4*>(static_cast<const T*>(res.gate) + b * res.g_bs);
+            uint4* orow = reinterpret_cast<uint4*>(static_cast<T*>(res.x_out) + b * res.o_bs + r * res.o_rs);
+#pragma unroll
+            for (int j = 0; j < NW; ++j) {
+                const int u = lane + 32 * j;
+                if (u < words) {
+                    float xv[E], yv[E], gv[E];
+                    Unit<T>::unpack(raw[j], xv);
+                    Unit<T>::unpack(__ldg(yr + u), yv);
+                    Unit<T>::unpack(__ldg(gr + u), gv);
+#pragma unroll
+                    for (int i = 0; i < E; ++i) xv[i] = __fadd_rn(xv[i], __fmul_rn(gv[i], yv[i]));   // two roundings, like torch
+                    raw[j] = Unit<T>::pack(xv);    // the stream stays in T: normalise what was stored
+                    orow[u] = raw[j];
+                }
+            }
+        }
 
         float pivot = 0.0f;
         if (lane < words) {
@@ -644,7 +688,7 @@ __global__ void __launch_bounds__(256, NW <= 6 ? 4 : 3) norm_quant_kernel(const 
 
 template <typename T, int OUT>
 static void launch_norm(const ActQuantParams& p, bool dual, const void* shift, const void* scale, long long mod_bs, float eps,
-                        cudaStream_t st) {
+                        const NormResidual& res, cudaStream_t st) {
     const long long rows = p.batch * p.M;
     int block = 256;
     int grid = grid_for(rows);
@@ -655,21 +699,41 @@ static void launch_norm(const ActQuantParams& p, bool dual, const void* shift, c
     const T* sh = static_cast<const T*>(shift);
     const T* sc = static_cast<const T*>(scale);
     const long long per_lane = (p.K / Unit<T>::E + 31) / 32;
-#define SQ_NORM(NW)                                                                                \
-    do {                                                                                           \
-        if (dual) norm_quant_kernel<T, OUT, true, NW><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);  \
-        else norm_quant_kernel<T, OUT, false, NW><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps);      \
+#define SQ_NORM2(NW, RES)                                                                                  \
+    do {                                                                                                   \
+        if (dual) norm_quant_kernel<T, OUT, true, NW, RES><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps, res);  \
+        else norm_quant_kernel<T, OUT, false, NW, RES><<<grid, block, 0, st>>>(p, sh, sc, mod_bs, eps, res);      \
+    } while (0)
+#define SQ_NORM(NW)                                \
+    do {                                           \
+        if (res.y != nullptr) SQ_NORM2(NW, true);  \
+        else SQ_NORM2(NW, false);                  \
     } while (0)
     if (per_lane <= 4) SQ_NORM(4);
     else if (per_lane <= 6) SQ_NORM(6);
     else SQ_NORM(kNormWords);
 #undef SQ_NORM
+#undef SQ_NORM2
 }
 
-int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st) {
+int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps,
+                      const sq_norm_residual* r, cudaStream_t st) {
     int rc = validate(a, false);
     if (rc != SQ_OK) return rc;
     if (a->batch * a->M * a->K == 0) return SQ_OK;
+    NormResidual res = {};
+    if (r != nullptr) {
+        SQ_REQUIRE(r->y_dev && r->gate_dev && r->x_out_dev, SQ_ERR_INVALID_ARG, "sq_norm_quantize_act: residual pointers must not be NULL");
+        SQ_REQUIRE(r->x_out_dev != a->x_dev, SQ_ERR_INVALID_ARG, "sq_norm_quantize_act: x_out must not alias x");
+        const long long e16 = a->x_dtype == SQ_F32 ? 4 : 8;      // elements per 16 bytes
+        SQ_REQUIRE(reinterpret_cast<uintptr_t>(r->y_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(r->gate_dev) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(r->x_out_dev) % 16 == 0 && r->y_batch_stride % e16 == 0 && r->y_row_stride % e16 == 0 &&
+                       r->gate_batch_stride % e16 == 0 && r->x_out_batch_stride % e16 == 0 && r->x_out_row_stride % e16 == 0,
+                   SQ_ERR_ALIGNMENT, "sq_norm_quantize_act: residual pointers and strides must be 16-byte aligned");
+        res.y = r->y_dev; res.gate = r->gate_dev; res.x_out = r->x_out_dev;
+        res.y_bs = r->y_batch_stride; res.y_rs = r->y_row_stride; res.g_bs = r->gate_batch_stride;
+        res.o_bs = r->x_out_batch_stride; res.o_rs = r->x_out_row_stride;
+    }
     SQ_REQUIRE((shift == nullptr) == (scale == nullptr), SQ_ERR_INVALID_ARG, "sq_norm_quantize_act: shift and scale go together");
     SQ_REQUIRE(a->sx_row_stride == 0 && a->smooth_dev == nullptr && a->pre_act == SQ_ACT_NONE, SQ_ERR_UNSUPPORTED,
                "sq_norm_quantize_act: static per-segment scales only, no smoothing vector, no pre_act");
@@ -687,8 +751,8 @@ int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void*
     const bool dual = a->xq_neg_dev != nullptr;
 #define SQ_DISPATCH(T)                                                                          \
     do {                                                                                        \
-        if (a->out_kind == SQ_Q_INT8) launch_norm<T, SQ_Q_INT8>(p, dual, shift, scale, mod_bs, eps, st); \
-        else launch_norm<T, SQ_Q_E4M3>(p, dual, shift, scale, mod_bs, eps, st);                 \
+        if (a->out_kind == SQ_Q_INT8) launch_norm<T, SQ_Q_INT8>(p, dual, shift, scale, mod_bs, eps, res, st); \
+        else launch_norm<T, SQ_Q_E4M3>(p, dual, shift, scale, mod_bs, eps, res, st);                 \
     } while (0)
     if (a->x_dtype == SQ_F32) SQ_DISPATCH(float);
     else if (a->x_dtype == SQ_F16) SQ_DISPATCH(__half);

@@ -22,7 +22,8 @@ void clear_error() { g_err[0] = 0; }
 // implemented in act_quant.cu / weight_quant.cu / seg_gemm.cu
 int quantize_act(const sq_act_quant_args* a, cudaStream_t st);
 int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_neg_out, cudaStream_t st);
-int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps, cudaStream_t st);
+int norm_quantize_act(const sq_act_quant_args* a, const void* shift, const void* scale, long long mod_bs, float eps,
+                      const sq_norm_residual* r, cudaStream_t st);
 int gated_residual(const sq_gated_residual_args* a, cudaStream_t st);
 int quantize_weight(const void* w, int w_dtype, long long N, long long K, int scale_mode, float scale_scalar,
                     const float* scale, int group_size, int out_kind, void* out, cudaStream_t st);
@@ -72,7 +73,13 @@ int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev, fl
 int sq_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev, int64_t mod_batch_stride,
                          float eps, sq_stream_t stream) {
     sq::clear_error();
-    return sq::norm_quantize_act(args, shift_dev, scale_dev, mod_batch_stride, eps, static_cast<cudaStream_t>(stream));
+    return sq::norm_quantize_act(args, shift_dev, scale_dev, mod_batch_stride, eps, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int sq_residual_norm_quantize_act(const sq_act_quant_args* args, const void* shift_dev, const void* scale_dev, int64_t mod_batch_stride,
+                                  float eps, const sq_norm_residual* residual, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::norm_quantize_act(args, shift_dev, scale_dev, mod_batch_stride, eps, residual, static_cast<cudaStream_t>(stream));
 }
 
 int sq_gated_residual(const sq_gated_residual_args* args, sq_stream_t stream) {

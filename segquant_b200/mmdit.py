@@ -103,9 +103,10 @@ class FusedNorm:
 
     MAX_ROW_BYTES = 4096
 
-    def __init__(self, merge_gemms=True):
+    def __init__(self, merge_gemms=True, fuse_residual=True):
         self.plan = {}
         self.merge_gemms = merge_gemms
+        self.fuse_residual = fuse_residual
 
     def _params(self, layers, x):
         key = tuple(id(l) for l in layers)
@@ -155,23 +156,31 @@ class FusedNorm:
             return None
         return m
 
-    def __call__(self, layers, x, shift, scale, outs=None):
+    def __call__(self, layers, x, shift, scale, outs=None, residual=None):
+        """Returns (outputs, x'): residual=(gate, y) first updates the stream, x' = x + gate * y, inside the same kernel."""
         from . import ops
         outs = outs or [None] * len(layers)
         p = self._params(layers, x)
+        if p is None or (residual is not None and not self.fuse_residual):
+            if residual is not None:
+                x = _gated_add(x, *residual)
+                residual = None
         if p is None:
             n = _modulate(x, shift, scale)
-            return [l(n, out=o) for l, o in zip(layers, outs)]
+            return [l(n, out=o) for l, o in zip(layers, outs)], x
         bounds, sx, sx_neg, kind = p
-        xq, xq_neg = ops.norm_quantize_act(x, bounds, sx, sx_neg, out_kind=kind, shift=shift, scale=scale)
+        if residual is None:
+            xq, xq_neg = ops.norm_quantize_act(x, bounds, sx, sx_neg, out_kind=kind, shift=shift, scale=scale)
+        else:
+            xq, xq_neg, x = ops.norm_quantize_act(x, bounds, sx, sx_neg, out_kind=kind, shift=shift, scale=scale, residual=residual)
         m = self._merged(layers, outs) if self.merge_gemms else None
         if m is not None:
             o0 = outs[0]
             joint = torch.as_strided(o0, (o0.shape[0], o0.shape[1], m["N"]), o0.stride())
             ops.gemm(m["kind"], xq, m["wq"], m["N"], bounds, sx, m["sw"], xq_neg=xq_neg, sx_neg=sx_neg, bias=m["bias"],
                      out_dtype=joint.dtype, out=joint, y_strides=(joint.stride(0), joint.stride(1)), sx_batch_stride=0)
-            return list(outs)
-        return [l.layer.forward_quantized(xq, xq_neg, out=o, out_dtype=x.dtype) for l, o in zip(layers, outs)]
+            return list(outs), x
+        return [l.layer.forward_quantized(xq, xq_neg, out=o, out_dtype=x.dtype) for l, o in zip(layers, outs)], x
 
 
 def _timestep_embedding(t, dim=256):
@@ -202,10 +211,12 @@ class JointBlock:
             names += ["to_add_out", "ffc0", "ffc2"]
         return [getattr(self, n) for n in names]
 
-    def forward(self, img, txt, c_act, call, norm_call):
+    def forward(self, img, txt, c_act, call, norm_call, pend_img=None, pend_txt=None):
         """c_act = SiLU(conditioning) [B, H]; call(layer, x, out=None, pre_act=None) runs either the calibration or the
-        quantized linear on pre_act(x), writing into `out` when given; norm_call(layers, x, shift, scale, outs) runs
-        `layers` on the normalised and modulated x."""
+        quantized linear on pre_act(x), writing into `out` when given; norm_call(layers, x, shift, scale, outs, residual)
+        first applies the pending gated residual (gate, y) to the stream x, then runs `layers` on the normalised and
+        modulated x, and returns (outputs, updated x).  pend_* are the residuals the previous block left unapplied;
+        the block returns its own (of the MLP) the same way, so every residual update rides on the next normalisation."""
         B, Ti, H = img.shape
         Tt = txt.shape[1]
         m = call(self.norm1, c_act).chunk(6, dim=-1)                         # shift, scale, gate (msa), shift, scale, gate (mlp)
@@ -214,8 +225,8 @@ class JointBlock:
         # the six projections write straight into their token range of one joint buffer, q | k | v side by side per
         # token, so the three projections of a stream can be one GEMM of 3 H columns
         qkv = torch.empty((B, Ti + Tt, 3, H), dtype=img.dtype, device=img.device)
-        norm_call((self.to_q, self.to_k, self.to_v), img, m[0], m[1], [qkv[:, :Ti, j] for j in range(3)])
-        norm_call((self.add_q, self.add_k, self.add_v), txt, mc[0], mc[1], [qkv[:, Ti:, j] for j in range(3)])
+        _, img = norm_call((self.to_q, self.to_k, self.to_v), img, m[0], m[1], [qkv[:, :Ti, j] for j in range(3)], pend_img)
+        _, txt = norm_call((self.add_q, self.add_k, self.add_v), txt, mc[0], mc[1], [qkv[:, Ti:, j] for j in range(3)], pend_txt)
 
         def heads(t):
             return t.view(B, Ti + Tt, self.heads, H // self.heads).transpose(1, 2)
@@ -224,14 +235,13 @@ class JointBlock:
         a = a.transpose(1, 2).reshape(B, Ti + Tt, H)
         a_img, a_txt = a[:, :Ti], a[:, Ti:]
 
-        img = _gated_add(img, m[2], call(self.to_out, a_img))
-        h = norm_call((self.ff0,), img, m[3], m[4])[0]
-        img = _gated_add(img, m[5], call(self.ff2, h, pre_act="gelu_tanh"))
+        (h,), img = norm_call((self.ff0,), img, m[3], m[4], None, (m[2], call(self.to_out, a_img)))
+        pend_img = (m[5], call(self.ff2, h, pre_act="gelu_tanh"))
+        pend_txt = None
         if not self.last:
-            txt = _gated_add(txt, mc[2], call(self.to_add_out, a_txt))
-            h = norm_call((self.ffc0,), txt, mc[3], mc[4])[0]
-            txt = _gated_add(txt, mc[5], call(self.ffc2, h, pre_act="gelu_tanh"))
-        return img, txt
+            (h,), txt = norm_call((self.ffc0,), txt, mc[3], mc[4], None, (mc[2], call(self.to_add_out, a_txt)))
+            pend_txt = (mc[5], call(self.ffc2, h, pre_act="gelu_tanh"))
+        return img, txt, pend_img, pend_txt
 
 
 class SyntheticMMDiT:
@@ -265,10 +275,11 @@ class SyntheticMMDiT:
         c_act = F.silu(temb + pemb)
         txt = call(self.context_embedder, text)
         img = latents
+        pend_img = pend_txt = None
         for blk in self.blocks:
-            img, txt = blk.forward(img, txt, c_act, call, norm_call)
+            img, txt, pend_img, pend_txt = blk.forward(img, txt, c_act, call, norm_call, pend_img, pend_txt)
         mod = call(self.norm_out, c_act).chunk(2, dim=-1)                    # scale, shift
-        return norm_call((self.proj_out,), img, mod[1], mod[0])[0]
+        return norm_call((self.proj_out,), img, mod[1], mod[0], None, pend_img)[0][0]
 
     def calibrate(self, latents, text, pooled, timestep):
         """One forward of the float model; every linear records its input range and is then quantized."""
@@ -279,9 +290,11 @@ class SyntheticMMDiT:
                     out.copy_(y)
                     return out
                 return y
-            def calib_norm(layers, x, shift, scale, outs=None):
+            def calib_norm(layers, x, shift, scale, outs=None, residual=None):
+                if residual is not None:
+                    x = _gated_add(x, *residual)
                 n = _modulate(x, shift, scale)
-                return [calib(l, n, o) for l, o in zip(layers, outs or [None] * len(layers))]
+                return [calib(l, n, o) for l, o in zip(layers, outs or [None] * len(layers))], x
             y = self._forward(latents, text, pooled, timestep, calib, calib_norm)
             for lin in self.linears():
                 lin.finish()
@@ -292,9 +305,11 @@ class SyntheticMMDiT:
         if not self.calibrated:
             raise RuntimeError("call calibrate() once before running the quantized model")
         with torch.no_grad():
-            def unfused(layers, x, shift, scale, outs=None):
+            def unfused(layers, x, shift, scale, outs=None, residual=None):
+                if residual is not None:
+                    x = _gated_add(x, *residual)
                 n = _modulate(x, shift, scale)
-                return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))]
+                return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))], x
             return self._forward(latents, text, pooled, timestep,
                                  lambda layer, x, out=None, pre_act=None: layer(x, out=out, pre_act=pre_act),
                                  self.fused_norm or unfused)

@@ -113,11 +113,14 @@ def quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, per_token=Fal
     return xq, xqn
 
 
-def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=None, scale=None, eps=1e-6):
+def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=None, scale=None, eps=1e-6, residual=None):
     """LayerNorm(x) * (1 + scale) + shift, quantised with the static per-segment scales, in one pass over x.
 
     x: (B, T, K) with contiguous rows; shift / scale: (B, K) in x's dtype (or both None for a plain LayerNorm);
-    sx (and sx_neg for DualScale): (S,) float32 shared by all batches.  Returns (xq, xq_neg) uint8 (B, T, K)."""
+    sx (and sx_neg for DualScale): (S,) float32 shared by all batches.  Returns (xq, xq_neg) uint8 (B, T, K).
+
+    residual=(gate (B, K), y (B, T, K)): the stream is first updated, x' = x + gate * y (bit-identical to torch.addcmul),
+    in the same pass; returns (xq, xq_neg, x') with x' a new tensor of x's dtype."""
     global launch_count
     _need_cuda(x, sx, sx_neg, shift, scale)
     if x.dim() != 3 or x.stride(-1) != 1:
@@ -127,7 +130,7 @@ def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=No
     xq = torch.empty((B, M, K), dtype=torch.uint8, device=x.device)
     xqn = torch.empty((B, M, K), dtype=torch.uint8, device=x.device) if dual else None
     if x.numel() == 0:
-        return xq, xqn
+        return (xq, xqn) if residual is None else (xq, xqn, x.clone())
     a = L.ActQuantArgs()
     a.x_dev, a.x_dtype, a.out_kind = x.data_ptr(), _dt(x), out_kind
     a.batch, a.M, a.K = B, M, K
@@ -147,12 +150,27 @@ def norm_quantize_act(x, bounds, sx, sx_neg=None, out_kind=L.SQ_Q_INT8, shift=No
         if shift.stride(-1) != 1 or scale.stride(-1) != 1 or (B > 1 and shift.stride(0) != scale.stride(0)):
             shift, scale = shift.contiguous(), scale.contiguous()     # views with one common row stride are read in place
         mod_bs = shift.stride(0) if B > 1 else 0
+    res, x_new = None, None
+    if residual is not None:
+        gate, y = residual
+        _need_cuda(gate, y)
+        if y.shape != x.shape or y.dtype != x.dtype or y.stride(-1) != 1 or gate.shape != (B, K) or gate.dtype != x.dtype:
+            raise ValueError("residual=(gate (B, K), y (B, T, K)) in x's dtype, rows contiguous")
+        if gate.stride(-1) != 1:
+            gate = gate.contiguous()
+        x_new = torch.empty((B, M, K), dtype=x.dtype, device=x.device)
+        res = L.NormResidual()
+        res.y_dev, res.gate_dev, res.x_out_dev = y.data_ptr(), gate.data_ptr(), x_new.data_ptr()
+        res.y_batch_stride, res.y_row_stride = (y.stride(0) if B > 1 else 0), y.stride(1)
+        res.gate_batch_stride = gate.stride(0) if B > 1 else 0
+        res.x_out_batch_stride, res.x_out_row_stride = M * K, K
     with torch.cuda.device(x.device):
-        L.check(L.load().sq_norm_quantize_act(ctypes.byref(a), shift.data_ptr() if shift is not None else None,
-                                              scale.data_ptr() if scale is not None else None, mod_bs, float(eps), _stream(x)),
+        L.check(L.load().sq_residual_norm_quantize_act(ctypes.byref(a), shift.data_ptr() if shift is not None else None,
+                                                       scale.data_ptr() if scale is not None else None, mod_bs, float(eps),
+                                                       ctypes.byref(res) if res is not None else None, _stream(x)),
                 "sq_norm_quantize_act")
     launch_count += 1
-    return xq, xqn
+    return (xq, xqn) if residual is None else (xq, xqn, x_new)
 
 
 def gated_residual(x, gate, y, out=None):

@@ -158,6 +158,10 @@ def test_fused_norm_step_matches_unfused_step():
     separate = model(*inp).float()
     model.fused_norm.merge_gemms = True
     assert torch.equal(fused, separate)
+    model.fused_norm.fuse_residual = False      # gated residual as its own kernel: same arithmetic, same roundings
+    separate = model(*inp).float()
+    model.fused_norm.fuse_residual = True
+    assert torch.equal(fused, separate)
     from segquant_b200.mmdit import QLinear
     keep, model.fused_norm = model.fused_norm, None
     QLinear.fuse_activation = False
@@ -189,4 +193,26 @@ def test_gated_residual_is_bit_identical_to_addcmul(dtype):
     assert torch.equal(xc, want)
     with pytest.raises(Exception):
         ops.gated_residual(x[..., :20], gate[:, :20], y[..., :20])
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype,dual", [(torch.bfloat16, False), (torch.bfloat16, True), (torch.float16, False)])
+def test_norm_quantize_act_with_residual(dtype, dual):
+    """residual=(gate, y): the updated stream is bit-identical to torch.addcmul and the codes are those of the plain
+    kernel run on that updated stream."""
+    from segquant_b200 import _lib as L, ops
+    torch.manual_seed(9)
+    B, T, K = 2, 150, 1024 if dtype == torch.float32 else 1536
+    x = torch.randn(B, T, K, device="cuda").to(dtype)
+    y = (torch.randn(B, T, K, device="cuda") * 2).to(dtype)
+    mod = (torch.randn(B, 6 * K, device="cuda") * 0.3).to(dtype)
+    shift, scale, gate = mod[:, :K], mod[:, K:2 * K], mod[:, 2 * K:3 * K]
+    sx = torch.tensor([127.0 / 4.0], device="cuda")
+    sxn = torch.tensor([127.0 / 3.0], device="cuda") if dual else None
+    q, qn, x_new = ops.norm_quantize_act(x, [0, K], sx, sxn, shift=shift, scale=scale, residual=(gate, y))
+    want_x = torch.addcmul(x, gate.unsqueeze(1), y)
+    assert torch.equal(x_new, want_x)
+    rq, rqn = ops.norm_quantize_act(want_x, [0, K], sx, sxn, shift=shift, scale=scale)
+    assert torch.equal(q, rq)
+    assert (qn is None and rqn is None) or torch.equal(qn, rqn)
     assert ops.device_status() == 0
