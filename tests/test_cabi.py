@@ -40,6 +40,7 @@ def test_struct_layout_matches_header(tmp_path):
     fields_a = [f[0] for f in L.ActQuantArgs._fields_]
     fields_g = [f[0] for f in L.GemmArgs._fields_]
     fields_r = [f[0] for f in L.GatedResidualArgs._fields_]
+    fields_n = [f[0] for f in L.NormResidual._fields_]
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){",
              'printf("A %zu\\n", sizeof(sq_act_quant_args));', 'printf("G %zu\\n", sizeof(sq_gemm_args));']
     for f in fields_a:
@@ -49,6 +50,9 @@ def test_struct_layout_matches_header(tmp_path):
     lines.append('printf("R %zu\\n", sizeof(sq_gated_residual_args));')
     for f in fields_r:
         lines.append(f'printf("R.{f} %zu\\n", offsetof(sq_gated_residual_args, {f}));')
+    lines.append('printf("N %zu\\n", sizeof(sq_norm_residual));')
+    for f in fields_n:
+        lines.append(f'printf("N.{f} %zu\\n", offsetof(sq_norm_residual, {f}));')
     lines.append("return 0;}")
     src = tmp_path / "layout.c"
     src.write_text("\n".join(lines))
@@ -59,6 +63,9 @@ def test_struct_layout_matches_header(tmp_path):
     assert int(got["A"]) == ctypes.sizeof(L.ActQuantArgs)
     assert int(got["G"]) == ctypes.sizeof(L.GemmArgs)
     assert int(got["R"]) == ctypes.sizeof(L.GatedResidualArgs)
+    assert int(got["N"]) == ctypes.sizeof(L.NormResidual)
+    for f in fields_n:
+        assert int(got[f"N.{f}"]) == getattr(L.NormResidual, f).offset, f
     for f in fields_r:
         assert int(got[f"R.{f}"]) == getattr(L.GatedResidualArgs, f).offset, f
     for f in fields_a:
