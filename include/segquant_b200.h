@@ -122,7 +122,10 @@ int sq_quantize_act(const sq_act_quant_args* args, sq_stream_t stream);
  * sx_out_dev[(b*num_segs + s)*M + r] and quantises with it in the same launch.
  * With DualScale the positive side uses qmax/pos_amax and the negative side |qmin|/neg_amax
  * (quantizer.py:187-203; 448 on both sides for e4m3, :425-440); they go to sx_out_dev and
- * sx_neg_out_dev.  Uses args->x*, batch/M/K, seg_bounds, out_kind, xq*; ignores args->sx*.
+ * sx_neg_out_dev.  Uses args->x*, batch/M/K, seg_bounds, out_kind, xq*, smooth_dev; ignores args->sx*.
+ * With smooth_dev the row is first divided by the K smoothing factors and rounded to the dtype of x, which
+ * is the tensor the reference's Smooth / SVD optimizers calibrate on (optimizer.py:467-470, :724-728): pass the
+ * factors already rounded to that dtype.
  */
 int sq_quantize_act_dynamic(const sq_act_quant_args* args, float* sx_out_dev,
                             float* sx_neg_out_dev, sq_stream_t stream);

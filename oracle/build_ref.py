@@ -41,6 +41,8 @@ def load_prebuilt():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SEGQUANT_REFERENCE")
+    if not root:
+        raise SystemExit("usage: build_ref.py <reference checkout>  (or set SEGQUANT_REFERENCE)")
     m = build(root)
     print("built", m.__file__ if hasattr(m, "__file__") else m)

@@ -77,6 +77,22 @@ class AMaxCalibrator(BaseCalibrator):
         return f"AMaxCalibrator(quantizer={self.quantizer!r})"
 
 
+def colpacked1d_to_rowpacked1d(q_colpacked_1d, out, cols):
+    """Re-pack int4 weights from the column-major pairing a blocked weight search produces -- byte (c, j) of a
+    (cols, out/2) array holds rows 2j (low nibble) and 2j+1 (high nibble) of column c -- into this library's storage:
+    row-major [out, cols/2] bytes, element 2k of a row in the low nibble, 2k+1 in the high nibble (what the GEMM's
+    TMA loads consume).  Same contract as GPTQCalibrator.colpacked1d_to_rowpacked1d of the reference
+    (segquant/calibrator/calibrator.py:202-223).  Returns a 1-D uint8 tensor of out * cols / 2 bytes."""
+    import torch
+    if out % 2 or cols % 2:
+        raise ValueError("Output and columns must be even for int4 quantization.")
+    b = q_colpacked_1d.reshape(cols, out // 2)
+    full = torch.empty((out, cols), dtype=torch.uint8, device=b.device)     # one nibble per entry, [row, column]
+    full[0::2] = (b & 0x0F).t()
+    full[1::2] = (b >> 4).t()
+    return (full[:, 0::2] | (full[:, 1::2] << 4)).reshape(-1)
+
+
 @CalibratorRegistry.register("gptq")
 def _gptq(**kwargs):
     raise NotImplementedError("GPTQ calibration is an offline weight search that this library does not provide; "

@@ -264,12 +264,27 @@ __global__ void __launch_bounds__(256, 4) act_quant_kernel(const __grid_constant
 // (segquant/quantizers/quantizer.py:209-217, :187-203), and torch evaluates scalar / tensor as
 // tensor.reciprocal() * scalar: two roundings to that dtype, reproduced here.
 template <typename T>
+__device__ __forceinline__ void smooth16(float (&v)[16], const float* __restrict__ sm) {
+#pragma unroll
+    for (int i4 = 0; i4 < 4; ++i4) {
+        const float4 d = __ldg(reinterpret_cast<const float4*>(sm) + i4);
+        v[4 * i4 + 0] = to_float<T>(from_float<T>(__fdiv_rn(v[4 * i4 + 0], d.x)));
+        v[4 * i4 + 1] = to_float<T>(from_float<T>(__fdiv_rn(v[4 * i4 + 1], d.y)));
+        v[4 * i4 + 2] = to_float<T>(from_float<T>(__fdiv_rn(v[4 * i4 + 2], d.z)));
+        v[4 * i4 + 3] = to_float<T>(from_float<T>(__fdiv_rn(v[4 * i4 + 3], d.w)));
+    }
+}
+
+template <typename T>
 __device__ __forceinline__ float scale_like_torch(float qmax, float amax) {
     const float r = to_float<T>(from_float<T>(__frcp_rn(amax)));
     return to_float<T>(from_float<T>(r * qmax));
 }
 
-template <typename T, int OUT, bool DUAL>
+// SMOOTH: every element is first divided by its channel's smoothing factor and rounded to T, as the reference's
+// `input_chunk.div_(s.to(dtype))` leaves it (segquant/optimum/optimizer.py:467-470) before the per-token calibration
+// sees it; p.smooth holds the factors already rounded to T (as fp32).
+template <typename T, int OUT, bool DUAL, bool SMOOTH>
 __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_constant__ ActQuantParams p) {
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
@@ -292,7 +307,7 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
         uint8_t* qnr = DUAL ? p.xq_neg + b * p.xq_batch_stride + r * p.xq_row_stride : nullptr;
 
         float amax = 0.0f, nmax = 0.0f;
-        if constexpr (sizeof(T) == 2) {
+        if constexpr (sizeof(T) == 2 && !SMOOTH) {
             // 16-bit inputs: the extremes are taken on packed pairs (one abs + one max instruction per two elements;
             // max of values is exact in their own format), converted to fp32 once per row
             using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
@@ -321,6 +336,7 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
             for (int k = k0 + (lane << 4); k < k1; k += 512) {
                 float v[16];
                 load16<T>(xr + k, v);
+                if constexpr (SMOOTH) smooth16<T>(v, p.smooth + k);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     if constexpr (DUAL) {
@@ -348,6 +364,7 @@ __global__ void __launch_bounds__(256) act_quant_dynamic_kernel(const __grid_con
         for (int k = k0 + (lane << 4); k < k1; k += 512) {
             float v[16];
             load16<T>(xr + k, v);
+            if constexpr (SMOOTH) smooth16<T>(v, p.smooth + k);
             if constexpr (!DUAL) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] *= sc;
@@ -463,8 +480,13 @@ static void launch_dynamic(const ActQuantParams& p, bool dual, cudaStream_t st) 
     // SM (164 us), keeping the segment in the registers of a 32-256 thread group (172-203 us), parking it in shared
     // memory between the passes (175 us, 8 warps per SM).
     const int grid = grid_for(p.batch * p.M * p.num_segs);
-    if (dual) act_quant_dynamic_kernel<T, OUT, true><<<grid, 256, 0, st>>>(p);
-    else act_quant_dynamic_kernel<T, OUT, false><<<grid, 256, 0, st>>>(p);
+    if (p.smooth != nullptr) {
+        if (dual) act_quant_dynamic_kernel<T, OUT, true, true><<<grid, 256, 0, st>>>(p);
+        else act_quant_dynamic_kernel<T, OUT, false, true><<<grid, 256, 0, st>>>(p);
+        return;
+    }
+    if (dual) act_quant_dynamic_kernel<T, OUT, true, false><<<grid, 256, 0, st>>>(p);
+    else act_quant_dynamic_kernel<T, OUT, false, false><<<grid, 256, 0, st>>>(p);
 }
 
 int quantize_act(const sq_act_quant_args* a, cudaStream_t st) {
@@ -491,7 +513,6 @@ int quantize_act_dynamic(const sq_act_quant_args* a, float* sx_out, float* sx_ne
     int rc = validate(a, true);
     if (rc != SQ_OK) return rc;
     SQ_REQUIRE(sx_out != nullptr, SQ_ERR_INVALID_ARG, "sq_quantize_act_dynamic: sx_out_dev is NULL");
-    SQ_REQUIRE(a->smooth_dev == nullptr, SQ_ERR_UNSUPPORTED, "sq_quantize_act_dynamic: smooth_dev is not supported");
     const bool dual = a->xq_neg_dev != nullptr;
     SQ_REQUIRE(!dual || sx_neg_out != nullptr, SQ_ERR_INVALID_ARG,
                "sq_quantize_act_dynamic: DualScale needs sx_neg_out_dev");

@@ -202,11 +202,12 @@ def gated_residual(x, gate, y, out=None):
     return out
 
 
-def quantize_act_dynamic(x, bounds, out_kind=L.SQ_Q_INT8, dual=False):
+def quantize_act_dynamic(x, bounds, out_kind=L.SQ_Q_INT8, dual=False, smooth=None):
     """Per-token dynamic scales + quantise in one launch.  x (M, K).  Returns
-    (xq, xq_neg, sx, sx_neg) with scales of shape (S, M)."""
+    (xq, xq_neg, sx, sx_neg) with scales of shape (S, M).  smooth: (K,) float32 divisors, already rounded
+    to x's dtype; the kernel calibrates and quantises round_dtype(x / smooth)."""
     global launch_count
-    _need_cuda(x)
+    _need_cuda(x, smooth)
     if x.dim() != 2 or x.stride(-1) != 1:
         x = x.reshape(-1, x.shape[-1]).contiguous()
     M, K = x.shape
@@ -226,6 +227,7 @@ def quantize_act_dynamic(x, bounds, out_kind=L.SQ_Q_INT8, dual=False):
     a.xq_dev = xq.data_ptr()
     a.xq_neg_dev = xqn.data_ptr() if dual else None
     a.xq_batch_stride, a.xq_row_stride = M * K, K
+    a.smooth_dev = smooth.data_ptr() if smooth is not None else None
     with torch.cuda.device(x.device):
         L.check(L.load().sq_quantize_act_dynamic(ctypes.byref(a), ctypes.c_void_p(sx.data_ptr()),
                                                  ctypes.c_void_p(sxn.data_ptr()) if dual else None, _stream(x)),
@@ -399,7 +401,7 @@ def seg_linear(kernel_type, x, wq, N, bounds, sx, sw, *, sx_neg=None, dynamic=Fa
         return y.reshape(*lead, N)
     x2 = x.reshape(-1, K)
     if dynamic:
-        xq, xqn, sxd, sxnd = quantize_act_dynamic(x2, bounds, a_kind, dual=dual)
+        xq, xqn, sxd, sxnd = quantize_act_dynamic(x2, bounds, a_kind, dual=dual, smooth=smooth)
         y = gemm(kind, xq.unsqueeze(0), wq, N, bounds, sxd, sw, xq_neg=xqn, sx_neg=sxnd, per_token=True,
                  group_size=group_size, sw_strides=sw_strides, bias=bias, out_dtype=out_dtype,
                  w_seg_as_batch=w_seg_as_batch)

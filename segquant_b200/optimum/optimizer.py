@@ -15,10 +15,13 @@ DefaultOptimizer (:166-293) quantises plainly.  Differences, all deliberate:
 * the fake path does not write into the caller's tensor (the reference does, :120-121).
 * unequal K-segments and group-wise weight scales are accepted.
 """
+from collections import deque
+
+import numpy as np
 import torch
 
 from .. import ops
-from ..layers.segment_tensor_manager import segmented_matmul
+from ..layers.segment_tensor_manager import WeightSegmentTensorManager, segmented_matmul
 
 
 def _as_f32(v, device):
@@ -156,6 +159,13 @@ class BaseOptimizer:
         return y.view(B, M, f["N"])
 
     # ---- housekeeping ------------------------------------------------------------------------------
+    def __getstate__(self):
+        """What torch.save(module) stores: the packed weights, scales, smoothing / low-rank factors and quantiser
+        objects; the device-resident argument cache of the fused forward is rebuilt on the first call after loading."""
+        state = dict(self.__dict__)
+        state["_fused"] = None
+        return state
+
     def _calibrate_weights(self, i_view, w_view):
         for cal, w_chunk, x_chunk in zip(self.weight_calibrators, w_view, i_view):
             cal.calibrate(w_chunk, input_data=x_chunk)
@@ -273,15 +283,20 @@ class SmoothOptimizer(BaseOptimizer):
       scales `(S, N)` are applied by the GEMM epilogue unit by unit;
     * N-segments: every chunk smooths x with its own s_i, so x is quantised once per chunk and each
       chunk's GEMM writes its column range of the output in place.
-    The alpha search of the reference (`search_alpha_config`) is not provided."""
+
+    Alpha search (`search_alpha_config = {"enable": True, "min", "max", "step"}`, :351-365, :523-572): the
+    candidates min, min+step, ... are tried in turn, every chunk with the same candidate; a caller (quantize())
+    runs smooth -> calibrate -> finish_calibrate, measures each chunk's error against the float layer and calls
+    search_step(errs, origin_weight), which keeps the best alpha per chunk, restores the original weight, resets
+    the calibrators and moves to the next candidate; it returns True once the candidates are used up, leaving the
+    best alphas in place for the final smooth / calibrate pass.  As in the reference the last candidate of the
+    range is taken off the list by the step that ends the search and is therefore never evaluated."""
 
     def __init__(self, seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
                  real_quant=False, dual_scale=False, kernel_type=None, alpha=0.5, search_alpha_config=None,
                  verbose=False, **kwargs):
         assert len(input_calibrators) == chunks and len(weight_calibrators) == chunks, \
             "SmoothOptimizer needs one input and one weight calibrator per chunk"
-        if search_alpha_config is not None and search_alpha_config.get("enable"):
-            raise NotImplementedError("SmoothOptimizer: alpha search is not provided; pass a fixed alpha")
         super().__init__(seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
                          real_quant, dual_scale, kernel_type)
         self.alpha = [float(alpha)] * chunks
@@ -289,6 +304,16 @@ class SmoothOptimizer(BaseOptimizer):
         self.s = [None] * chunks
         self.has_smoothed = False
         self.verbose = verbose
+        self.search_alpha = bool(search_alpha_config and search_alpha_config.get("enable"))
+        if self.search_alpha:
+            lo, hi, step = (float(search_alpha_config[k]) for k in ("min", "max", "step"))
+            cands = [float(a) for a in np.arange(lo, hi + 1e-8, step)]
+            if not cands:
+                raise ValueError("search_alpha_config gives no candidate")
+            self.candidate_alphas = [deque(cands) for _ in range(chunks)]
+            self.alpha = [c.popleft() for c in self.candidate_alphas]
+            self.opt_err = [float("inf")] * chunks
+            self.opt_alpha = list(self.alpha)
 
     def __repr__(self):
         head = f"SmoothOptimizer(alpha={self.alpha},kernel={self.kernel_type}\n" if self.real_quant else f"SmoothOptimizer(alpha={self.alpha}\n"
@@ -333,14 +358,10 @@ class SmoothOptimizer(BaseOptimizer):
         self._calibrate_weights(chunks, self.weight_manager.iter_list())
 
     def finish_calibrate(self):
-        for i, cal in enumerate(self.input_calibrators):
+        for cal in self.input_calibrators:
             cal.finish_calibrate()
-            self.input_calibrators[i] = cal.quantizer
         wm = self.weight_manager
-        parts = []
-        for i, (cal, chunk) in enumerate(zip(self.weight_calibrators, wm.iter_list())):
-            parts.append(cal.finish_calibrate(chunk.contiguous()))
-            self.weight_calibrators[i] = cal.quantizer
+        parts = [cal.finish_calibrate(chunk.contiguous()) for cal, chunk in zip(self.weight_calibrators, wm.iter_list())]
         if self.seg_mode == "input":
             if self.packed:
                 wm.weight_tensor = torch.cat([p.reshape(wm.out_features, -1) for p in parts], dim=1).contiguous()
@@ -349,9 +370,46 @@ class SmoothOptimizer(BaseOptimizer):
                 wm.weight_tensor = torch.cat(parts, dim=1).contiguous()
         else:
             wm.replace_with_segments_layout(torch.stack(parts, dim=0), packed=self.packed)
-        self.max_x, self.max_w = None, None
         self.has_calibrated = True
         self.make_scale_tensor()
+        if not self.search_alpha:      # a search still needs the calibrators and the traced maxima (:492-493)
+            self.input_calibrators = [c.quantizer for c in self.input_calibrators]
+            self.weight_calibrators = [c.quantizer for c in self.weight_calibrators]
+            self.max_x, self.max_w = None, None
+
+    # ---- alpha search (:523-572) --------------------------------------------------------------------
+    def search_step(self, errs, origin_weight):
+        """Record this candidate's per-chunk errors, move every chunk to its next candidate and reset the
+        optimizer onto `origin_weight`.  True when the search is over."""
+        assert len(errs) == self.chunks, "errlist length must be chunks"
+        for i, err in enumerate(errs):
+            if err < self.opt_err[i]:
+                self.opt_err[i], self.opt_alpha[i] = err, self.alpha[i]
+            if self.verbose:
+                print(f"Chunk {i}: current err={err:.4f}, best err={self.opt_err[i]:.4f}, best alpha={self.opt_alpha[i]:.4f}")
+        self.alpha = [c.popleft() for c in self.candidate_alphas]
+        self._reset(origin_weight)
+        if all(len(c) == 0 for c in self.candidate_alphas):
+            self._finish_search()
+            return True
+        return False
+
+    def _finish_search(self):
+        if self.verbose:
+            print(f"Best alphas found: {self.opt_alpha}")
+        self.alpha = self.opt_alpha
+        del self.opt_alpha, self.opt_err, self.candidate_alphas
+        self.search_alpha = False
+
+    def _reset(self, origin_weight):
+        old = self.weight_manager
+        self.weight_manager = WeightSegmentTensorManager(origin_weight.clone(), seg_mode=self.seg_mode, segments=self.chunks,
+                                                         segment_size=self.chunksizes[0], segment_sizes=self.chunksizes)
+        for cal in list(self.input_calibrators) + list(self.weight_calibrators):
+            cal.reset()
+        self.has_smoothed = self.has_calibrated = False
+        self.scale_tensor, self._fused = None, None
+        del old
 
     # ---- forward -------------------------------------------------------------------------------
     def forward(self, input_manager):
@@ -420,3 +478,198 @@ class SmoothOptimizer(BaseOptimizer):
     def _move(self, device):
         super()._move(device)
         self.s = [None if s is None else s.to(device) for s in self.s]
+
+
+@OptimizerRegistry.register("svd")
+class SVDOptimizer(SmoothOptimizer):
+    """SmoothOptimizer plus a 16-bit low-rank branch (segquant/optimum/optimizer.py:575-731, the SVDQuant
+    decomposition every W4A8 recipe of the reference uses: config/flux/dit/intw4a8.yaml:49-75).
+
+    After smoothing, every weight chunk W_i (out_i, in_i) is split as W_i^T = L1_i L2_i + R_i with
+    L1_i = U[:, :r] diag(sigma[:r]) (in_i, r), L2_i = V^T[:r] (r, out_i) from an SVD taken in `precision`
+    (float64 or float32, :659-687); only the residual R_i is quantised.  The forward adds the low-rank product
+    of the smoothed activations to the quantised GEMM's output: y = Q(x / s) Q(R)^T + (x / s) L1 L2.
+
+    Real-quant path (fused_forward): the quantised part is the fused quantise + tcgen05 GEMM (smoothing inside
+    the quantise kernel, bias in the epilogue); the low-rank part runs as two plain library GEMMs in the
+    activation dtype, x @ (L1 / s) -- the smoothing folded into L1 once at calibration, so no smoothed copy of
+    x is ever made -- then an accumulate of h @ L2 into y.  The activations of that branch are NOT quantised,
+    as in the reference's real path (its kernels leave their input untouched).
+
+    Fake path (real_quant=False): the reference's call_func overwrites the smoothed chunks with their
+    fake-quantised values before the low-rank product reads them (:120-121, then :729-731), so its CPU path
+    feeds the low-rank branch quantised activations.  That behaviour is kept here so that real_quant=False
+    reproduces the reference's CPU numbers."""
+
+    def __init__(self, seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                 real_quant=False, dual_scale=False, kernel_type=None, alpha=0.5, low_rank=32, search_alpha_config=None,
+                 verbose=False, **kwargs):
+        super().__init__(seg_mode, chunks, chunksizes, weight_manager, input_calibrators, weight_calibrators,
+                         real_quant, dual_scale, kernel_type, alpha, search_alpha_config, verbose)
+        self.low_rank = int(low_rank)
+        self.l1s, self.l2s = [None] * chunks, [None] * chunks
+        self.has_svd = False
+        self.precision = kwargs.get("precision", "float64")
+        if self.precision not in ("float32", "float64"):
+            raise ValueError(f"Unsupported precision: {self.precision}. Use 'float32' or 'float64'.")
+
+    def __repr__(self):
+        head = (f"SVDOptimizer(alpha={self.alpha}, low_rank={self.low_rank}, kernel={self.kernel_type}\n" if self.real_quant
+                else f"SVDOptimizer(alpha={self.alpha}, low_rank={self.low_rank}\n")
+        iq = ",\n      ".join(repr(c) for c in self.input_calibrators)
+        wq = ",\n      ".join(repr(c) for c in self.weight_calibrators)
+        return f"{head}    input_quantizers=[\n      {iq}\n  ],\n    weight_quantizers=[\n      {wq}\n  ]\n)"
+
+    def _svd_w(self):
+        assert self.has_smoothed, "SVDOptimizer: linear is not smoothed"
+        work = getattr(torch, self.precision)
+        l1s, l2s = [], []
+        for chunk in self.weight_manager.iter_list():
+            wt = chunk.t().to(work)                                   # (in_i, out_i)
+            u, sig, vt = torch.linalg.svd(wt, full_matrices=False)
+            if u.shape[1] < self.low_rank or vt.shape[0] < self.low_rank:
+                raise ValueError(f"Low-rank dimension {self.low_rank} exceeds layer dimensions {u.shape[1]} and {vt.shape[0]}.")
+            us = u[:, :self.low_rank] * sig[:self.low_rank]
+            vr = vt[:self.low_rank]
+            l1s.append(us.to(device=chunk.device, dtype=chunk.dtype))
+            l2s.append(vr.to(device=chunk.device, dtype=chunk.dtype))
+            chunk.copy_((wt.to(torch.float64) - (us @ vr).to(torch.float64)).to(chunk.dtype).t())
+        uniform = len({tuple(t.shape) for t in l1s}) == 1
+        self.l1s = torch.stack(l1s) if uniform else l1s               # (S, in_i, r)
+        self.l2s = torch.stack(l2s) if uniform else l2s               # (S, r, out_i)
+
+    def smooth(self):
+        super().smooth()
+        self._svd_w()
+        self.has_svd = True
+
+    def calibrate(self, input_manager):
+        assert self.has_svd, "SVDOptimizer: linear is not svd"
+        super().calibrate(input_manager)
+
+    def _reset(self, origin_weight):
+        super()._reset(origin_weight)
+        self.l1s, self.l2s = [None] * self.chunks, [None] * self.chunks
+        self.has_svd = False
+
+    @staticmethod
+    def _low_rank_mul(chunks, l1s, l2s):
+        """(S, ..., in_i) x (S, in_i, r) x (S, r, out_i) -> (S, ..., out_i)."""
+        S, lead = chunks.shape[0], chunks.shape[1:-1]
+        x3 = chunks.reshape(S, -1, chunks.shape[-1])
+        out = torch.bmm(torch.bmm(x3, l1s.to(x3.dtype)), l2s.to(x3.dtype))
+        return out.reshape(S, *lead, out.shape[-1])
+
+    def forward(self, input_manager):
+        """Un-summed per-segment outputs, quantised product plus low-rank product per chunk."""
+        if not input_manager.uniform and self.seg_mode == "input":
+            raise NotImplementedError("chunked outputs need equal segments; use forward(x) (fused)")
+        chunks = torch.stack(self._smoothed(input_manager))
+        if self.real_quant:
+            return self.call_func(chunks, self.weight_manager.iter_view()) + self._low_rank_mul(chunks, self.l1s, self.l2s)
+        # the reference's CPU path: the low-rank branch sees the fake-quantised chunks (see the class docstring)
+        fake = torch.stack([q.quantize(chunks[i]) for i, q in enumerate(self.input_calibrators)])
+        return segmented_matmul(fake, self.weight_manager.iter_view()) + self._low_rank_mul(fake, self.l1s, self.l2s)
+
+    # ---- fused real-quant forward ----------------------------------------------------------------------
+    def _build_fused(self):
+        wm = self.weight_manager
+        N, K, S = wm.out_features, wm.in_features, self.chunks
+        dev = wm.device()
+        iq = self._input_quantizer()
+        dynamic = bool(iq.dynamic)
+        if getattr(self._weight_quantizer(), "group_size", None):
+            raise RuntimeError("SVDOptimizer: group-wise weight scales are not supported")
+        sw = self.scale_tensor[-1]
+        sx = self.scale_tensor[0].reshape(-1).contiguous()
+        sxn = self.scale_tensor[1].reshape(-1).contiguous() if self.dual_scale else None
+        if not dynamic and sx.numel() != S:
+            raise RuntimeError("static per-token activation scales are only served by forward(x, chunked=True)")
+        s_all = [s.to(device=dev, dtype=torch.float32).contiguous() for s in self.s]
+        l1 = [t.to(dev) for t in (self.l1s.unbind(0) if isinstance(self.l1s, torch.Tensor) else self.l1s)]
+        l2 = [t.to(dev) for t in (self.l2s.unbind(0) if isinstance(self.l2s, torch.Tensor) else self.l2s)]
+        r = self.low_rank
+        if self.seg_mode == "input":
+            sw_t, strides = (sw.reshape(S).contiguous(), (0, 1, 0, 0)) if sw.numel() == S else (sw.reshape(S, N).contiguous(), (0, N, 0, 1))
+            # low-rank branch over all K-segments at once: x [M, K] @ blockdiag_i(L1_i / s_i) [K, S r] -> h, then
+            # h @ vstack_i(L2_i) [S r, N]; the block diagonal costs S x the multiplications of the dense factors,
+            # which is nothing next to the main GEMM (r = 32..64)
+            b = wm.bounds
+            l1_bd = torch.zeros((K, S * r), dtype=torch.float32, device=dev)
+            for i in range(S):
+                l1_bd[b[i]:b[i + 1], i * r:(i + 1) * r] = l1[i].float() / s_all[i].unsqueeze(1)
+            self._fused = dict(mode="input", bounds=b, sx=sx, sx_neg=sxn, sw=sw_t, sw_strides=strides, dynamic=dynamic,
+                               wq=wm.weight_tensor.reshape(1, N, -1), N=N, smooth=torch.cat(s_all).contiguous(),
+                               l1=l1_bd, l2=torch.cat([t.float() for t in l2], dim=0).contiguous(), lr_cache={})
+        else:
+            n = N // S
+            wq = wm.weight_tensor.reshape(S, n, -1)
+            per = []
+            for i in range(S):
+                sw_i, strides = ((sw.reshape(S)[i:i + 1].contiguous(), (0, 0, 0, 0)) if sw.numel() == S
+                                 else (sw.reshape(S, n)[i].contiguous(), (0, 0, 0, 1)))
+                per.append(dict(sx=sx[i:i + 1].contiguous() if not dynamic else sx, sx_neg=None if sxn is None else sxn[i:i + 1].contiguous(),
+                                sw=sw_i, sw_strides=strides, wq=wq[i:i + 1], smooth=s_all[i]))
+            l1_cat = torch.cat([l1[i].float() / s_all[i].unsqueeze(1) for i in range(S)], dim=1).contiguous()   # (K, S r)
+            self._fused = dict(mode="weight", per=per, N=N, n=n, K=K, dynamic=dynamic, l1=l1_cat,
+                               l2=[t.float().contiguous() for t in l2], lr_cache={})
+
+    def _lr(self, f, dtype):
+        """The low-rank factors in the activation dtype (cast once per dtype)."""
+        if dtype not in f["lr_cache"]:
+            l2 = f["l2"]
+            f["lr_cache"][dtype] = (f["l1"].to(dtype), [t.to(dtype) for t in l2] if isinstance(l2, list) else l2.to(dtype))
+        return f["lr_cache"][dtype]
+
+    def _smooth_arg(self, smooth, x, dynamic):
+        # the dynamic kernel calibrates on round_dtype(x / round_dtype(s)), the tensor the reference's per-token
+        # calibration sees; the static kernel divides in fp32
+        return smooth.to(x.dtype).float().contiguous() if dynamic and x.dtype != torch.float32 else smooth
+
+    def fused_forward(self, x, bias=None, out=None):
+        if not self.real_quant:
+            raise RuntimeError("fused_forward is the real-quant path")
+        if self._fused is None:
+            self._build_fused()
+        f = self._fused
+        r = self.low_rank
+        lead, K = x.shape[:-1], x.shape[-1]
+        x2 = x.reshape(-1, K)
+        l1, l2 = self._lr(f, x.dtype)
+        if f["mode"] == "input":
+            y = ops.seg_linear(self.kernel_type, x if out is not None else x2, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"],
+                               sx_neg=f["sx_neg"], dynamic=f["dynamic"], sw_strides=f["sw_strides"], bias=bias,
+                               smooth=self._smooth_arg(f["smooth"], x, f["dynamic"]), out=out)
+            y2 = y.reshape(-1, f["N"]) if y.is_contiguous() else None
+            h = x2 @ l1
+            if y2 is not None:
+                y2.addmm_(h, l2)
+            else:                                   # a strided (B, M, N) output view: one accumulate per batch entry
+                h3 = h.view(*y.shape[:2], -1)
+                for bidx in range(y.shape[0]):
+                    y[bidx].addmm_(h3[bidx], l2)
+            return y if out is not None else y.reshape(*lead, f["N"])
+        # N-segments: chunk i smooths x with its own s_i, writes columns [i n, (i+1) n) and adds its own low-rank product
+        if f["dynamic"]:
+            raise RuntimeError("SVDOptimizer: dynamic activation scales with N-segments are not supported by the fused forward")
+        x3 = x.reshape(1, -1, K) if x.dim() != 3 else x
+        y = out if out is not None else torch.empty((*x3.shape[:2], f["N"]), dtype=x.dtype, device=x.device)
+        n = f["n"]
+        h = x2 @ l1                                                     # (M, S r): every chunk's hidden in one GEMM
+        for i, c in enumerate(f["per"]):
+            yi = y[..., i * n:(i + 1) * n]
+            ops.seg_linear(self.kernel_type, x3, c["wq"], n, [0, K], c["sx"], c["sw"], sx_neg=c["sx_neg"],
+                           sw_strides=c["sw_strides"], bias=None if bias is None else bias[i * n:(i + 1) * n],
+                           smooth=c["smooth"], out=yi)
+            hi = h[:, i * r:(i + 1) * r].view(*y.shape[:2], r)
+            for bidx in range(y.shape[0]):
+                yi[bidx].addmm_(hi[bidx], l2[i])
+        return y if out is not None else y.reshape(*lead, f["N"])
+
+    def _move(self, device):
+        super()._move(device)
+        if isinstance(self.l1s, torch.Tensor):
+            self.l1s, self.l2s = self.l1s.to(device), self.l2s.to(device)
+        else:
+            self.l1s = [None if t is None else t.to(device) for t in self.l1s]
+            self.l2s = [None if t is None else t.to(device) for t in self.l2s]

@@ -1,11 +1,10 @@
 """Generate the golden fixtures in this directory by running the REFERENCE's own Python code.
 
-    python tests/golden/make_golden.py [<reference checkout>]
+    python tests/golden/make_golden.py [<reference checkout> [fixture name ...]]
 
-The reference (OptiSys-ZJU/segquant) is imported from its read-only checkout; nothing of it is
-copied.  `import segquant` would JIT-build its CUDA/CUTLASS extensions, so the package module is
-pre-registered with only its __path__, and the four real-quant loaders are replaced by stubs
-without GEMM functions -- SegmentLinear then takes its fake-quant branch
+The reference (OptiSys-ZJU/segquant) is imported from its read-only checkout (the argument, or the
+SEGQUANT_REFERENCE environment variable) by oracle/reference_loader.py with stub extension loaders;
+nothing of it is copied.  SegmentLinear then takes its fake-quant branch
 (segquant/layers/SegmentLinear.py:105-113), which is the reference's CPU path.  The fp8 round trip
 uses the reference's own fake_e4m3fy C++ built into oracle/_ref/ (oracle/build_ref.py).
 
@@ -15,7 +14,6 @@ tests/test_gpu_parity.py checks the CUDA path against them on the GPU.
 """
 import os
 import sys
-import types
 
 import numpy as np
 import torch
@@ -27,27 +25,11 @@ sys.path.insert(0, REPO)
 
 def import_reference(root):
     from oracle.build_ref import load_prebuilt
-    fp8_ext = load_prebuilt()
-    if fp8_ext is None:
-        raise SystemExit("oracle/_ref is not built: run `python oracle/build_ref.py` first")
-    sys.path.insert(0, root)
-    pkg = types.ModuleType("segquant")
-    pkg.__path__ = [os.path.join(root, "segquant")]
-    sys.modules["segquant"] = pkg
-    import segquant.utils.extension as ext
-
-    class _NoKernels:
-        pass
-
-    ext.load_fake_quant_fp8_ext = lambda verbose=False, required=False: fp8_ext
-    ext.load_real_quant_fp8_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wfpe4m3Afpe4m3",))
-    ext.load_real_quant_int8_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wint8Aint8",))
-    ext.load_real_quant_int4_ext = lambda verbose=False, required=False: (_NoKernels(), ("Wint4Aint4",))
-    ext.load_real_quant_mix_ext = lambda verbose=False, required=False: (_NoKernels(), tuple(ext.supported_type))
-    import segquant.quantizers.quantizer as q
-    q.load_fake_quant_fp8_ext = ext.load_fake_quant_fp8_ext
-    from segquant.layers.SegmentLinear import SegmentLinear
-    return SegmentLinear, q
+    if load_prebuilt() is None:
+        raise SystemExit("oracle/_ref is not built: run `python oracle/build_ref.py <reference checkout>` first")
+    from oracle.reference_loader import import_reference as imp
+    ref = imp("stub", root)
+    return ref.SegmentLinear, ref.quantizer
 
 
 def t2n(t):
@@ -146,6 +128,53 @@ def gen_smooth_int8(SegmentLinear, seed=6, M=80, K=256, N=64, S=4, mode="input")
                 w_fake=t2n(lin.optimizer.weight_manager.weight_tensor))
 
 
+def gen_svd_w4a8(SegmentLinear, seed=8, M=64, K=256, N=96, S=2, mode="input", dynamic=False, low_rank=16):
+    """The W4A8 recipe of config/flux/dit/intw4a8.yaml:49-75 at toy size (AMax instead of GPTQ calibration): SVDOptimizer,
+    int4 per-output-channel weights on the SVD residual, int8 activations (static per segment, or dynamic per token).
+    `y` is the reference's CPU (fake-quant) output; l1s / l2s / s / w_fake let a test rebuild what the real-quant path
+    computes (low-rank branch on the unquantised smoothed activations)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[:, torch.randperm(K, generator=g)[:5]] *= 15.0
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    in_args = {"real_quant": False, "axis": -1, "dynamic": True} if dynamic else {"real_quant": False, "axis": None}
+    lin = SegmentLinear(K, N, bias=True, seg_mode=mode, chunks=S, custom_weight_tensor=w.clone(),
+                        custom_bias_tensor=b.clone(), input_quant_type="int8", weight_quant_type="int4",
+                        input_quant_args=in_args, weight_quant_args={"real_quant": False, "axis": 1},
+                        opt_type="svd", opt_kwargs={"alpha": 0.5, "low_rank": low_rank, "precision": "float64"},
+                        calib_type="amax", calib_kwargs={}, device="cpu")
+    lin.trace(x.clone())
+    lin.smooth()
+    lin.calibrate(x.clone())
+    lin.finish_calibrate()
+    y = lin(x.clone())
+    opt = lin.optimizer
+    sx, sw = opt.scale_tensor
+    return dict(x=t2n(x), w=t2n(w), b=t2n(b), y=t2n(y), sx=t2n(sx), sw=t2n(sw), s=t2n(torch.stack([v.float() for v in opt.s])),
+                l1s=t2n(opt.l1s), l2s=t2n(opt.l2s), chunks=np.int32(S), low_rank=np.int32(low_rank),
+                w_fake=t2n(opt.weight_manager.weight_tensor))
+
+
+def gen_quantize_toy(root, search):
+    """The reference's own quantize() (segquant/torch/quantization.py:259-425) on tests/golden/toy_model.py, CPU fake path,
+    no segmentation (the pattern detector is not exercised): outputs of the quantised model plus the alphas it settled on."""
+    sys.path.insert(0, HERE)
+    from toy_model import ToyBlock, toy_batches, toy_config
+    from segquant.config import Calibrate, DType, Optimum
+    from segquant.torch.quantization import quantize
+    model = ToyBlock()
+    batches = toy_batches()
+    x, c = batches[0][0]
+    y_float = model(x, c)
+    qm = quantize(model, batches, toy_config(DType, Optimum, Calibrate, search=search))
+    y = qm(x.clone(), c.clone())
+    alphas = np.array([qm.to_q.optimizer.alpha[0], qm.ff[2].optimizer.alpha[0], qm.norm_lin.optimizer.alpha[0]], np.float64)
+    return dict(y=t2n(y), y_float=t2n(y_float), alphas=alphas, replaced=np.array(
+        [type(m).__name__ == "SegmentLinear" for m in (qm.norm_lin, qm.to_q, qm.to_k, qm.to_v, qm.ff[0], qm.ff[2], qm.proj_out)]),
+        sx_to_q=t2n(qm.to_q.optimizer.scale_tensor[0]), sw_ff2=t2n(qm.ff[2].optimizer.scale_tensor[1]))
+
+
 def gen_quantizer_vectors(q, seed=4):
     """Scale definitions and fake-quant outputs straight from the reference's quantizer classes."""
     g = torch.Generator().manual_seed(seed)
@@ -191,7 +220,9 @@ def gen_quantizer_vectors(q, seed=4):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SEGQUANT_REFERENCE")
+    if not root:
+        raise SystemExit("usage: make_golden.py <reference checkout>  (or set SEGQUANT_REFERENCE)")
     torch.set_num_threads(1)  # deterministic reductions
     SegmentLinear, q = import_reference(root)
     fixtures = {
@@ -201,8 +232,16 @@ def main():
         "quantizers": gen_quantizer_vectors(q),
         "smooth_input_seg_int8": gen_smooth_int8(SegmentLinear, mode="input"),
         "smooth_weight_seg_int8": gen_smooth_int8(SegmentLinear, seed=7, S=2, mode="weight"),
+        "svd_w4a8_input_seg": gen_svd_w4a8(SegmentLinear),
+        "svd_w4a8_dynamic": gen_svd_w4a8(SegmentLinear, seed=9, S=1, mode="weight", dynamic=True),
+        "svd_w4a8_weight_seg": gen_svd_w4a8(SegmentLinear, seed=10, N=128, S=2, mode="weight"),
+        "quantize_toy_smooth": gen_quantize_toy(root, search=False),
+        "quantize_toy_search": gen_quantize_toy(root, search=True),
     }
+    only = set(sys.argv[2:])
     for name, d in fixtures.items():
+        if only and name not in only:
+            continue
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **d)
         print(f"wrote {path} ({os.path.getsize(path) / 1024:.1f} KB): {sorted(d)}")

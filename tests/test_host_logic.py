@@ -214,6 +214,83 @@ def test_smooth_optimizer_equals_reference(golden, name, mode, chunks):
     y = lin(x)
     assert torch.equal(x, x0)
     assert torch.allclose(y, torch.from_numpy(g["y"]), rtol=1e-5, atol=1e-5)
-    with pytest.raises(NotImplementedError):
-        SegmentLinear(8, 8, input_quant_type="int8", weight_quant_type="int8", opt_type="smooth",
-                      opt_kwargs={"search_alpha_config": {"enable": True, "min": 0.1, "max": 0.9, "step": 0.1}}, device="cpu")
+
+
+# ---------------------------------------------------------------------------------------------
+# SVDOptimizer (low-rank branch) and SmoothOptimizer's alpha search
+# ---------------------------------------------------------------------------------------------
+def _svd_layer(g, mode, chunks, dynamic=False, real=False, device="cpu", **opt):
+    x, w, b = (torch.from_numpy(g[k]) for k in "xwb")
+    in_args = {"real_quant": real, "axis": -1, "dynamic": True} if dynamic else {"real_quant": real, "axis": None}
+    lin = SegmentLinear(w.shape[1], w.shape[0], bias=True, seg_mode=mode, chunks=chunks, custom_weight_tensor=w.to(device),
+                        custom_bias_tensor=b.to(device), input_quant_type="int8", weight_quant_type="int4", input_quant_args=in_args,
+                        weight_quant_args={"real_quant": real, "axis": 1}, opt_type="svd",
+                        opt_kwargs=dict({"alpha": 0.5, "low_rank": int(g["low_rank"]), "precision": "float64"}, **opt), device=device)
+    x = x.to(device)
+    lin.trace(x)
+    lin.smooth()
+    lin.calibrate(x)
+    lin.finish_calibrate()
+    return lin, x
+
+
+@pytest.mark.parametrize("name,mode,dynamic", [("svd_w4a8_input_seg", "input", False), ("svd_w4a8_dynamic", "weight", True),
+                                               ("svd_w4a8_weight_seg", "weight", False)])
+def test_svd_optimizer_fake_path_equals_reference(golden, name, mode, dynamic):
+    """opt_type="svd" with real_quant=False reproduces the reference's CPU output, its smoothing vector, the product of
+    its low-rank factors (the factors themselves are only defined up to the sign of each singular pair) and the
+    fake-quantised residual weight."""
+    g = golden(name)
+    lin, x = _svd_layer(g, mode, int(g["chunks"]), dynamic)
+    opt = lin.optimizer
+    assert np.allclose(torch.stack(opt.s).numpy(), g["s"], rtol=1e-6)
+    prod = torch.bmm(opt.l1s, opt.l2s).numpy()
+    want = np.matmul(g["l1s"], g["l2s"])
+    assert np.abs(prod - want).max() <= 1e-6 * np.abs(want).max() + 1e-7
+    assert opt.l1s.shape == g["l1s"].shape and opt.l2s.shape == g["l2s"].shape
+    assert np.allclose(opt.weight_manager.weight_tensor.numpy(), g["w_fake"], atol=1e-6)
+    x0 = x.clone()
+    y = lin(x).numpy()
+    assert torch.equal(x, x0)
+    assert np.abs(y - g["y"]).max() <= 2e-5 * np.abs(g["y"]).max()
+    parts = lin(x, chunked=True)
+    y2 = (parts.sum(0) if mode == "input" else parts.movedim(0, -2).reshape(x.shape[0], -1)) + lin.bias_data
+    assert np.abs(y2.numpy() - y).max() <= 1e-5
+    assert "SVDOptimizer" in repr(lin)
+
+
+def test_smooth_alpha_search_life_cycle(golden):
+    """search_alpha_config: candidates are tried in order, the best alpha per chunk is kept, the weight is restored
+    between candidates, and (as in the reference) the last candidate of the range is never evaluated."""
+    g = golden("smooth_input_seg_int8")
+    x, w, b = (torch.from_numpy(g[k]) for k in "xwb")
+    lin = SegmentLinear(w.shape[1], w.shape[0], bias=True, seg_mode="input", chunks=4, custom_weight_tensor=w, custom_bias_tensor=b,
+                        input_quant_type="int8", weight_quant_type="int8", input_quant_args={"real_quant": False, "axis": None},
+                        weight_quant_args={"real_quant": False, "axis": 1}, opt_type="smooth",
+                        opt_kwargs={"alpha": 0.5, "search_alpha_config": {"enable": True, "min": 0.2, "max": 0.8, "step": 0.2}}, device="cpu")
+    opt = lin.optimizer
+    assert opt.search_alpha and opt.alpha == [pytest.approx(0.2)] * 4
+    lin.trace(x)
+    tried, done = [], False
+    while not done:
+        tried.append(opt.alpha[0])
+        lin.smooth()
+        lin.calibrate(x)
+        lin.finish_calibrate()
+        real = lin.segment_forward(x, w)
+        cur = lin(x, chunked=True)
+        errs = [((r - c) ** 2).mean().item() for r, c in zip(real, cur)]
+        # make chunk 2 prefer the second candidate whatever the data says
+        if len(tried) == 2:
+            errs[2] = -1.0
+        done = opt.search_step(errs, origin_weight=w)
+        assert torch.equal(opt.weight_manager.weight_tensor, w) and not opt.has_smoothed
+    assert [round(a, 6) for a in tried] == [0.2, 0.4, 0.6]            # 0.8 is popped by the step that ends the search
+    assert not opt.search_alpha and opt.alpha[2] == pytest.approx(0.4)
+    lin.smooth()
+    lin.calibrate(x)
+    lin.finish_calibrate()
+    y = lin(x)
+    assert torch.isfinite(y).all() and opt.max_x is None
+    ref = x @ w.t() + b
+    assert torch.nn.functional.cosine_similarity(y.flatten(), ref.flatten(), dim=0) > 0.999
