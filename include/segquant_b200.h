@@ -57,8 +57,8 @@ extern "C" {
 #define SQ_GEMM_W8A8_F8 1   /* Wfpe4m3Afpe4m3  : e4m3 x e4m3  -> fp32                             */
 #define SQ_GEMM_W4A8 2      /* Wint4Aint8      : int8 x int4  -> int32                            */
 
-#define SQ_MAX_SEGS 64
-#define SQ_MAX_PEERS 8      /* most activation-scale segments along K in one call                 */
+#define SQ_MAX_SEGS 64      /* most activation-scale segments along K in one call                 */
+#define SQ_MAX_PEERS 8      /* most peer GPUs' output buffers one sq_gemm call also writes (fused all-gather) */
 
 typedef void* sq_stream_t;  /* a cudaStream_t */
 
@@ -73,6 +73,26 @@ const char* sq_status_string(int status);
    anything; otherwise a code identifying the wait that gave up.  Returns SQ_ERR_CUDA (<0) if
    the device cannot be queried. */
 int64_t sq_device_status(void);
+/* Same read (and clear), as a status: SQ_OK, or SQ_ERR_DEVICE_TIMEOUT with sq_last_error() naming the block and the
+   wait that gave up (the kernel that reported it returned early: its output is incomplete), or SQ_ERR_CUDA.
+   The reference has no counterpart: its CUTLASS kernels have no waits of their own, and a hung launch there ends
+   in the CUDA watchdog or never (real_gemm.cu:300-304 only checks the launch status). */
+int sq_check_device(void);
+/* Limit, in SM cycles, of every bounded wait inside the GEMM kernels launched after this call (process-wide).
+   0 restores the default of 4e9 (about 2 s); accepted range [1e6, 1e12]. */
+int sq_set_wait_limit_cycles(int64_t cycles);
+/* Launches a one-CTA probe kernel that exercises the bounded-wait / abort path on purpose and safely: one warp waits,
+   with the library's wait helper, on a barrier nobody arrives at and gives up after limit_cycles (<= 1e8); a second
+   warp with a 64x longer limit must leave early through the CTA's abort flag.  The kernel returns normally; afterwards
+   sq_device_status() reports (0 << 8 | 9) once.  out_dev[4] (int32, caller-provided): abort flag, return values of the
+   two waits (both 0), and 1 if the second warp left before its own limit.  Test aid; no counterpart in the reference. */
+int sq_wait_probe(int64_t limit_cycles, int32_t* out_dev, sq_stream_t stream);
+/* Process-wide override of the GEMM schedule the host would pick (tuning and test aid; the environment variables
+   SEGQUANT_B200_BN / _CTA2 / _KSUB / _NO_GEMV give the initial values and are read once).  bn: 0 = automatic, or
+   128 / 192 / 256 tile columns; two_cta: -1 = automatic, 0 = one-CTA kernel, 1 = CTA-pair kernel; ksub: 0 = automatic,
+   1 / 2 = 128-byte K sub-tiles per stage of the pair kernel; no_gemv: 1 = never use the skinny-M kernel.
+   Results never depend on the schedule (integer sums are exact, the fp32 steps are the same). */
+int sq_set_gemm_schedule(int32_t bn, int32_t two_cta, int32_t ksub, int32_t no_gemv);
 
 /* ---- activation quantise ------------------------------------------------------------------
  * Replaces real_quantize_scaled_kernel / real_quantize_dual_scaled_kernel

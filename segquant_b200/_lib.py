@@ -26,7 +26,8 @@ SQ_GEMM_W8A8_I8, SQ_GEMM_W8A8_F8, SQ_GEMM_W4A8 = 0, 1, 2
 EXPORTED_SYMBOLS = (
     "sq_version", "sq_last_error", "sq_status_string", "sq_device_status",
     "sq_quantize_act", "sq_quantize_act_dynamic", "sq_norm_quantize_act", "sq_residual_norm_quantize_act", "sq_gated_residual", "sq_quantize_weight", "sq_unpack_int4",
-    "sq_gemm", "sq_gemm_num_units", "sq_seg_linear",
+    "sq_gemm", "sq_gemm_num_units", "sq_seg_linear", "sq_seg_linear_static",
+    "sq_check_device", "sq_set_wait_limit_cycles", "sq_wait_probe", "sq_set_gemm_schedule",
 )
 
 
@@ -144,6 +145,13 @@ def load():
     lib.sq_status_string.restype = ctypes.c_char_p
     lib.sq_status_string.argtypes = [ctypes.c_int]
     lib.sq_device_status.restype = ctypes.c_int64
+    lib.sq_check_device.restype = ctypes.c_int
+    lib.sq_set_wait_limit_cycles.restype = ctypes.c_int
+    lib.sq_set_wait_limit_cycles.argtypes = [ctypes.c_int64]
+    lib.sq_wait_probe.restype = ctypes.c_int
+    lib.sq_wait_probe.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+    lib.sq_set_gemm_schedule.restype = ctypes.c_int
+    lib.sq_set_gemm_schedule.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.sq_quantize_act.restype = ctypes.c_int
     lib.sq_quantize_act.argtypes = [ctypes.POINTER(ActQuantArgs), ctypes.c_void_p]
     lib.sq_quantize_act_dynamic.restype = ctypes.c_int

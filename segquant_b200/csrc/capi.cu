@@ -31,6 +31,9 @@ int unpack_int4(const void* packed, void* out, long long numel, cudaStream_t st)
 int gemm(const sq_gemm_args* a, cudaStream_t st);
 int gemm_num_units(int num_segs, const int* seg_bounds, int group_size);
 long long read_device_status();
+int set_gemm_schedule(int bn, int two_cta, int ksub, int no_gemv);
+int set_wait_limit(long long cycles);
+int wait_probe(long long limit_cycles, int* out_dev, cudaStream_t st);
 
 }  // namespace sq
 
@@ -58,6 +61,36 @@ int64_t sq_device_status(void) {
     const long long v = sq::read_device_status();
     if (v < 0) sq::set_error("sq_device_status: the device could not be queried");
     return v;
+}
+
+int sq_check_device(void) {
+    sq::clear_error();
+    const long long v = sq::read_device_status();
+    if (v < 0) {
+        sq::set_error("sq_check_device: the device could not be queried");
+        return SQ_ERR_CUDA;
+    }
+    if (v != 0) {
+        sq::set_error("a bounded wait inside a kernel ran out: block %lld, wait id %lld (status word 0x%llx); the launch that "
+                      "reported it returned without completing its output", v >> 8, v & 0xff, static_cast<unsigned long long>(v));
+        return SQ_ERR_DEVICE_TIMEOUT;
+    }
+    return SQ_OK;
+}
+
+int sq_set_gemm_schedule(int32_t bn, int32_t two_cta, int32_t ksub, int32_t no_gemv) {
+    sq::clear_error();
+    return sq::set_gemm_schedule(bn, two_cta, ksub, no_gemv);
+}
+
+int sq_set_wait_limit_cycles(int64_t cycles) {
+    sq::clear_error();
+    return sq::set_wait_limit(cycles);
+}
+
+int sq_wait_probe(int64_t limit_cycles, int32_t* out_dev, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::wait_probe(limit_cycles, out_dev, static_cast<cudaStream_t>(stream));
 }
 
 int sq_quantize_act(const sq_act_quant_args* args, sq_stream_t stream) {

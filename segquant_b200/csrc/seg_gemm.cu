@@ -1,6 +1,9 @@
 // Host side of the segmented quantised GEMM: argument validation, schedule choice, TMA descriptors
 // and dispatch to the kernel translation units (seg_gemm_tu_*.cu; device code in seg_gemm_kernels.cuh).
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #include "seg_gemm_params.cuh"
 
@@ -28,6 +31,15 @@ long long read_device_status() {
 #undef SQ_X
     return first;
 }
+
+int wait_probe(long long limit_cycles, int* out_dev, cudaStream_t st) {
+    SQ_REQUIRE(out_dev != nullptr, SQ_ERR_INVALID_ARG, "sq_wait_probe: out_dev is NULL");
+    SQ_REQUIRE(limit_cycles > 0 && limit_cycles <= 100000000ll, SQ_ERR_INVALID_ARG,
+               "sq_wait_probe: limit_cycles must lie in (0, 1e8] (the probe is meant to give up within milliseconds)");
+    return tu_wait_probe<SQ_GEMM_W8A8_I8, false>(limit_cycles, out_dev, st);
+}
+
+int set_wait_limit(long long cycles);
 
 #ifdef SQ_TRACE
 extern "C" int sq_trace_read(long long* out, int n) {
@@ -57,9 +69,38 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
     return fn;
 }
 
+// Encoded descriptors are cached by everything that goes into them: a layer that is called again with the same
+// buffers (a serving loop, a CUDA-graph capture of many layers that share weights) pays a hash lookup instead of a
+// driver call per operand.  A descriptor holds no reference to the memory, so a stale entry is harmless: the key
+// includes the address and every extent.  Bounded: the table is emptied when it reaches kMapCacheMax entries.
+struct MapKey {
+    uint64_t v[9];
+    bool operator==(const MapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = 1469598103934665603ull;
+        for (uint64_t x : k.v) { h ^= x; h *= 1099511628211ull; }
+        return static_cast<size_t>(h);
+    }
+};
+constexpr size_t kMapCacheMax = 8192;
+static std::mutex g_map_mutex;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash>& map_cache() {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> m;
+    return m;
+}
+
 // 3-D uint8 tensor {inner bytes, rows, batch}.
 static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t row_stride,
                     uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows, bool swizzle128, const char* what) {
+    const MapKey key{{reinterpret_cast<uint64_t>(base), inner, rows, batch, row_stride, batch_stride, box_inner, box_rows,
+                      swizzle128 ? 1ull : 0ull}};
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = map_cache().find(key);
+        if (it != map_cache().end()) { *map = it->second; return SQ_OK; }
+    }
     auto fn = get_encode_fn();
     SQ_REQUIRE(fn != nullptr, SQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {inner, rows, batch};
@@ -73,25 +114,67 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
                "cuTensorMapEncodeTiled(%s) failed with CUresult %d (dims %llu x %llu x %llu, strides %llu, %llu)", what,
                static_cast<int>(r), (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch,
                (unsigned long long)row_stride, (unsigned long long)batch_stride);
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (map_cache().size() >= kMapCacheMax) map_cache().clear();
+        map_cache().emplace(key, *map);
+    }
     return SQ_OK;
 }
+
+// Process-wide schedule overrides (tuning and test aids).  The environment variables SEGQUANT_B200_BN=128|192|256,
+// SEGQUANT_B200_CTA2=0|1, SEGQUANT_B200_KSUB=1|2 and SEGQUANT_B200_NO_GEMV=1 are read ONCE, on first use;
+// sq_set_gemm_schedule() changes the choice afterwards.  0 / negative = automatic.
+struct Overrides {
+    int bn = 0;        // 128 / 192 / 256, 0 = automatic
+    int cta2 = -1;     // 0 / 1, -1 = automatic
+    int ksub = 0;      // 1 / 2, 0 = automatic
+    int no_gemv = 0;   // 1: never take the skinny-M kernel
+    long long wait_cycles = 4000000000ll;   // limit of every bounded wait inside the GEMM kernels (SM cycles)
+};
+static Overrides& overrides() {
+    static Overrides ov = [] {
+        Overrides o;
+        if (const char* env = getenv("SEGQUANT_B200_BN")) {
+            const int v = atoi(env);
+            if (v == 128 || v == 192 || v == 256) o.bn = v;
+        }
+        if (const char* env = getenv("SEGQUANT_B200_CTA2")) o.cta2 = atoi(env) ? 1 : 0;
+        if (const char* env = getenv("SEGQUANT_B200_KSUB")) o.ksub = atoi(env) == 1 ? 1 : (atoi(env) == 2 ? 2 : 0);
+        if (const char* env = getenv("SEGQUANT_B200_NO_GEMV")) o.no_gemv = env[0] == '1' ? 1 : 0;
+        return o;
+    }();
+    return ov;
+}
+int set_gemm_schedule(int bn, int two_cta, int ksub, int no_gemv) {
+    SQ_REQUIRE(bn == 0 || bn == 128 || bn == 192 || bn == 256, SQ_ERR_INVALID_ARG, "sq_set_gemm_schedule: bn must be 0, 128, 192 or 256");
+    SQ_REQUIRE(ksub >= 0 && ksub <= 2, SQ_ERR_INVALID_ARG, "sq_set_gemm_schedule: ksub must be 0, 1 or 2");
+    Overrides& o = overrides();
+    o.bn = bn;
+    o.cta2 = two_cta < 0 ? -1 : (two_cta ? 1 : 0);
+    o.ksub = ksub;
+    o.no_gemv = no_gemv > 0 ? 1 : 0;
+    return SQ_OK;
+}
+int set_wait_limit(long long cycles) {
+    SQ_REQUIRE(cycles == 0 || (cycles >= 1000000ll && cycles <= 1000000000000ll), SQ_ERR_INVALID_ARG,
+               "sq_set_wait_limit_cycles: 0 (default) or a value in [1e6, 1e12]");
+    overrides().wait_cycles = cycles == 0 ? 4000000000ll : cycles;
+    return SQ_OK;
+}
+int forced_ksub() { return overrides().ksub; }
+bool gemv_disabled() { return overrides().no_gemv != 0; }
 
 // Schedule choice against wave quantisation.  The persistent grid runs ceil(tiles / slots) rounds
 // (148 CTAs, or 74 CTA pairs each covering twice the rows); a round costs about (bn + fixed) per
 // tile divided by the efficiency of the mode (a single CTA is limited by shared-memory bandwidth,
 // see seg_gemm_2cta.cuh).  Narrow tiles re-read more operands, which the fixed term also stands for.
-// SEGQUANT_B200_BN=128|192|256 and SEGQUANT_B200_CTA2=0|1 force a choice (tuning aids).
 struct Schedule {
     int bn;
     bool two_cta;
 };
 static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind) {
-    int force_bn = 0, force_cta2 = -1;
-    if (const char* env = getenv("SEGQUANT_B200_BN")) {
-        const int v = atoi(env);
-        if (v == 128 || v == 192 || v == 256) force_bn = v;
-    }
-    if (const char* env = getenv("SEGQUANT_B200_CTA2")) force_cta2 = atoi(env) ? 1 : 0;
+    const int force_bn = overrides().bn, force_cta2 = overrides().cta2;
     const int widths[3] = {256, 192, 128};
     Schedule best{256, false};
     double best_cost = 1e300;
@@ -244,6 +327,10 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
             SQ_REQUIRE(a->peer_y_dev[j] != nullptr && reinterpret_cast<uintptr_t>(a->peer_y_dev[j]) % 16 == 0, SQ_ERR_INVALID_ARG,
                        "sq_gemm: peer_y_dev[%d] is NULL or not 16-byte aligned", j);
     }
+    if (a->bias_dev)
+        SQ_REQUIRE(a->bias_dtype == SQ_F32 || a->bias_dtype == SQ_F16 || a->bias_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
+                   "sq_gemm: unknown bias_dtype %d", a->bias_dtype);
+    p.wait_cycles = overrides().wait_cycles;
     // a handful of rows: stream the weights once on the CUDA cores instead of padding 128-row tensor-core tiles
     if (gemv_applies(a, dual)) return launch_gemv(p, a, dual, st);
     const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind);
@@ -254,9 +341,6 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.all_magic = max_unit_k(a->num_segs, a->seg_bounds, a->group_size) <= 224 ? 1 : 0;
     p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
-    if (a->bias_dev)
-        SQ_REQUIRE(a->bias_dtype == SQ_F32 || a->bias_dtype == SQ_F16 || a->bias_dtype == SQ_BF16, SQ_ERR_INVALID_ARG,
-                   "sq_gemm: unknown bias_dtype %d", a->bias_dtype);
 
     CUtensorMap ma, man, mw;
     const uint64_t a_batches = p.a_batched ? a->batch : 1;

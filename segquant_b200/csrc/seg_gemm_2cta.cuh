@@ -57,7 +57,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     return done;
 }
 // Bounded wait with cluster-scope acquire (pairs with arrivals made by the other CTA).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const long long t0 = clock64();
 #pragma unroll 1
@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
         if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((it & 1023u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > 4000000000ll) {
+            if (clock64() - t0 > limit) {
                 atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
                 *abort_flag = 1;
                 __threadfence_block();
@@ -217,7 +217,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
                     const int wk_off = p.w_seg_as_batch ? k_beg : 0;
                     for (int k = k_beg; k < k_end; k += BKS) {
-                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
                         if (lane == 0) {
                             SQ_STAMP(0, 2 * trace_it);
                             const int left = k_end - k;
@@ -261,9 +261,9 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     uint32_t accumulate = 0;
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
                         if (kW4) {
-                            if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
+                            if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
                         }
                         tc_fence_after();
                         if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
@@ -281,7 +281,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             }
                             const uint32_t buf = one_buf ? 0u : (au & 1u);
                             const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
                             tc_fence_after();
                             cur_buf = buf;
                             d_pos = tmem_base + buf * BN;
@@ -317,7 +317,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     }
                                     const uint32_t buf = one_buf ? 0u : (au & 1u);
                                     const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                    if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                                    if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
                                     tc_fence_after();
                                     cur_buf = buf;
                                     d_pos = tmem_base + buf * BN;
@@ -378,7 +378,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
                     for (int kb = k_beg; kb < k_end; kb += BKS) {
-                        if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
                         const int left = k_end - kb;
                         const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;
                         // packed bytes sit in the upper half of the buffer they expand into: pull every chunk into
@@ -397,7 +397,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
-                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
 #pragma unroll
                         for (int jsub = 0; jsub < KSUB; ++jsub) {
                             if (jsub >= nsub) break;
@@ -488,12 +488,12 @@ static int launch_2cta_k(const CUtensorMap& ma, const CUtensorMap& man, const CU
 }
 
 // 256-byte K stages wherever two of them fit in shared memory (all but W4A8 + DualScale).
-// SEGQUANT_B200_KSUB=1 forces 128-byte stages (tuning aid).
+// SEGQUANT_B200_KSUB=1 / sq_set_gemm_schedule(ksub=1) forces 128-byte stages (tuning aid).
 template <int KIND, bool DUAL>
 static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     constexpr bool can2 = Cfg2<KIND, DUAL, 2>::kStagesRaw >= 2;
     bool want2 = can2;
-    if (const char* env = getenv("SEGQUANT_B200_KSUB")) want2 = can2 && atoi(env) != 1;
+    if (forced_ksub() != 0) want2 = can2 && forced_ksub() != 1;
     if constexpr (can2) {
         if (want2) return launch_2cta_k<KIND, DUAL, 2>(ma, man, mw, my, p, st);
     }

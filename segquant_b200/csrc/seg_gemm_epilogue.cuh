@@ -143,7 +143,7 @@ __device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab,
 
             const uint32_t slot = au & (kTabSlots - 1);
             const uint32_t par = (au / kTabSlots) & 1u;
-            if (!mbar_wait(bar_tab_empty + slot * 8, par ^ 1u, abort_flag, kWaitTabEmpty)) return;
+            if (!mbar_wait(bar_tab_empty + slot * 8, par ^ 1u, abort_flag, kWaitTabEmpty, p.wait_cycles)) return;
             uint8_t* sl = tab + slot * kTabSlotBytes;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -268,7 +268,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const OutMaps
 
     for (int u = 0; u < p.units; ++u) {
         const uint32_t slot = au & (kTabSlots - 1);
-        if (!mbar_wait(bar_tab_full + slot * 8, (au / kTabSlots) & 1u, abort_flag, kWaitTabFull)) return false;
+        if (!mbar_wait(bar_tab_full + slot * 8, (au / kTabSlots) & 1u, abort_flag, kWaitTabFull, p.wait_cycles)) return false;
         const uint8_t* sl = tab + slot * kTabSlotBytes;
         float rxm = 1.0f, rxnm = 1.0f;
         if (PER_TOKEN && p.sx_rs != 0) {
@@ -277,7 +277,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmParams& p, const OutMaps
         }
         const uint32_t buf = one_buf ? 0u : (au & 1u);
         const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-        if (!mbar_wait(bar_tmem_full + buf * 8, tph, abort_flag, kWaitTmemFull)) return false;
+        if (!mbar_wait(bar_tmem_full + buf * 8, tph, abort_flag, kWaitTmemFull, p.wait_cycles)) return false;
         tc_fence_after();
         if (threadIdx.x == 128) SQ_STAMP(2, 2 * au);
         SQ_EPI(0);

@@ -102,9 +102,9 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// Bounded wait: gives up after ~4e9 SM cycles (about 2 s), or as soon as another role has raised the
-// abort flag.  (Backing off with nanosleep was measured: no gain for the epilogue, slower hand-offs.)  The timeout uses the SM-local cycle counter: reading %globaltimer costs microseconds.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Bounded wait: gives up after `limit` SM cycles (GemmParams::wait_cycles, 4e9 = about 2 s unless the host changed
+// it), or as soon as another role has raised the abort flag.  (Backing off with nanosleep was measured: no gain for the epilogue, slower hand-offs.)  The timeout uses the SM-local cycle counter: reading %globaltimer costs microseconds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
 #pragma unroll 1
@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 1023u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > 4000000000ll) {
+            if (clock64() - t0 > limit) {
                 atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(blockIdx.x) << 8) | static_cast<unsigned>(code));
                 *abort_flag = 1;
                 __threadfence_block();
@@ -480,7 +480,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
                     const int wk_off = p.w_seg_as_batch ? k_beg : 0;
                     for (int k = k_beg; k < k_end; k += BK) {
-                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
                         if (lane == 0) {
                             SQ_STAMP(0, 2 * trace_it);
                             const uint32_t full = smem_u32(&bar_full[st]);
@@ -515,9 +515,9 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BK) {
                         SQ_FINE(0);
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
                         if (kW4) {
-                            if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt)) { ok = false; break; }
+                            if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
                         }
                         SQ_FINE(1);
                         tc_fence_after();
@@ -533,7 +533,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (kb != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
                             const uint32_t buf = one_buf ? 0u : (au & 1u);
                             const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                            if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                            if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
                             tc_fence_after();
                             cur_buf = buf;
                             d_pos = tmem_base + buf * BN;
@@ -565,7 +565,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                     if (lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
                                     const uint32_t buf = one_buf ? 0u : (au & 1u);
                                     const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                    if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty)) { ok = false; break; }
+                                    if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
                                     tc_fence_after();
                                     cur_buf = buf;
                                     d_pos = tmem_base + buf * BN;
@@ -621,7 +621,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const int st = it % kStages;
                         const uint32_t ph = (it / kStages) & 1u;
                         SQ_CVT(0);
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
                         SQ_CVT(1);
                         const uint8_t* src = smem_gen + (stage_bp(st) - smem_base);
                         uint8_t* dst = smem_gen + (stage_b(st) - smem_base);
@@ -664,7 +664,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (row0 + 32 * i < p.bn) expand_store(lo4[i], i);
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
-                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
                         SQ_CVT(3);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
@@ -724,6 +724,49 @@ template <>
 int launch_gemm<SQ_TU_KIND, SQ_TU_DUAL>(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw,
                                         const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     return two_cta ? launch_2cta<SQ_TU_KIND, SQ_TU_DUAL>(ma, man, mw, my, p, st) : launch<SQ_TU_KIND, SQ_TU_DUAL>(ma, man, mw, my, p, st);
+}
+
+// Stand-alone exercise of the bounded-wait / abort path the GEMM kernels rely on, for a test that must not make a
+// GEMM kernel itself give up: one CTA, two warps.  Warp 0 waits (same mbar_wait helper, same status word) on a barrier
+// nobody ever arrives at, so its wait runs out after `limit` cycles: it records (block << 8 | kWaitProbe), raises the
+// CTA's abort flag and returns false.  Warp 1 waits on a second silent barrier with a 64 times longer limit and must
+// leave early because it sees the abort flag.  Nothing traps and nothing spins without a bound.
+// out[0] = abort flag at exit, out[1] / out[2] = what the two waits returned, out[3] = 1 if warp 1 left before its own limit.
+static __global__ void wait_probe_kernel(long long limit, int* out) {
+    __shared__ __align__(8) uint64_t bar[2];
+    __shared__ int abort_flag_s;
+    __shared__ int res[3];
+    volatile int* abort_flag = &abort_flag_s;
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        mbar_init(smem_u32(&bar[0]), 1);
+        mbar_init(smem_u32(&bar[1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5;
+    const long long t0 = clock64();
+    const bool ok = warp == 0 ? mbar_wait(smem_u32(&bar[0]), 0u, abort_flag, kWaitProbe, limit)
+                              : mbar_wait(smem_u32(&bar[1]), 0u, abort_flag, kWaitProbe + 1, 64 * limit);
+    const long long waited = clock64() - t0;
+    if ((threadIdx.x & 31) == 0) {
+        res[warp] = ok ? 1 : 0;
+        if (warp == 1) res[2] = waited < 32 * limit ? 1 : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        out[0] = abort_flag_s;
+        out[1] = res[0];
+        out[2] = res[1];
+        out[3] = res[2];
+    }
+}
+
+template <>
+int tu_wait_probe<SQ_TU_KIND, SQ_TU_DUAL>(long long limit_cycles, int* out_dev, cudaStream_t st) {
+    wait_probe_kernel<<<1, 64, 0, st>>>(limit_cycles, out_dev);
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
 }
 
 template <>

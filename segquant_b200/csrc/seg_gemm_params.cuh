@@ -25,7 +25,7 @@ constexpr uint32_t kTabSlotBytes = 4096;         // r[2][BN] + rx[2][BM] + bias[
 constexpr uint32_t kTabBytesAll = kTabSlots * kTabSlotBytes;
 
 // status-word codes (low byte = which wait, rest = block index)
-enum WaitCode : int { kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitTabFull = 7, kWaitTabEmpty = 8 };
+enum WaitCode : int { kWaitProbe = 9, kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEmpty = 3, kWaitTmemFull = 4, kWaitCvt = 5, kWaitFullCvt = 6, kWaitTabFull = 7, kWaitTabEmpty = 8 };
 
 constexpr int BM2 = 256;  // tile rows of a CTA pair
 
@@ -62,6 +62,7 @@ struct GemmParams {
     long long peer_rs, peer_co;
     int all_magic;  // every accumulation unit has K <= 224: int32 accumulators stay inside [-2^22, 2^22)
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
+    long long wait_cycles;  // SM cycles after which a bounded wait gives up (default 4e9, about 2 s)
 };
 
 // Output descriptors: this rank's matrix and, for the fused all-gather, the same column range of every
@@ -79,6 +80,10 @@ int launch_gemm(bool two_cta, const CUtensorMap& ma, const CUtensorMap& man, con
 // Reads and clears the status word kernels of that translation unit write when a bounded wait gives up.
 template <int KIND, bool DUAL>
 long long tu_read_status();
+// Launches the wait probe of that translation unit (see wait_probe_kernel in seg_gemm_kernels.cuh).
+template <int KIND, bool DUAL>
+int tu_wait_probe(long long limit_cycles, int* out_dev, cudaStream_t st);
+int forced_ksub();      // seg_gemm.cu: process-wide schedule overrides (0 = automatic)
 #ifdef SQ_TRACE
 template <int KIND, bool DUAL>
 int tu_trace_read(long long* out, int n);

@@ -20,6 +20,8 @@
 
 namespace sq {
 
+bool gemv_disabled();   // seg_gemm.cu: process-wide schedule overrides
+
 constexpr int kGemvCols = 4;        // output columns per warp
 constexpr int kGemvWarps = 8;       // warps per CTA
 constexpr int kGemvSteps = 3;       // 512-byte steps of a weight row whose loads are in flight together
@@ -188,7 +190,7 @@ bool gemv_applies(const sq_gemm_args* a, bool dual) {
     if (a->kind == SQ_GEMM_W4A8 || a->batch != 1 || a->M > kGemvMaxRows || a->acc_dump_dev != nullptr || a->num_peer_outputs != 0 ||
         a->w_seg_as_batch)
         return false;
-    if (getenv("SEGQUANT_B200_NO_GEMV") != nullptr) return false;
+    if (gemv_disabled()) return false;   // SEGQUANT_B200_NO_GEMV=1 or sq_set_gemm_schedule(): tensor-core path only
     const int mr = a->M <= 2 ? 2 : 4;
     if (static_cast<long long>(mr) * a->K * (dual ? 2 : 1) > kGemvMaxSmem) return false;
     return (reinterpret_cast<uintptr_t>(a->xq_dev) % 16 == 0) && (a->xq_row_stride % 16 == 0) &&

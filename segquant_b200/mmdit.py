@@ -244,6 +244,34 @@ class JointBlock:
         return img, txt, pend_img, pend_txt
 
 
+def calibration_calls():
+    """(call, norm_call) for JointBlock.forward that run the FLOAT linears and let each one record its input range."""
+    def calib(layer, x, out=None, pre_act=None):
+        y = layer.calibrate_forward(x if pre_act is None else _ACTS[pre_act](x))
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def calib_norm(layers, x, shift, scale, outs=None, residual=None):
+        if residual is not None:
+            x = _gated_add(x, *residual)
+        n = _modulate(x, shift, scale)
+        return [calib(l, n, o) for l, o in zip(layers, outs or [None] * len(layers))], x
+    return calib, calib_norm
+
+
+def quantized_calls(fused_norm=None):
+    """(call, norm_call) for JointBlock.forward that run the quantized linears; fused_norm: a FusedNorm, or None to run
+    layer_norm / modulation / quantise / gated residual as separate kernels."""
+    def unfused(layers, x, shift, scale, outs=None, residual=None):
+        if residual is not None:
+            x = _gated_add(x, *residual)
+        n = _modulate(x, shift, scale)
+        return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))], x
+    return (lambda layer, x, out=None, pre_act=None: layer(x, out=out, pre_act=pre_act)), (fused_norm or unfused)
+
+
 class SyntheticMMDiT:
     def __init__(self, device, blocks=24, hidden=1536, heads=24, img_tokens=4096, txt_tokens=333, seed=0,
                  dtype=torch.bfloat16, out_proj_segments=1):
@@ -284,17 +312,7 @@ class SyntheticMMDiT:
     def calibrate(self, latents, text, pooled, timestep):
         """One forward of the float model; every linear records its input range and is then quantized."""
         with torch.no_grad():
-            def calib(layer, x, out=None, pre_act=None):
-                y = layer.calibrate_forward(x if pre_act is None else _ACTS[pre_act](x))
-                if out is not None:
-                    out.copy_(y)
-                    return out
-                return y
-            def calib_norm(layers, x, shift, scale, outs=None, residual=None):
-                if residual is not None:
-                    x = _gated_add(x, *residual)
-                n = _modulate(x, shift, scale)
-                return [calib(l, n, o) for l, o in zip(layers, outs or [None] * len(layers))], x
+            calib, calib_norm = calibration_calls()
             y = self._forward(latents, text, pooled, timestep, calib, calib_norm)
             for lin in self.linears():
                 lin.finish()
@@ -305,14 +323,8 @@ class SyntheticMMDiT:
         if not self.calibrated:
             raise RuntimeError("call calibrate() once before running the quantized model")
         with torch.no_grad():
-            def unfused(layers, x, shift, scale, outs=None, residual=None):
-                if residual is not None:
-                    x = _gated_add(x, *residual)
-                n = _modulate(x, shift, scale)
-                return [l(n, out=o) for l, o in zip(layers, outs or [None] * len(layers))], x
-            return self._forward(latents, text, pooled, timestep,
-                                 lambda layer, x, out=None, pre_act=None: layer(x, out=out, pre_act=pre_act),
-                                 self.fused_norm or unfused)
+            call, norm_call = quantized_calls(self.fused_norm)
+            return self._forward(latents, text, pooled, timestep, call, norm_call)
 
     def linear_ops(self, batch):
         """Useful operations 2*M*N*K of one step, summed over every quantized linear."""

@@ -364,6 +364,16 @@ def device_status():
     return int(L.load().sq_device_status())
 
 
+def check_device():
+    """Synchronise and raise SegQuantError(SQ_ERR_DEVICE_TIMEOUT) if a kernel reported a bounded wait that ran out."""
+    L.check(L.load().sq_check_device(), "sq_check_device")
+
+
+def set_gemm_schedule(bn=0, two_cta=-1, ksub=0, no_gemv=0):
+    """Force the GEMM schedule process-wide (0 / -1 = automatic); results do not depend on it.  Test and tuning aid."""
+    L.check(L.load().sq_set_gemm_schedule(int(bn), int(two_cta), int(ksub), int(no_gemv)), "sq_set_gemm_schedule")
+
+
 # ---------------------------------------------------------------------------------------------
 # fused layer forward
 # ---------------------------------------------------------------------------------------------

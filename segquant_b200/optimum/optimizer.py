@@ -650,12 +650,25 @@ class SVDOptimizer(SmoothOptimizer):
                     y[bidx].addmm_(h3[bidx], l2)
             return y if out is not None else y.reshape(*lead, f["N"])
         # N-segments: chunk i smooths x with its own s_i, writes columns [i n, (i+1) n) and adds its own low-rank product
-        if f["dynamic"]:
-            raise RuntimeError("SVDOptimizer: dynamic activation scales with N-segments are not supported by the fused forward")
-        x3 = x.reshape(1, -1, K) if x.dim() != 3 else x
-        y = out if out is not None else torch.empty((*x3.shape[:2], f["N"]), dtype=x.dtype, device=x.device)
         n = f["n"]
         h = x2 @ l1                                                     # (M, S r): every chunk's hidden in one GEMM
+        if f["dynamic"]:
+            # per-token scales are computed inside the quantise kernel, chunk by chunk (each chunk has its own s_i)
+            if out is not None:
+                raise ValueError("out= needs static activation scales")
+            y2 = torch.empty((x2.shape[0], f["N"]), dtype=x.dtype, device=x.device)
+            for i, c in enumerate(f["per"]):
+                yi = ops.seg_linear(self.kernel_type, x2, c["wq"], n, [0, K], c["sx"], c["sw"], sx_neg=c["sx_neg"], dynamic=True,
+                                    sw_strides=c["sw_strides"], bias=None if bias is None else bias[i * n:(i + 1) * n],
+                                    smooth=self._smooth_arg(c["smooth"], x, True))
+                yi.addmm_(h[:, i * r:(i + 1) * r], l2[i])
+                if len(f["per"]) == 1:
+                    y2 = yi
+                else:
+                    y2[:, i * n:(i + 1) * n] = yi
+            return y2.reshape(*lead, f["N"])
+        x3 = x.reshape(1, -1, K) if x.dim() != 3 else x
+        y = out if out is not None else torch.empty((*x3.shape[:2], f["N"]), dtype=x.dtype, device=x.device)
         for i, c in enumerate(f["per"]):
             yi = y[..., i * n:(i + 1) * n]
             ops.seg_linear(self.kernel_type, x3, c["wq"], n, [0, K], c["sx"], c["sw"], sx_neg=c["sx_neg"],

@@ -26,7 +26,7 @@ def test_every_declared_symbol_is_exported(native_lib):
     assert "sq_gemm" in names and "sq_quantize_act" in names and len(names) >= 11
     for n in names:
         assert hasattr(native_lib, n), f"{n} declared in include/segquant_b200.h but not exported"
-    assert set(names) == set(L.EXPORTED_SYMBOLS) | ({"sq_seg_linear_static"} & set(names))
+    assert set(names) == set(L.EXPORTED_SYMBOLS)
 
 
 def test_version_and_status_strings(native_lib):

@@ -497,7 +497,7 @@ def test_smooth_optimizer_real_path_vs_reference_golden(golden, name, mode, chun
     ("f8", 2, 300, 1536, None, 0, True, False),
     ("f8", 3, 64, 512, [0, 256, 512], 0, False, True),
 ])
-def test_skinny_m_path_matches_oracle_and_tensor_core_path(monkeypatch, kind, M, N, K, bounds, group, dual, per_token):
+def test_skinny_m_path_matches_oracle_and_tensor_core_path(kind, M, N, K, bounds, group, dual, per_token):
     gk = {"i8": L.SQ_GEMM_W8A8_I8, "f8": L.SQ_GEMM_W8A8_F8}[kind]
     ok = {"i8": O.GEMM_I8, "f8": O.GEMM_F8}[kind]
     xq, xn, wq, _ = random_operands(kind, M, N, K, seed=11)
@@ -521,11 +521,86 @@ def test_skinny_m_path_matches_oracle_and_tensor_core_path(monkeypatch, kind, M,
                         group_size=group, sw_strides=strides, bias=t(bias), out_dtype=torch.float32)[0].cpu().numpy()
 
     y_skinny = run()
-    monkeypatch.setenv("SEGQUANT_B200_NO_GEMV", "1")
-    y_tc = run()
-    monkeypatch.delenv("SEGQUANT_B200_NO_GEMV")
+    ops.set_gemm_schedule(no_gemv=1)
+    try:
+        y_tc = run()
+    finally:
+        ops.set_gemm_schedule()
     assert max_rel(y_skinny, y_ref) < 1e-5
     assert max_rel(y_tc, y_ref) < 1e-5
     if kind == "i8":
         assert np.array_equal(y_skinny, y_tc)     # integer sums are exact on both paths and the fp32 steps are the same
+    assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# BASELINE config 3 at its stated shapes: W4A8, int4 weights with bf16 group scales (g = 128)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name,N,K,bounds,dual", [
+    ("qkv", 9216, 3072, [0, 1024, 3072], False),
+    ("mlp_up", 12288, 3072, [0, 1024, 3072], False),
+    ("mlp_down", 3072, 12288, [0, 12288], True),
+])
+def test_full_size_config3_w4a8_projections(name, N, K, bounds, dual):
+    """M = 4608 (4096 image + 512 text tokens), X bf16 with K-segments 0:1024 ~ N(0,1) and 1024:3072 ~ N(0,3) (QKV, MLP up) or
+    X = SiLU(N(0,1)) with DualScale (MLP down); weights signed int4 packed two per byte, bf16 group scales of 128 along K;
+    int8 activations, static per segment.  Checks: packed weight bytes and activation bytes of a row sample equal the C
+    oracle's; the fp32 output of 256 rows spread over eight M-tiles (all N columns) within 1e-5 of the oracle's; the whole
+    bf16 output against the fp32 fake-quant path (oracle/fake_path.py arithmetic, evaluated with torch on the GPU):
+    max rel err <= 1e-2 and cosine >= 0.9999."""
+    g = torch.Generator().manual_seed(2)
+    M, G = 4608, 128
+    S = len(bounds) - 1
+    if dual:
+        x = torch.nn.functional.silu(torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    else:
+        x = torch.randn(M, K, generator=g)
+        x[:, 1024:] *= 3.0
+        x = x.to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    xd, wd = x.to(DEV), w.to(DEV)
+    # weights: group scales 7 / amax, kept in bf16 (what the kernel's epilogue reads), packed by the native kernel
+    sw16 = (7.0 / wd.float().view(N, K // G, G).abs().amax(-1)).to(torch.bfloat16).contiguous()            # (N, K/G)
+    sw32 = sw16.float().contiguous()
+    wq = torch.empty(N * K // 2, dtype=torch.uint8, device=DEV)
+    ops.quantize_weight(wd, wq, sw32, L.SQ_Q_INT4, group_size=G)
+    nrows = 64
+    want_w = O.quantize_weight(w[:nrows].float().numpy(), sw32[:nrows].cpu().numpy(), O.Q_INT4, group_size=G)
+    assert np.array_equal(wq[:nrows * K // 2].cpu().numpy(), want_w.reshape(-1))
+    # activations
+    xf = xd.float()
+    if dual:
+        sp, sn = F.dual_scales(x.float(), 127.0, 128.0)
+        sx, sxn = np.array([sp], np.float32), np.array([sn], np.float32)
+    else:
+        sx = np.array([127.0 / xf[:, bounds[s]:bounds[s + 1]].abs().max().item() for s in range(S)], np.float32)
+        sxn = None
+    xq, xqn = ops.quantize_act(xd, bounds, t(sx), t(sxn) if dual else None, L.SQ_Q_INT8)
+    rows = np.concatenate([np.arange(r0, r0 + 32) for r0 in (0, 577, 1154, 1731, 2308, 2885, 3462, M - 32)])
+    rows_t = torch.from_numpy(rows).to(DEV)
+    want_x = O.quantize_act(x[rows].float().numpy(), bounds, sx, sx_neg=sxn, out_kind=O.Q_INT8)
+    if dual:
+        assert np.array_equal(xq[0, rows_t].cpu().numpy().view(np.int8), want_x[0]) and np.array_equal(xqn[0, rows_t].cpu().numpy().view(np.int8), want_x[1])
+    else:
+        assert np.array_equal(xq[0, rows_t].cpu().numpy().view(np.int8), want_x)
+    kw = dict(xq_neg=xqn, sx_neg=t(sxn) if dual else None, group_size=G, sw_strides=(0, 0, 1, K // G))
+    wq3 = wq.view(1, N, K // 2)
+    y32 = ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, t(sx), sw16, out_dtype=torch.float32, **kw)[0]
+    y16 = ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, t(sx), sw16, out_dtype=torch.bfloat16, **kw)[0]
+    assert torch.equal(y16, y32.to(torch.bfloat16))
+    # (1) row sample against the C oracle, on the very bytes the kernel consumed
+    xq_rows = (want_x[0] if dual else want_x)
+    y_ref = O.seg_gemm(O.GEMM_W4A8, xq_rows, wq.cpu().numpy(), bounds, sx, sw32.t().contiguous().cpu().numpy(),
+                       xq_neg=want_x[1] if dual else None, sx_neg=sxn, group_size=G)
+    assert max_rel(y32[rows_t].cpu().numpy(), y_ref) < 1e-5, name
+    # (2) whole output against the fp32 fake-quant path
+    torch.backends.cuda.matmul.allow_tf32 = False
+    sw_g = sw32.unsqueeze(-1)
+    w_fake = (torch.clamp(torch.round(wd.float().view(N, K // G, G) * sw_g), -8, 7) / sw_g).view(N, K)
+    if dual:
+        want = F.seg_linear_fake(xf, w_fake, None, bounds, act="int8", sx_pos=[float(sx[0])], sx_neg=[float(sxn[0])])
+    else:
+        want = F.seg_linear_fake(xf, w_fake, None, bounds, act="int8", sx=[float(v) for v in sx])
+    got, want = y16.float().cpu().numpy(), want.cpu().numpy()
+    assert max_rel(got, want) <= 1e-2 and cosine(got, want) >= 0.9999, (name, max_rel(got, want), cosine(got, want))
     assert ops.device_status() == 0
