@@ -1,23 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the real-quantized segmented linear path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload layer|mmdit|sweep|kernels]
 
-Workload (the configuration the metric is quoted on): the DualScale W8A8 FP8-e4m3 MLP
-down-projection -- X = GELU(Z), Z bf16 [4096, 6144] ~ N(0,1); W bf16 [1536, 6144] ~ N(0, 0.02) with
-per-output-channel e4m3 scales; bias ~ N(0, 0.01); seed 1.  Synthetic data, random-init weights.
-One step = one layer forward on one batch: activation quantise (positive / negative split) +
-dual tcgen05 GEMM + scale / bias / bf16-cast epilogue.
+Headline workload (the same layer at every N): a FLUX-shape W8A8 INT8 SegLinear of the GEMM sweep -- X bf16
+[M=16384, K=12288] in 4 equal K-segments whose magnitudes are drawn log-uniform in [0.25, 32], W bf16 [N=3072, K=12288]
+~ N(0, 0.02) with per-output-channel int8 scales, bf16 output, seed 5.  Synthetic data, random-init weights.
+One step = one layer forward on one batch: activation quantise (per-segment scales) + tcgen05 GEMM + scale / cast
+epilogue.  With N > 1 the layer is COLUMN-SHARDED over the ranks (N/g output columns each, activations replicated)
+and a step also includes the exchange of the output column blocks over NVLink: strong scaling.
 
-Prints ONE JSON line (rank 0).  `value` is useful TOPS = 2*M*N*K*ranks / step time with inputs
-resident in HBM; `e2e` is the same through SegmentLinear.forward with pinned HOST input and a
-device->host read of the output inside the timed region.  With N > 1 every rank runs its own
-batch (batch-data-parallel, no collective on the data path: weak scaling); the column-sharded
-variant with an NCCL all-gather of output slices is timed too and reported under "sharded".
+Prints ONE JSON line (rank 0).  `value` is useful TOPS = 2*M*N*K / step time with inputs resident in HBM; `e2e` is the
+same through the public layer API with pinned HOST input and a device->host read of the output inside the timed region.
+`roofline` describes the dominant kernel (the GEMM) against 2 x the measured bf16 rate, burst and sustained;
+`cpu_baseline` is the reference's own CPU path for the same layer on the box's host cores; `configs` (N = 1) carries
+one compact entry per BASELINE configuration: the INT8 4-segment layer, the DualScale FP8 layer, the three W4A8
+projections and the synthetic MMDiT denoise step.
 
-`--impl reference` times the reference's CPU path for the same layer: the fake-quant
-SegmentLinear forward restated in oracle/fake_path.py with torch CPU kernels on all host
-cores, on a bounded row sample.
+`--impl reference` times the reference's own fake-quant SegmentLinear forward (imported, unmodified, through
+oracle/reference_loader.py; the restatement in oracle/fake_path.py only where the reference package is absent) for the
+headline layer on all host cores.
 """
 import argparse
 import json
@@ -32,19 +34,36 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-M, K, N = 4096, 6144, 1536
-SEED = 1
-ROTATE = 4            # independent layer instances cycled through so that every step's operands come from HBM
-CPU_SAMPLE_ROWS = 1024
+# headline layer: a config[4] sweep point at FLUX shape (MLP down-projection), 4 K-segments
+HM, HK, HN, HS, HSEED = 16384, 12288, 3072, 4, 5
+HEAD_NAME = f"config[4] point: W8A8 INT8 SegLinear M={HM} K={HK} N={HN}, {HS} K-segments (scales log-uniform in [0.25, 32]), bf16 in/out, seed {HSEED}"
+# profiles/seg_gemm2_int8_16384x3072x12288.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline GEMM
+HEAD_TRAFFIC_NCU = None
+HEAD_TRAFFIC_SRC = "profiles/seg_gemm2_int8_16384x3072x12288.md"
 
 
-def make_inputs(seed, m=M, device="cpu"):
-    g = torch.Generator().manual_seed(seed)
-    z = torch.randn(m, K, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    x = torch.nn.functional.gelu(z.float()).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-    b = (torch.randn(N, generator=g, dtype=torch.float32) * 0.01).to(torch.bfloat16)
-    return x.to(device), w.to(device), b.to(device)
+def log_uniform_scales(S, gen):
+    return torch.exp(torch.empty(S).uniform_(-1.386, 3.466, generator=gen))   # [0.25, 32]
+
+
+def headline_tensors(rows=HM, n_rows=None):
+    """(x bf16 [rows, K], w bf16 [N, K]) from the seeded generator; identical on every rank."""
+    g = torch.Generator().manual_seed(HSEED)
+    scale = log_uniform_scales(HS, g)
+    w = (torch.randn(HN, HK, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(rows, HK, generator=g)
+    seg = HK // HS
+    for s in range(HS):
+        x[:, s * seg:(s + 1) * seg] *= scale[s]
+    return x.to(torch.bfloat16), w
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except OSError:
+        return {}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -74,62 +93,127 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 9:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
+
+    def mark(self):
+        return time.perf_counter()
+
+    def summary(self, t0=None, t1=None):
+        rows = [p for (t, p) in self.samples if (t0 is None or t >= t0) and (t1 is None or t <= t1)]
+        sm = sorted(int(s[1]) for s in rows if s[1].isdigit())
+        mx = [int(s[2]) for s in rows if s[2].isdigit()]
+        pw = [float(s[3]) for s in rows if s[3].replace(".", "", 1).isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in rows:
+            for name, v in zip(names, s[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(rows)}
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()   # the exact process started above
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = sorted(int(s[1]) for s in self.samples if s[1].isdigit())
-        mx = [int(s[2]) for s in self.samples if s[2].isdigit()]
-        reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            for name, v in zip(names, s[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(self.samples)}
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU baseline (the reference's fake-quant path, restated)
+# CPU baseline: the reference's own fake-quant path (or its restatement where the package is absent)
 # ---------------------------------------------------------------------------------------------
-def cpu_baseline(steps=3, warmup=1, rows=CPU_SAMPLE_ROWS):
-    from oracle import fake_path as F
+def _import_reference():
+    try:
+        from oracle.reference_loader import find_reference, import_reference
+        if find_reference() is None:
+            return None
+        import contextlib
+        import io
+        with contextlib.redirect_stdout(io.StringIO()):      # the reference prints on import; keep stdout one JSON line
+            return import_reference("stub")
+    except Exception:
+        return None
+
+
+def cpu_headline(runs=5, warmup=2):
+    """The reference's SegmentLinear(real_quant=False).forward for the WHOLE headline layer (all rows, fp32 tensors: the
+    bf16 values up-cast, which is the reference's fp32 CPU path), all host cores, best of `runs` after `warmup`."""
     torch.set_num_threads(os.cpu_count() or 1)
-    x, w, b = make_inputs(SEED, m=rows)
-    x, w, b = x.float(), w.float(), b.float()     # bf16 tensors up-cast: the reference's fp32 path
-    w_fake, _ = F.fake_weight_fp8(w)
-    sp, sn = F.dual_scales(x, 448.0, 448.0)
+    x, w = headline_tensors()
+    x, w = x.float(), w.float()
+    ref = _import_reference()
+    if ref is not None:
+        lin = ref.SegmentLinear(HK, HN, bias=False, seg_mode="input", chunks=HS, custom_weight_tensor=w,
+                                input_quant_type="int8", weight_quant_type="int8",
+                                input_quant_args={"real_quant": False, "axis": None}, weight_quant_args={"real_quant": False, "axis": 1},
+                                opt_type="default", opt_kwargs={}, calib_type="amax", calib_kwargs={}, device="cpu")
+        lin.calibrate(x.clone())
+        lin.finish_calibrate()
+        kind, what = "reference", "the reference's own segquant.layers.SegmentLinear (unmodified package, stub extension loaders), real_quant=False"
+
+        def fwd(xc):
+            return lin(xc)          # writes into xc (optimizer.py:120-121): a fresh copy per run, made outside the timed region
+    else:
+        from oracle import fake_path as F
+        seg = HK // HS
+        bounds = [i * seg for i in range(HS + 1)]
+        w_fake = F.fake_weight_int(w, 127.0)[0]
+        sx = [F.amax_scale(x[:, bounds[s]:bounds[s + 1]], 127.0) for s in range(HS)]
+        kind, what = "port", "oracle/fake_path.py restatement of the reference's fake-quant forward (reference package not importable here)"
+
+        def fwd(xc):
+            return F.seg_linear_fake(xc, w_fake, None, bounds, act="int8", sx=sx)
     times = []
-    for i in range(warmup + steps):
+    with torch.no_grad():
+        for i in range(warmup + runs):
+            xc = x.clone()
+            t0 = time.perf_counter()
+            fwd(xc)
+            dt = time.perf_counter() - t0
+            if i >= warmup:
+                times.append(dt)
+    best = min(times)
+    return {"value": 2.0 * HM * HN * HK / best / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"the whole headline layer (all {HM} rows), fp32 fake-quant forward (per-segment quantise-dequantise + matmul + segment sum), "
+                      f"{what}; best of {runs} runs after {warmup} warm-ups (mean {sum(times) / len(times) * 1e3:.0f} ms)",
+            "ms_per_step": best * 1e3}
+
+
+def cpu_mmdit_block(batch=2):
+    """One fake-quant joint block (hidden 1536, 4096 + 333 tokens) on the host cores, best of 2 after 1 warm-up; the step
+    baseline is this x 24 blocks (extrapolated, embedders and output head ignored)."""
+    from oracle.mmdit_block_cpu import FakeQuantJointBlock
+    torch.set_num_threads(os.cpu_count() or 1)
+    ref = _import_reference()
+    blk = FakeQuantJointBlock(ref=ref)
+    g = torch.Generator().manual_seed(3)
+    img, txt = torch.randn(batch, 4096, 1536, generator=g), torch.randn(batch, 333, 1536, generator=g)
+    c = torch.nn.functional.silu(torch.randn(batch, 1536, generator=g))
+    blk.calibrate(img, txt, c)
+    times = []
+    for i in range(3):
         t0 = time.perf_counter()
-        F.seg_linear_fake(x.clone(), w_fake, b, [0, K], act="fp8", sx_pos=[sp], sx_neg=[sn])
-        dt = time.perf_counter() - t0
-        if i >= warmup:
-            times.append(dt)
-    t = sum(times) / len(times)
-    return {"value": 2.0 * rows * N * K / t / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"first {rows} of {M} rows of the same layer, fp32 fake-quant forward (quantise-dequantise + matmul + bias), "
-                      f"mean of {steps} runs after {warmup} warm-up", "ms_per_step": t * 1e3}
+        blk(img, txt, c)
+        if i >= 1:
+            times.append(time.perf_counter() - t0)
+    return {"one_block_ms": min(times) * 1e3, "step_ms_extrapolated": min(times) * 1e3 * 24, "kind": blk.kind, "cores": torch.get_num_threads(),
+            "sample": f"ONE fake-quant joint block (all 14 linears + joint attention, fp32, batch {batch}) timed on the host cores, x 24 blocks"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cb = cpu_baseline(steps=max(1, args.steps), warmup=max(1, min(args.warmup, 3)))
+    cb = cpu_headline(runs=max(1, args.steps), warmup=max(1, args.warmup))
     line = {
         "impl": "reference", "metric": "seglinear_gemm_tops", "value": cb["value"], "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config[1]: DualScale W8A8 FP8-e4m3 down-projection, M=4096 K=6144 N=1536, seed 1",
-                   "note": "reference's own CPU path (fake-quant SegmentLinear forward) on host cores"},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": HEAD_NAME, "note": "reference's own CPU path (fake-quant SegmentLinear forward) on host cores; "
+                                                  "value from the best timed step"},
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -138,25 +222,10 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------
-# our arm
+# helpers of our arm
 # ---------------------------------------------------------------------------------------------
-def build_layer(x, w, b, device):
-    from segquant_b200.layers.SegmentLinear import SegmentLinear
-    lin = SegmentLinear(K, N, bias=True, seg_mode="weight", chunks=1, custom_weight_tensor=w, custom_bias_tensor=b,
-                        input_quant_type="fpe4m3", weight_quant_type="fpe4m3",
-                        input_quant_args={"real_quant": True, "axis": None, "dual_scale": True},
-                        weight_quant_args={"real_quant": True, "axis": 1},
-                        opt_type="default", opt_kwargs={}, calib_type="amax", calib_kwargs={}, device=device)
-    lin.calibrate(x)
-    lin.finish_calibrate()
-    return lin
-
-
-def run_ours(args):
+def _dist_setup():
     import torch.distributed as dist
-    from segquant_b200 import _lib as L
-    from segquant_b200 import ops
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -166,240 +235,459 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    L.load()
+    return dist, world, rank, dev
 
-    # ---- ROTATE independent layer instances (different seeds per rank and slot)
-    layers, xs = [], []
-    for r in range(ROTATE):
-        x, w, b = make_inputs(SEED + 1000 * rank + r if (rank or r) else SEED, device=dev)
-        layers.append(build_layer(x, w, b, dev))
-        xs.append(x)
+
+def timed(fn, steps, warmup=3):
+    """Mean milliseconds per call of fn over `steps` calls (CUDA events on the current stream), after `warmup` calls."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def split_timed(quant, gemm, steps):
+    """(quantise ms, GEMM ms) per launch: CUDA events around each launch on the launch stream, mean over `steps`."""
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for e in ev:
+        e[0].record()
+        quant()
+        e[1].record()
+        gemm()
+        e[2].record()
+    torch.cuda.synchronize()
+    return (sum(e[0].elapsed_time(e[1]) for e in ev) / steps, sum(e[1].elapsed_time(e[2]) for e in ev) / steps)
+
+
+def layer_bound(M, N, K, in_bytes, out_bytes, w_bytes_per_el, dual, peaks):
+    """Roofline bound of a layer step in ms: max(useful-or-issued ops / tensor peak, algorithmic bytes / HBM bandwidth)."""
+    tensor = 2.0 * peaks["tensor"]
+    ops = 2.0 * M * N * K * (2 if dual else 1)
+    byt = M * K * in_bytes + 2 * M * K * (2 if dual else 1) + N * K * w_bytes_per_el + M * N * out_bytes   # x in, xq out + in, W, y
+    t_tensor, t_hbm = ops / (tensor * 1e12) * 1e3, byt / (peaks["hbm"] * 1e9) * 1e3
+    return ("tensor" if t_tensor >= t_hbm else "hbm"), max(t_tensor, t_hbm)
+
+
+# ---------------------------------------------------------------------------------------------
+# the other BASELINE configurations, one compact entry each (N = 1)
+# ---------------------------------------------------------------------------------------------
+def config_entries(dev, peaks, steps=20):
+    from segquant_b200 import _lib as L
+    from segquant_b200 import ops
+    from segquant_b200.layers.SegmentLinear import SegmentLinear
+    out = {}
+    pk = {"tensor": peaks.get("bf16_tflops") or 1590.0, "hbm": peaks.get("hbm_gbs") or 6650.0}
+    peak8 = 2.0 * pk["tensor"]
+
+    def run_layer(lin, x, kernel_type, dual, rotate):
+        """rotate: independent (layer, x) pairs cycled so operands come from HBM; returns (step ms, quant ms, gemm ms)."""
+        kind, a_kind, _ = ops.KERNELS[kernel_type]
+        fs = []
+        for ln, xx in rotate:
+            ln.optimizer._build_fused()
+            f = ln.optimizer._fused
+            M_, K_ = xx.shape
+            fs.append((f, xx, torch.empty((1, M_, K_), dtype=torch.uint8, device=dev),
+                       torch.empty((1, M_, K_), dtype=torch.uint8, device=dev) if dual else None,
+                       torch.empty((1, M_, f["N"]), dtype=xx.dtype, device=dev), ln.bias_data if ln.bias else None))
+        state = {"i": 0}
+
+        def quant():
+            f, xx, xq, xqn, y, b = fs[state["i"] % len(fs)]
+            ops.quantize_act(xx, f["bounds"], f["sx"], f["sx_neg"], a_kind, out=xq, out_neg=xqn)
+
+        def gemm():
+            f, xx, xq, xqn, y, b = fs[state["i"] % len(fs)]
+            ops.gemm(kind, xq, f["wq"], f["N"], f["bounds"], f["sx"], f["sw"], xq_neg=xqn, sx_neg=f["sx_neg"], group_size=f["group"],
+                     sw_strides=f["sw_strides"], bias=b, out_dtype=xx.dtype, out=y)
+            state["i"] += 1
+
+        def step():
+            quant()
+            gemm()
+        ms = timed(step, steps)
+        q_ms, g_ms = split_timed(quant, gemm, steps)
+        return ms, q_ms, g_ms
+
+    # ---- config[0]: INT8, 4 K-segments, fp32 in / out, M=4096 K=N=1536, seed 0
+    M, K, N, S = 4096, 1536, 1536, 4
+    rot = []
+    for r in range(4):
+        g = torch.Generator().manual_seed(0 + 100 * r)
+        x = torch.randn(M, K, generator=g)
+        for s, f_ in enumerate([0.5, 1.0, 4.0, 16.0]):
+            x[:, s * 384:(s + 1) * 384] *= f_
+        x[:, torch.randperm(K, generator=g)[:30]] *= 20.0
+        w = torch.randn(N, K, generator=g) * 0.02
+        b = torch.randn(N, generator=g) * 0.01
+        lin = SegmentLinear(K, N, bias=True, seg_mode="input", chunks=S, custom_weight_tensor=w.to(dev), custom_bias_tensor=b.to(dev),
+                            input_quant_type="int8", weight_quant_type="int8", input_quant_args={"real_quant": True, "axis": None},
+                            weight_quant_args={"real_quant": True, "axis": 1}, device=dev)
+        xd = x.to(dev)
+        lin.calibrate(xd)
+        lin.finish_calibrate()
+        rot.append((lin, xd))
+    ms, q_ms, g_ms = run_layer(rot[0][0], rot[0][1], "Wint8Aint8", False, rot)
+    bound, t_bound = layer_bound(M, N, K, 4, 4, 1, False, pk)
+    out["config0_int8_4seg"] = {"workload": "config[0]: W8A8 INT8, fp32 in/out, M=4096 K=N=1536, 4 K-segments, seed 0", "ms": ms,
+                                "tops_useful": 2.0 * M * N * K / ms / 1e9, "act_quant_ms": q_ms,
+                                "roofline": {"bound": bound, "frac": t_bound / ms, "bound_ms": t_bound, "kernel": "seg_gemm_kernel<I8>", "kernel_ms": g_ms,
+                                             "kernel_frac_of_2x_bf16": 2.0 * M * N * K / g_ms / 1e9 / peak8}}
+    del rot
+    # ---- config[1]: DualScale FP8 after GELU, bf16, M=4096 K=6144 N=1536, seed 1
+    M, K, N = 4096, 6144, 1536
+    rot = []
+    for r in range(4):
+        g = torch.Generator().manual_seed(1 + 100 * r)
+        x = torch.nn.functional.gelu(torch.randn(M, K, generator=g).to(torch.bfloat16).float()).to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        b = (torch.randn(N, generator=g) * 0.01).to(torch.bfloat16)
+        lin = SegmentLinear(K, N, bias=True, seg_mode="weight", chunks=1, custom_weight_tensor=w.to(dev), custom_bias_tensor=b.to(dev),
+                            input_quant_type="fpe4m3", weight_quant_type="fpe4m3",
+                            input_quant_args={"real_quant": True, "axis": None, "dual_scale": True},
+                            weight_quant_args={"real_quant": True, "axis": 1}, device=dev)
+        xd = x.to(dev)
+        lin.calibrate(xd)
+        lin.finish_calibrate()
+        rot.append((lin, xd))
+    ms, q_ms, g_ms = run_layer(rot[0][0], rot[0][1], "Wfpe4m3Afpe4m3", True, rot)
+    bound, t_bound = layer_bound(M, N, K, 2, 2, 1, True, pk)
+    out["config1_fp8_dual"] = {"workload": "config[1]: DualScale W8A8 FP8-e4m3 down-projection, bf16, M=4096 K=6144 N=1536, seed 1", "ms": ms,
+                               "tops_useful": 2.0 * M * N * K / ms / 1e9, "act_quant_ms": q_ms,
+                               "act_quant_gbs": M * K * 4 / q_ms / 1e6, "act_quant_frac_of_hbm": M * K * 4 / q_ms / 1e6 / pk["hbm"],
+                               "roofline": {"bound": bound, "frac": t_bound / ms, "bound_ms": t_bound, "kernel": "seg_gemm2_kernel<F8, dual>", "kernel_ms": g_ms,
+                                            "kernel_frac_issued": 4.0 * M * N * K / g_ms / 1e9 / peak8,
+                                            "kernel_frac_useful": 2.0 * M * N * K / g_ms / 1e9 / peak8,
+                                            "note": "DualScale issues 4*M*N*K (positive and negative activation tiles against the same weights); "
+                                                    "the useful fraction cannot exceed 0.5 by construction"}}
+    del rot
+    # ---- config[2]: W4A8, int4 weights with bf16 group scales (g=128), M=4608; QKV, MLP up (2 unequal K-segments), MLP down (DualScale after SiLU)
+    M, G = 4608, 128
+    entries = {}
+    for name, N, K, bounds, dual in (("qkv", 9216, 3072, [0, 1024, 3072], False), ("mlp_up", 12288, 3072, [0, 1024, 3072], False),
+                                     ("mlp_down", 3072, 12288, [0, 12288], True)):
+        g = torch.Generator().manual_seed(2)
+        if dual:
+            x = torch.nn.functional.silu(torch.randn(M, K, generator=g)).to(torch.bfloat16).to(dev)
+        else:
+            x = torch.randn(M, K, generator=g)
+            x[:, 1024:] *= 3.0
+            x = x.to(torch.bfloat16).to(dev)
+        w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        sw16 = (7.0 / w.float().view(N, K // G, G).abs().amax(-1)).to(torch.bfloat16).contiguous()
+        wq = torch.empty(N * K // 2, dtype=torch.uint8, device=dev)
+        ops.quantize_weight(w, wq, sw16.float().contiguous(), L.SQ_Q_INT4, group_size=G)
+        wq3 = wq.view(1, N, K // 2)
+        xf = x.float()
+        if dual:
+            pos, neg = xf.clamp(min=0).max().item(), (-xf).clamp(min=0).max().item()
+            sx, sxn = torch.tensor([127.0 / pos], device=dev), torch.tensor([128.0 / neg], device=dev)
+        else:
+            sx = torch.stack([127.0 / xf[:, bounds[s]:bounds[s + 1]].abs().max() for s in range(len(bounds) - 1)]).contiguous()
+            sxn = None
+        del xf, w
+        xq = torch.empty((1, M, K), dtype=torch.uint8, device=dev)
+        xqn = torch.empty((1, M, K), dtype=torch.uint8, device=dev) if dual else None
+        y = torch.empty((1, M, N), dtype=torch.bfloat16, device=dev)
+
+        def quant():
+            ops.quantize_act(x, bounds, sx, sxn, L.SQ_Q_INT8, out=xq, out_neg=xqn)
+
+        def gemm():
+            ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, sx, sw16, xq_neg=xqn, sx_neg=sxn, group_size=G, sw_strides=(0, 0, 1, K // G),
+                     out_dtype=torch.bfloat16, out=y)
+
+        def step():
+            quant()
+            gemm()
+        ms = timed(step, steps)
+        q_ms, g_ms = split_timed(quant, gemm, steps)
+        entries[name] = {"N": N, "K": K, "dual_scale": dual, "ms": ms, "tops_useful": 2.0 * M * N * K / ms / 1e9, "act_quant_ms": q_ms,
+                         "kernel_ms": g_ms, "kernel_frac_of_2x_bf16": 2.0 * M * N * K * (2 if dual else 1) / g_ms / 1e9 / peak8}
+        del x, wq, wq3, xq, xqn, y
+    out["config2_w4a8_g128"] = {"workload": "config[2]: W4A8, int4 weights + bf16 group scales (g=128), bf16, M=4608, seed 2 "
+                                            "(operands 50-170 MB per projection: weights partly L2-resident between steps, activations from HBM)",
+                                "kernel": "seg_gemm_kernel<W4A8>", "projections": entries,
+                                "note": "kernel_frac counts issued ops (4*M*N*K for the DualScale down-projection) against 2 x measured bf16"}
+    return out
+
+
+def mmdit_entry(dev, steps=5, cpu=True):
+    from segquant_b200 import ops
+    from segquant_b200.mmdit import GraphedStep, SyntheticMMDiT, synthetic_inputs
+    model = SyntheticMMDiT(dev)
+    inputs = synthetic_inputs(2, dev, seed=100)
+    model.calibrate(*inputs)
+    torch.cuda.synchronize()
+    step = GraphedStep(model, *inputs)
+    l0 = ops.launch_count
+    ms = timed(lambda: step(*inputs), steps, warmup=3)
+    launches = (ops.launch_count - l0) // (steps + 3)
+    lin_ops = model.linear_ops(2)
+    entry = {"workload": "config[3]: synthetic MMDiT denoise step, 24 joint blocks, hidden 1536, 4096+333 tokens, batch 2, every linear W8A8 INT8 "
+                         "SegLinear, attention / norms bf16; one CUDA graph per step", "ms": ms, "linear_tops_useful": lin_ops / ms / 1e9,
+             "library_kernels_per_step": launches}
+    del step, model
+    torch.cuda.empty_cache()
+    if cpu:
+        cb = cpu_mmdit_block(2)
+        entry["cpu_baseline"] = cb
+        entry["speedup_vs_cpu_extrapolated"] = cb["step_ms_extrapolated"] / ms
+    return entry
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm: the headline layer
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    from segquant_b200 import _lib as L
+    from segquant_b200 import ops
+    dist, world, rank, dev = _dist_setup()
+    L.load()
+    peaks = load_peaks()
+    bf16 = peaks.get("bf16_tflops")
+    peak8 = 2.0 * (bf16 or 1590.0)
+    peak8_sus = 2.0 * (peaks.get("bf16_tflops_sustained") or 1400.0)
+    hbm = peaks.get("hbm_gbs") or 6650.0
+    peak_src = "of measured" if bf16 else "of fallback"
+    if HN % world:
+        raise SystemExit(f"bench.py: N={HN} is not divisible by {world} ranks")
+    n_loc = HN // world
+
+    x_cpu, w_cpu = headline_tensors()
+    x = x_cpu.to(dev)
+    from segquant_b200.sharded import ColumnShardedSegLinear, row_range, shard_range
+    cs = ColumnShardedSegLinear.from_full(x, w_cpu.to(dev), None, rank, world, kernel_type="Wint8Aint8", seg_mode="input", chunks=HS)
+    lin = cs.layer
+    lin.optimizer._build_fused()
+    f = lin.optimizer._fused
+    kind, a_kind, _ = ops.KERNELS["Wint8Aint8"]
+    xq = torch.empty((1, HM, HK), dtype=torch.uint8, device=dev)
+    y_loc = torch.empty((1, HM, n_loc), dtype=torch.bfloat16, device=dev)
     torch.cuda.synchronize()
 
-    # pre-extract the fused-call arguments so the timed region is exactly the two kernels
-    fused = []
-    for lin in layers:
-        lin.optimizer._build_fused()
-        fused.append(lin.optimizer._fused)
-    kind, a_kind, _ = ops.KERNELS["Wfpe4m3Afpe4m3"]
-    xq = [torch.empty((1, M, K), dtype=torch.uint8, device=dev) for _ in range(ROTATE)]
-    xqn = [torch.empty((1, M, K), dtype=torch.uint8, device=dev) for _ in range(ROTATE)]
-    ys = [torch.empty((1, M, N), dtype=torch.bfloat16, device=dev) for _ in range(ROTATE)]
+    def quant():
+        ops.quantize_act(x, f["bounds"], f["sx"], None, a_kind, out=xq)
 
-    def step(i, ev=None):
-        r = i % ROTATE
-        f = fused[r]
-        if ev is not None:
-            ev[2].record()
-        ops.quantize_act(xs[r], f["bounds"], f["sx"], f["sx_neg"], a_kind, out=xq[r], out_neg=xqn[r])
-        if ev is not None:
-            ev[0].record()
-        ops.gemm(kind, xq[r], f["wq"], N, f["bounds"], f["sx"], f["sw"], xq_neg=xqn[r], sx_neg=f["sx_neg"],
-                 sw_strides=f["sw_strides"], bias=layers[r].bias_data, out_dtype=torch.bfloat16, out=ys[r])
-        if ev is not None:
-            ev[1].record()
+    def gemm():
+        ops.gemm(kind, xq, f["wq"], n_loc, f["bounds"], f["sx"], f["sw"], sw_strides=f["sw_strides"], out_dtype=torch.bfloat16, out=y_loc)
+
+    exchange = None
+    if world > 1:
+        cs.enable_symmetric(HM)
+        exchange = args.exchange
+        fwd = {"auto": cs.forward_auto, "push": cs.forward_push, "fused": cs.forward_fused, "nccl": cs.forward}[exchange]
+
+        def step():
+            return fwd(x)
+    else:
+        def step():
+            quant()
+            gemm()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    def max_over_ranks(vals):
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        step()
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+        time.sleep(0.3)
     barrier()
     launches0 = ops.launch_count
-    gemm_events = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(3)) for _ in range(args.steps)]
+    t_mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        step(i, gemm_events[i])
+    for _ in range(args.steps):
+        step()
     e1.record()
     barrier()
+    t_mark1 = sampler.mark()
     launches = ops.launch_count - launches0
-    ms_total = e0.elapsed_time(e1)
-    gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events) / args.steps
-    quant_ms = sum(c.elapsed_time(a) for a, _, c in gemm_events) / args.steps
-    t = torch.tensor([ms_total, gemm_ms, quant_ms], dtype=torch.float64, device=dev)
+    (ms_step,) = max_over_ranks([e0.elapsed_time(e1) / args.steps])
+
+    # ---- the two kernels alone (every rank, max over ranks)
+    q_ms, g_ms = split_timed(quant, gemm, args.steps)
+    q_ms, g_ms = max_over_ranks([q_ms, g_ms])
+    sharded = None
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = t[0].item() / args.steps
-    gemm_ms = t[1].item()
-    quant_ms = t[2].item()
+        # exchange alone: the same step with the GEMM output already in place (push of the block + barrier), and each method's total
+        lo, hi = shard_range(HN, world, rank)
+        esz = 2
+        out_bytes = HM * n_loc * esz * (world - 1)
+        totals = {}
+        for name, fn in (("nccl_allgather", cs.forward), ("block_push", cs.forward_push), ("fused_epilogue", cs.forward_fused)):
+            barrier()
+            (totals[name],) = max_over_ranks([timed(lambda: fn(x), args.steps)])
+        full, peers = cs._next_buffer(HM)
+        mine = full[:, lo:hi]
+
+        def push_only():
+            ops.push_columns(mine, [p + lo * esz for p in peers], HN * esz)
+            cs._barrier()
+        barrier()
+        (push_ms,) = max_over_ranks([timed(push_only, args.steps)])
+        # results: every method gives the same [M, N] matrix on every rank
+        y_nccl = cs.forward(x)
+        same = int(torch.equal(cs.forward_push(x), y_nccl)) & int(torch.equal(cs.forward_fused(x), y_nccl))
+        (same,) = max_over_ranks([1 - same])
+        nvlink = 770.0     # GB/s per direction per GPU: the measured peer-copy rate on this pool (nominal 900)
+        t_link = out_bytes / (nvlink * 1e9) * 1e3
+        sharded = {"what": f"N={HN} split into {world} column blocks of {n_loc}; activations replicated and quantised on every rank; "
+                           f"exchange method of the headline value: {exchange}",
+                   "gemm_only_ms": g_ms, "act_quant_ms": q_ms, "exchange_ms": push_ms, "total_ms": ms_step,
+                   "totals_ms_by_method": totals, "methods_agree": same == 0,
+                   "exchange_bytes_out_per_gpu": out_bytes, "exchange_gbs_per_gpu": out_bytes / push_ms / 1e6,
+                   "nvlink_frac": out_bytes / push_ms / 1e6 / nvlink,
+                   "nvlink_peak_gbs": nvlink, "nvlink_note": "measured peer-copy rate per direction per GPU on this pool (nominal 900)",
+                   "ceiling": {"exchange_ms_at_nvlink_peak": t_link,
+                               "total_ms_if_exchange_fully_overlapped": q_ms + max(g_ms, t_link),
+                               "note": "the exchange must move (g-1)/g*M*N*2 bytes out of every GPU; the quantise of the replicated activations does not shrink with g"}}
+
+    # ---- sustained: the same step looped for more than a second (N = 1)
+    sustained = None
+    if world == 1:
+        n_sus = max(50, int(1300.0 / ms_step))
+        ts0 = sampler.mark()
+        ms_sus = timed(step, n_sus, warmup=0)
+        ts1 = sampler.mark()
+        gq, gg = split_timed(quant, gemm, 20)
+        time.sleep(0.15)
+        clk = sampler.summary(ts0, ts1)
+        sustained = {"steps": n_sus, "seconds": ms_sus * n_sus / 1e3, "ms_per_step": ms_sus, "tops_useful": 2.0 * HM * HN * HK / ms_sus / 1e9,
+                     "kernel_ms_hot": gg, "sm_mhz_median": clk["sm_mhz"], "power_w_max": clk["power_w_max"], "reasons": clk["reasons"],
+                     "peak": peak8_sus, "frac": 2.0 * HM * HN * HK / (ms_sus - gq) / 1e9 / peak8_sus if ms_sus > gq else None,
+                     "note": f"frac = 2*M*N*K / (step - quantise) against 2 x the measured sustained bf16 rate ({peak_src}); quantise time "
+                             "taken right after the loop, at the same clocks"}
 
     # ---- end to end through the public layer API with host buffers
-    host_x = [x.cpu().pin_memory() for x in xs]
-    host_y = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    r_lo, r_hi = row_range(HM, world, rank)
+    host_x = [x_cpu[r_lo:r_hi].contiguous().pin_memory() for _ in range(2)]
+    o_lo, o_hi = row_range(HM, world, rank)
+    host_y = torch.empty((o_hi - o_lo, HN), dtype=torch.bfloat16).pin_memory()
+    if world == 1:
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        x_dev = [torch.empty((HM, HK), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        y_dev = [torch.empty((1, HM, HN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ev_in, ev_cmp, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
 
-    # A user streaming batches through the layer: host->device copy of step i+1, the layer forward of step i and the
-    # device->host read of step i-1 run on three streams with double-buffered device tensors, ordered by events.  Every
-    # step's input copy and result read are inside the timed region.
-    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    x_dev = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    y_dev = [torch.empty((1, M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_cmp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+        def e2e_step(i):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_cmp[b])              # the forward two steps ago has consumed x_dev[b]
+                x_dev[b].copy_(host_x[b], non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[b])
+                s_cmp.wait_event(ev_out[b])             # y_dev[b] has been read back
+                lin(x_dev[b].unsqueeze(0), out=y_dev[b])
+                ev_cmp[b].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[b])
+                host_y.copy_(y_dev[b][0], non_blocking=True)
+                ev_out[b].record(s_out)
 
-    def e2e_step(i):
-        r, b = i % ROTATE, i & 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_cmp[b])              # the forward two steps ago has consumed x_dev[b]
-            x_dev[b].copy_(host_x[r], non_blocking=True)
-            ev_in[b].record(s_in)
-        with torch.cuda.stream(s_cmp):
-            s_cmp.wait_event(ev_in[b])
-            s_cmp.wait_event(ev_out[b])             # y_dev[b] has been read back
-            layers[r](x_dev[b].unsqueeze(0), out=y_dev[b])
-            ev_cmp[b].record(s_cmp)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_cmp[b])
-            host_y.copy_(y_dev[b][0], non_blocking=True)
-            ev_out[b].record(s_out)
-
-    def e2e_join():
-        cur = torch.cuda.current_stream()
-        for st_ in (s_in, s_cmp, s_out):
-            cur.wait_stream(st_)
-
-    for st_ in (s_in, s_cmp, s_out):
-        st_.wait_stream(torch.cuda.current_stream())
-    for i in range(4):
-        e2e_step(i)
-    e2e_join()
+        def e2e_run(n):
+            for st_ in (s_in, s_cmp, s_out):
+                st_.wait_stream(torch.cuda.current_stream())
+            for i in range(n):
+                e2e_step(i)
+            for st_ in (s_in, s_cmp, s_out):
+                torch.cuda.current_stream().wait_stream(st_)
+        e2e_mode = ("SegmentLinear.forward(x, out=) fed from pinned host memory; copy-in, forward and read-back of consecutive steps "
+                    "overlap on three streams (double-buffered)")
+    else:
+        def e2e_run(n):
+            for i in range(n):
+                y_full = cs.forward_from_host_rows(host_x[i & 1], HM, exchange=exchange)
+                host_y.copy_(y_full[o_lo:o_hi], non_blocking=True)
+        e2e_mode = ("ColumnShardedSegLinear.forward_from_host_rows: every rank copies its 1/g of the input rows from pinned host memory, "
+                    "the rows are all-gathered over NVLink, sharded forward + exchange, every rank reads back its 1/g of the output rows")
+    e2e_run(3)
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
-    for st_ in (s_in, s_cmp, s_out):
-        st_.wait_stream(torch.cuda.current_stream())
-    for i in range(args.steps):
-        e2e_step(i)
-    e2e_join()
+    e2e_run(args.steps)
     e3.record()
     barrier()
-    t2 = torch.tensor([e2.elapsed_time(e3)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = t2.item() / args.steps
-    clocks = sampler.stop() if rank == 0 else None
-
-    # ---- column-sharded variant (N split over ranks, all-gather of output slices)
-    sharded = None
-    if world > 1 and N % world == 0:
-        from segquant_b200.sharded import ColumnShardedSegLinear
-        x0, w0, b0 = make_inputs(SEED, device=dev)
-        cs = ColumnShardedSegLinear.from_full(x0, w0, b0, rank, world, kernel_type="Wfpe4m3Afpe4m3", dual_scale=True)
-        for _ in range(3):
-            cs.forward(x0)
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(args.steps):
-            cs.forward(x0)
-        s1.record()
-        barrier()
-        ts = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
-        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-        sh_ms = ts.item() / args.steps
-        sharded = {"ms_per_step": sh_ms, "tops": 2.0 * M * N * K / sh_ms / 1e9, "scaling": "strong",
-                   "what": f"same layer, N={N} split into {world} column slices, NCCL all-gather of [M, N/{world}] bf16 slices"}
-        # fused form: the GEMM epilogue stores every tile into all ranks' [M, N] buffers (symmetric memory), no gather kernel
-        try:
-            ok_local = 1
-            try:
-                cs.enable_fused_gather(M)
-            except Exception as e:      # all ranks must agree before anyone enters the fused collectives
-                ok_local, err = 0, e
-            okt = torch.tensor([ok_local], device=dev)
-            dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-            if not okt.item():
-                raise RuntimeError(f"symmetric memory set-up failed on some rank: {err if not ok_local else 'peer'}")
-            ref_full = cs.forward(x0)
-            for _ in range(3):
-                y_f = cs.forward_fused(x0)
-            barrier()
-            same = torch.tensor([int(torch.equal(y_f, ref_full))], device=dev)
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record()
-            for _ in range(args.steps):
-                cs.forward_fused(x0)
-            f1.record()
-            barrier()
-            tf = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
-            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-            dist.all_reduce(same, op=dist.ReduceOp.MIN)
-            sharded["fused_gather_ms_per_step"] = tf.item() / args.steps
-            sharded["fused_equals_allgather"] = bool(same.item())
-        except Exception as e:   # symmetric memory unavailable on this box: the NCCL numbers above stand
-            sharded["fused_gather_error"] = f"{type(e).__name__}: {e}"[:200]
+    (e2e_ms,) = max_over_ranks([e2.elapsed_time(e3) / args.steps])
+    clocks = None
+    if rank == 0:
+        time.sleep(0.15)
+        clocks = sampler.summary(t_mark0, t_mark1)
+        if not clocks["samples"]:
+            clocks = sampler.summary()
+        sampler.stop()
 
     status = ops.device_status()
+    configs = None
+    if world == 1 and rank == 0 and args.configs != "none":
+        del x, xq, y_loc
+        torch.cuda.empty_cache()
+        configs = config_entries(dev, peaks)
+        configs["config3_mmdit_step"] = mmdit_entry(dev, cpu=args.configs == "all")
+        status = status or ops.device_status()
     if rank == 0:
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peaks = json.load(f)
-        except OSError:
-            pass
-        bf16 = peaks.get("bf16_tflops")
-        peak = 2.0 * bf16 if bf16 else 2.0 * 1590.0
-        issued_tflop = 4.0 * M * N * K / 1e12          # DualScale: two MMAs per K step
-        achieved = issued_tflop / (gemm_ms / 1e3)
-        cb = cpu_baseline()
+        achieved = 2.0 * HM * n_loc * HK / g_ms / 1e9
         line = {
-            "metric": "seglinear_gemm_tops", "value": 2.0 * M * N * K * world / ms_step / 1e9, "unit": "TOPS",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": "config[1]: DualScale W8A8 FP8-e4m3 down-projection, M=4096 K=6144 N=1536 per GPU, seed 1",
-                       "ops_counted": "useful 2*M*N*K (the kernel issues 4*M*N*K: positive and negative activation tiles)",
-                       "cache": f"{ROTATE} independent layer instances cycled (operands {ROTATE * (M * K * 4 + N * K + M * N * 2) / 1e6:.0f} MB > 126 MB L2)",
-                       "parallelism": f"dp{world}"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
-                         # (one ncu capture; 65.6 MB against 72.3 MB of algorithmic operand + output bytes)
-                         "traffic": 65.6e6, "traffic_unit": "bytes per launch (ncu)",
-                         "kernel": "seg_gemm2_kernel<F8, dual, KSUB=2>", "kernel_ms": gemm_ms,
-                         "note": ("achieved = issued 4*M*N*K per launch / mean launch time (CUDA events on the launch stream); "
-                                  "peak = 2 x measured bf16 burst (of measured)" if bf16 else
-                                  "achieved = issued 4*M*N*K per launch / mean launch time; peak = 2 x 1.59 PFLOP/s (of fallback)")},
-            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
-            "e2e": {"value": 2.0 * M * N * K * world / e2e_ms / 1e9, "unit": "TOPS", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
-                    "mode": "SegmentLinear.forward(x, out=) fed from pinned host memory; copy-in, forward and read-back of "
-                            "consecutive steps overlap on three streams (double-buffered)"},
-            "kernels": {"act_quant_ms": quant_ms, "act_quant_gbs": M * K * 4 / quant_ms / 1e6,
-                        "act_quant_note": "algorithmic bytes M*K*(2 in + 2 out) per launch / mean CUDA-event time",
-                        "seg_gemm_ms": gemm_ms},
+            "metric": "seglinear_gemm_tops", "value": 2.0 * HM * HN * HK / ms_step / 1e9, "unit": "TOPS",
+            "n_gpus": world, "steps": args.steps, "warmup": W, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": HEAD_NAME,
+                       "step": "activation quantise + GEMM + epilogue" + ("" if world == 1 else f" + exchange of the output column blocks ({exchange})"),
+                       "ops_counted": "useful 2*M*N*K of the whole layer",
+                       "cache": f"inputs larger than L2: activations {HM * HK * 2 / 1e6:.0f} MB bf16 + {HM * HK / 1e6:.0f} MB quantised per step (L2 126 MB)",
+                       "parallelism": "1 GPU" if world == 1 else f"column-sharded over {world} GPUs (N/{world} = {n_loc} columns each)"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak8, "unit": "TFLOP/s", "frac": achieved / peak8,
+                         "traffic": HEAD_TRAFFIC_NCU if world == 1 else None,
+                         "traffic_source": HEAD_TRAFFIC_SRC + " (one ncu capture of this kernel on this workload; a constant, not re-measured by this run)",
+                         "algorithmic_bytes": HM * HK + n_loc * HK + HM * n_loc * 2,
+                         "kernel": "seg_gemm2_kernel<I8, KSUB=2> (CTA pair, tcgen05.mma.cta_group::2.kind::i8)", "kernel_ms": g_ms,
+                         "frac_useful": achieved / peak8, "frac_issued": achieved / peak8,
+                         "sustained": sustained,
+                         "note": f"achieved = 2*M*(N/g)*K per launch / mean launch time (CUDA events on the launch stream); peak = 2 x measured bf16 burst ({peak_src}); "
+                                 "single-scale layer: issued = useful"},
+            "e2e": {"value": 2.0 * HM * HN * HK / e2e_ms / 1e9, "unit": "TOPS", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": (r_hi - r_lo) * HK * 2, "d2h_bytes_per_step": (o_hi - o_lo) * HN * 2, "bytes_are": "per rank", "mode": e2e_mode},
+            "kernels": {"act_quant_ms": q_ms, "act_quant_gbs": HM * HK * 3 / q_ms / 1e6, "act_quant_frac_of_hbm": HM * HK * 3 / q_ms / 1e6 / hbm,
+                        "act_quant_note": "algorithmic bytes M*K*(2 in + 1 out) per launch / mean CUDA-event time, inside the step loop",
+                        "seg_gemm_ms": g_ms},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
         }
         if sharded:
             line["sharded"] = sharded
+        if configs:
+            line["configs"] = configs
+        if world == 1 and args.configs != "none":
+            line["cpu_baseline"] = {k: v for k, v in cpu_headline().items() if k != "ms_per_step"}
+        else:
+            line["cpu_baseline"] = {"value": None, "unit": "TOPS", "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": "timed on rank 0 at N = 1 only (the host cores are busy driving the ranks here); see the N = 1 line or --impl reference"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
 # ---------------------------------------------------------------------------------------------
-# other BASELINE workloads (not the default line): synthetic MMDiT denoise step, GEMM sweep
+# other workloads (not the default line): synthetic MMDiT denoise step, GEMM sweep, HBM kernels
 # ---------------------------------------------------------------------------------------------
-def _dist_setup():
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; this library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    return dist, world, rank, dev
-
-
 def run_mmdit(args):
     """config[3]: 24-block SD3.5-medium-like MMDiT, every linear W8A8 INT8 SegLinear, attention / norms bf16.
     Batch 2 on one GPU; batch 16 split over 2 / 4 / 8 GPUs (replicas, no collective inside the step)."""
@@ -407,6 +695,8 @@ def run_mmdit(args):
     from segquant_b200.mmdit import GraphedStep, SyntheticMMDiT, synthetic_inputs
     dist, world, rank, dev = _dist_setup()
     batch = 2 if world == 1 else 16 // world
+    if args.mmdit_batch:
+        batch = args.mmdit_batch
     model = SyntheticMMDiT(dev, out_proj_segments=args.out_proj_segments)
     inputs = synthetic_inputs(batch, dev, seed=100 + rank)
     model.calibrate(*inputs)
@@ -450,12 +740,19 @@ def run_mmdit(args):
     t2 = torch.tensor([e2.elapsed_time(e3) / max(2, args.steps // 4)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        time.sleep(0.15)
+        clocks = sampler.summary()
+        sampler.stop()
     status = ops.device_status()
     if rank == 0:
+        peaks = load_peaks()
         lin_ops = eager.linear_ops(batch)
         tokens = eager.img_tokens + eager.txt_tokens
         attn_flops = 24 * batch * 4 * tokens * tokens * eager.hidden
+        p8, p16 = 2.0 * (peaks.get("bf16_tflops") or 1590.0), peaks.get("bf16_tflops") or 1590.0
+        bound_ms = (lin_ops / (p8 * 1e12) + attn_flops / (p16 * 1e12)) * 1e3
         line = {
             "metric": "mmdit_denoise_step_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
@@ -464,10 +761,14 @@ def run_mmdit(args):
                                    f"({batch * world} total), attention output projections with {args.out_proj_segments} K-segment(s)",
                        "launch": "eager" if args.no_graph else "one CUDA graph per step", "parallelism": f"dp{world} replicas"},
             "linear_tops": lin_ops / ms / 1e9, "linear_ops_per_step": lin_ops, "attention_flops_per_step": attn_flops,
+            "roofline": {"bound": "tensor", "bound_ms": bound_ms, "frac": bound_ms / ms, "unit": "ms",
+                         "note": "bound = int8 linear ops / (2 x measured bf16) + bf16 attention flops / measured bf16; frac = bound / measured step"},
             "e2e": {"value": t2.item(), "unit": "ms", "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
                     "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
         }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_mmdit_block(batch)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -478,7 +779,10 @@ SWEEP_NK = [(1536, 1536), (6144, 1536), (1536, 6144), (9216, 3072), (12288, 3072
 
 def run_sweep(args):
     """config[4]: M x (N, K) x {INT8, FP8, W4A8 g=128} x segments {1,2,4,8}; each point column-sharded over the
-    ranks with an NCCL all-gather of the output slices.  Prints one JSON line holding every point."""
+    ranks.  Per point: layer time (quantise + GEMM on this rank's columns), and with N > 1 the total with each exchange
+    (NCCL all-gather + interleave, block push, fused epilogue) and a check that all give the same matrix.  Every point is
+    also CHECKED: 64 rows spread over the matrix against the CPU oracle (run outside every timed region, as the checker);
+    the run fails if a point is more than one bf16 step off.  Prints one JSON line holding every point."""
     from segquant_b200 import _lib as L
     from segquant_b200 import ops
     from segquant_b200.sharded import all_gather_slices, shard_range
@@ -492,6 +796,13 @@ def run_sweep(args):
     seg_counts = [int(v) for v in args.sweep_segs.split(",")]
     w4_group = args.sweep_w4_group
     modes = [(n_, k_, w_, (w4_group if n_ == "w4a8" else g_)) for (n_, k_, w_, g_) in modes]
+    check = not args.no_check
+    if check:
+        import numpy as np
+        from oracle import oracle as O
+        okind = {"int8": O.GEMM_I8, "fp8": O.GEMM_F8, "w4a8": O.GEMM_W4A8}
+        oq = {"int8": O.Q_INT8, "fp8": O.Q_E4M3, "w4a8": O.Q_INT8}
+    worst = 0.0
     for (N, K) in nks:
         if N % world:
             continue
@@ -499,7 +810,7 @@ def run_sweep(args):
         n_loc = hi - lo
         full = peers = flag = None
         if world > 1 and args.fused_gather:
-            # every rank's [M, N] result buffer, mapped into all processes: the GEMM epilogue stores tiles to all of them
+            # every rank's [M, N] result buffer, mapped into all processes: epilogue stores / block pushes go to all of them
             import torch.distributed._symmetric_memory as symm
             full = symm.empty((max(Ms), N), dtype=torch.bfloat16, device=dev)
             handle = symm.rendezvous(full, dist.group.WORLD)
@@ -525,7 +836,7 @@ def run_sweep(args):
                         continue
                     bounds = ops.uniform_bounds(K, S)
                     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
-                    scale = torch.exp(torch.empty(S).uniform_(-1.386, 3.466, generator=g))   # log-uniform in [0.25, 32]
+                    scale = log_uniform_scales(S, g)
                     for s_ in range(S):
                         x[:, bounds[s_]:bounds[s_ + 1]] *= scale[s_].to(torch.bfloat16)
                     x = x.to(dev)
@@ -538,6 +849,19 @@ def run_sweep(args):
                     for _ in range(3):
                         y = fwd()
                     torch.cuda.synchronize()
+                    err = None
+                    if check:
+                        # 64 rows spread over the matrix, through the oracle's own quantise and integer GEMM
+                        rows = torch.linspace(0, M - 1, 64).long().unique()
+                        xr = x[rows].float().cpu().numpy()
+                        xq_ref = O.quantize_act(xr, bounds, sx.cpu().numpy(), out_kind=oq[name])
+                        sw_o = sw.t().contiguous().cpu().numpy() if group else sw.cpu().numpy()
+                        y_ref = O.seg_gemm(okind[name], xq_ref, wq.cpu().numpy() if wkind == L.SQ_Q_INT4 else wq.view(n_loc, K).cpu().numpy(),
+                                           bounds, sx.cpu().numpy(), sw_o, group_size=group)
+                        want = torch.from_numpy(y_ref).to(torch.bfloat16).float().numpy()
+                        got = y[rows.to(dev)].float().cpu().numpy()
+                        err = float(np.abs(got - want).max() / np.abs(want).max())
+                        worst = max(worst, err)
                     it = args.sweep_iters
                     # `it` forwards recorded once into a CUDA graph: small layers are otherwise bound by the Python / ctypes
                     # launch path (~30 us per call), not by the GPU
@@ -564,44 +888,62 @@ def run_sweep(args):
                     e[2].record()
                     torch.cuda.synchronize()
                     del graph
-                    ms_fused, fused_ok = None, None
+                    ms_fused = ms_push = None
+                    same_ok = None
                     if full is not None:
+                        ref_full = gathered.permute(1, 0, 2).reshape(M, N)
+                        mine = full[:M, lo:hi]
+
                         def fwd_fused():
                             ops.seg_linear(ktype, x.unsqueeze(0), wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides,
-                                           out=full[:M, lo:hi].unsqueeze(0), peer_outputs=(peers, N, lo))
+                                           out=mine.unsqueeze(0), peer_outputs=(peers, N, lo))
                             dist.all_reduce(flag)      # stream-ordered: every rank's kernel is complete after it
-                        for _ in range(2):
-                            fwd_fused()
-                        torch.cuda.synchronize()
-                        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        f0.record()
-                        for _ in range(it):
-                            fwd_fused()
-                        f1.record()
-                        torch.cuda.synchronize()
-                        tf = torch.tensor([f0.elapsed_time(f1) / it], dtype=torch.float64, device=dev)
-                        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-                        ms_fused = tf.item()
-                        same = torch.tensor([int(torch.equal(full[:M], gathered.permute(1, 0, 2).reshape(M, N)))], device=dev)
-                        dist.all_reduce(same, op=dist.ReduceOp.MIN)
-                        fused_ok = bool(same.item())
+
+                        def fwd_push():
+                            ops.seg_linear(ktype, x.unsqueeze(0), wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides, out=mine.unsqueeze(0))
+                            ops.push_columns(mine, [p_ + lo * 2 for p_ in peers], N * 2)
+                            dist.all_reduce(flag)
+                        res = []
+                        for fn in (fwd_fused, fwd_push):
+                            full.zero_()
+                            torch.cuda.synchronize()
+                            dist.barrier()
+                            ms_ = timed(fn, it, warmup=2)
+                            tf = torch.tensor([ms_], dtype=torch.float64, device=dev)
+                            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+                            same = torch.tensor([int(torch.equal(full[:M], ref_full))], device=dev)
+                            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                            res.append((tf.item(), bool(same.item())))
+                            dist.barrier()             # nobody clears its buffer while a peer may still compare against stores in flight
+                        (ms_fused, ok_f), (ms_push, ok_p) = res
+                        same_ok = ok_f and ok_p
                     t = torch.tensor([e[0].elapsed_time(e[1]) / it, e[1].elapsed_time(e[2]) / it], dtype=torch.float64, device=dev)
                     if world > 1:
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
                     ms_c, ms_t = t.tolist()
                     points.append({"mode": name, "M": M, "N": N, "K": K, "S": S, "layer_ms": ms_c, "layer_tops": 2.0 * M * N * K / ms_c / 1e9,
-                                   "with_allgather_ms": ms_t if world > 1 else None, "with_fused_gather_ms": ms_fused,
-                                   "fused_equals_allgather": fused_ok})
+                                   "max_rel_vs_oracle_64rows": err,
+                                   "with_allgather_ms": ms_t if world > 1 else None, "with_fused_gather_ms": ms_fused, "with_block_push_ms": ms_push,
+                                   "exchanges_equal_allgather": same_ok})
     status = ops.device_status()
+    if world > 1:
+        wt = torch.tensor([worst], dtype=torch.float64, device=dev)
+        dist.all_reduce(wt, op=dist.ReduceOp.MAX)
+        worst = wt.item()
     if rank == 0:
         best = {m: max((p["layer_tops"] for p in points if p["mode"] == m), default=0.0) for m in ("int8", "fp8", "w4a8")}
         print(json.dumps({"metric": "seglinear_gemm_tops_sweep", "unit": "TOPS", "n_gpus": world, "higher_is_better": True,
                           "scaling": "strong", "data": "synthetic", "value": max(best.values()), "best_tops": best,
                           "config": {"workload": "config[4]: GEMM sweep, layer = activation quantise + GEMM + epilogue, bf16 in/out, "
                                                  "N column-sharded over the ranks", "iters": args.sweep_iters},
+                          "correctness": {"checked": check, "worst_max_rel_vs_oracle": worst if check else None,
+                                          "bar": "bf16 output of 64 rows per point within one bf16 step (2^-8 relative to the largest value) of the "
+                                                 "CPU oracle's fp32 result rounded to bf16"},
                           "device_status": status, "points": points}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if check and worst > 2.0 ** -8:
+        raise SystemExit(f"bench.py sweep: a point is {worst:.3e} away from the oracle (bar 2^-8)")
 
 
 def run_kernels(args):
@@ -614,12 +956,7 @@ def run_kernels(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     R, K = args.kernel_rows, 12288
-    peaks = {}
-    try:
-        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
-            peaks = json.load(f)
-    except OSError:
-        pass
+    peaks = load_peaks()
     hbm = peaks.get("hbm_gbs") or 6650.0
     g = torch.Generator().manual_seed(11)
     x32 = torch.randn(R, K, generator=g).to(dev)
@@ -635,12 +972,15 @@ def run_kernels(args):
     xn = x16.view(1, R * K // 1536, 1536)
     yn, on = torch.randn_like(xn), torch.empty_like(xn)
     mod = (torch.randn(1, 2 * 1536, generator=g) * 0.3).to(torch.bfloat16).to(dev)
+    smooth = (torch.rand(K, generator=g) + 0.5).to(dev)
     cases = [
         ("act_quant bf16 -> int8, 4 segments", lambda: ops.quantize_act(x16, bounds, sx, None, L.SQ_Q_INT8), R * K * 3),
         ("act_quant bf16 -> e4m3 DualScale", lambda: ops.quantize_act(x16, bounds, sx, sxn, L.SQ_Q_E4M3), R * K * 4),
         ("act_quant GELU(bf16) -> int8 DualScale", lambda: ops.quantize_act(x16, bounds, sx, sxn, L.SQ_Q_INT8, pre_act="gelu_tanh"), R * K * 4),
         ("act_quant fp32 -> int8, 4 segments", lambda: ops.quantize_act(x32, bounds, sx, None, L.SQ_Q_INT8), R * K * 5),
         ("act_quant_dynamic bf16 -> int8 per token", lambda: ops.quantize_act_dynamic(x16, [0, K], L.SQ_Q_INT8), R * K * 3 + R * 4),
+        ("act_quant_dynamic bf16 -> int8 per token, rows of 3072", lambda: ops.quantize_act_dynamic(x16.view(-1, 3072), [0, 3072], L.SQ_Q_INT8), R * K * 3 + R * 16),
+        ("act_quant_dynamic bf16 / smooth -> int8 per token", lambda: ops.quantize_act_dynamic(x16, [0, K], L.SQ_Q_INT8, smooth=smooth), R * K * 3 + R * 4),
         ("weight_quant bf16 -> int8 per row", lambda: ops.quantize_weight(x16, wq8, sw_row, L.SQ_Q_INT8), R * K * 3),
         ("weight_quant bf16 -> packed int4, groups of 128", lambda: ops.quantize_weight(x16, wq4, sw_grp, L.SQ_Q_INT4, group_size=128),
          R * K * 2.5 + R * K // 128 * 4),
@@ -654,16 +994,7 @@ def run_kernels(args):
     ]
     rows = []
     for name, fn, nbytes in cases:
-        for _ in range(max(args.warmup, 3)):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = timed(fn, args.steps, warmup=max(args.warmup, 3))
         rows.append({"kernel": name, "ms": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / hbm, "bytes": nbytes})
     print(json.dumps({"metric": "hbm_kernel_gbs", "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
                       "value": max(r["gbs"] for r in rows), "peak": hbm, "peak_source": "measured" if peaks.get("hbm_gbs") else "fallback",
@@ -674,18 +1005,24 @@ def run_kernels(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep", "kernels"],
                     help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep), "
                          "kernels (the HBM-bound quantise / unpack kernels against the measured copy bandwidth)")
+    ap.add_argument("--configs", default="all", choices=["all", "gpu", "none"],
+                    help="layer at N = 1: also measure the other BASELINE configurations (all), without their CPU baselines (gpu), or not at all (none)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "fused", "nccl"], help="layer at N > 1: how output column blocks are exchanged")
     ap.add_argument("--out-proj-segments", type=int, default=1, help="mmdit: K-segments of the attention output projections (1 or 24)")
+    ap.add_argument("--mmdit-batch", type=int, default=0, help="mmdit: batch per GPU (default 2 on one GPU, 16 / N on N)")
     ap.add_argument("--no-graph", action="store_true", help="mmdit: launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu", action="store_true", help="mmdit: skip the CPU baseline (one fake-quant block on the host cores)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384")
     ap.add_argument("--sweep-iters", type=int, default=10)
     ap.add_argument("--fused-gather", action="store_true",
-                    help="sweep at N > 1: also time the fused form (epilogue stores every tile into all ranks' buffers over NVLink)")
+                    help="sweep at N > 1: also time the exchanges through symmetric memory (fused epilogue stores, block push)")
+    ap.add_argument("--no-check", action="store_true", help="sweep: skip the per-point check against the CPU oracle")
     ap.add_argument("--sweep-nk", default="", help="sweep: comma list of NxK pairs (default: the seven shapes of config[4])")
     ap.add_argument("--sweep-modes", default="int8,fp8,w4a8")
     ap.add_argument("--sweep-segs", default="1,2,4,8")

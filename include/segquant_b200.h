@@ -290,6 +290,16 @@ typedef struct sq_gemm_args {
 
 int sq_gemm(const sq_gemm_args* args, sq_stream_t stream);
 
+/* ---- exchange step of a column-sharded layer (no counterpart in the reference, which is single-GPU) ----------
+ * Copies the [rows, width_bytes] block that starts at src_dev (rows src_row_stride_bytes apart) -- this rank's column
+ * block, already in place inside its own [rows, N] result -- to num_peers peer GPUs' matrices: peer_dst_dev[j] points
+ * at the block's position in peer j's matrix (HOST array of device pointers into peer memory mapped into this process),
+ * rows dst_row_stride_bytes apart.  Plain 16-byte stores over NVLink, whole 512-byte row segments per warp; nothing is
+ * read from a peer and nothing waits: order the ranks with a stream-ordered barrier before anyone reads its matrix.
+ * width, strides and all pointers must be multiples of 16 bytes. */
+int sq_push_columns(const void* src_dev, int64_t rows, int64_t width_bytes, int64_t src_row_stride_bytes,
+                    int32_t num_peers, void* const* peer_dst_dev, int64_t dst_row_stride_bytes, sq_stream_t stream);
+
 /* Number of accumulation units sq_gemm will use for these segment bounds / group size
    (the `units` of the acc_dump layout).  Negative = error. */
 int sq_gemm_num_units(int32_t num_segs, const int32_t* seg_bounds, int32_t group_size);

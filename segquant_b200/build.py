@@ -15,7 +15,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsegquant_b200.so")
-SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu", "seg_gemv.cu", "static_scratch.cu", "gated_residual.cu",
+SOURCES = ["capi.cu", "act_quant.cu", "weight_quant.cu", "seg_gemm.cu", "seg_gemv.cu", "static_scratch.cu", "gated_residual.cu", "peer_push.cu",
            # one translation unit per (kind, DualScale): the GEMM kernels dominate compile time and build in parallel
            "seg_gemm_tu_i8.cu", "seg_gemm_tu_i8_dual.cu", "seg_gemm_tu_f8.cu", "seg_gemm_tu_f8_dual.cu",
            "seg_gemm_tu_w4.cu", "seg_gemm_tu_w4_dual.cu"]

@@ -34,6 +34,8 @@ long long read_device_status();
 int set_gemm_schedule(int bn, int two_cta, int ksub, int no_gemv);
 int set_wait_limit(long long cycles);
 int wait_probe(long long limit_cycles, int* out_dev, cudaStream_t st);
+int push_columns(const void* src, long long rows, long long width_bytes, long long src_row_stride, int n_peers,
+                 void* const* peer_dst, long long dst_row_stride, cudaStream_t st);
 
 }  // namespace sq
 
@@ -135,6 +137,13 @@ int sq_unpack_int4(const void* packed_dev, void* out_dev, int64_t numel, sq_stre
 int sq_gemm(const sq_gemm_args* args, sq_stream_t stream) {
     sq::clear_error();
     return sq::gemm(args, static_cast<cudaStream_t>(stream));
+}
+
+int sq_push_columns(const void* src_dev, int64_t rows, int64_t width_bytes, int64_t src_row_stride_bytes, int32_t num_peers,
+                    void* const* peer_dst_dev, int64_t dst_row_stride_bytes, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::push_columns(src_dev, rows, width_bytes, src_row_stride_bytes, num_peers, peer_dst_dev, dst_row_stride_bytes,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int sq_gemm_num_units(int32_t num_segs, const int32_t* seg_bounds, int32_t group_size) {

@@ -364,6 +364,23 @@ def device_status():
     return int(L.load().sq_device_status())
 
 
+def push_columns(block, peer_ptrs, peer_row_stride_bytes):
+    """Copy the 2-D view `block` ([rows, width], a column block inside this rank's result matrix, last dim contiguous) to
+    the device addresses peer_ptrs (the block's position inside each peer GPU's matrix, mapped into this process)."""
+    global launch_count
+    _need_cuda(block)
+    if block.dim() != 2 or block.stride(1) != 1:
+        raise ValueError("push_columns needs a [rows, width] view with a contiguous last dim")
+    if not peer_ptrs:
+        return
+    esz = block.element_size()
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+    with torch.cuda.device(block.device):
+        L.check(L.load().sq_push_columns(block.data_ptr(), block.shape[0], block.shape[1] * esz, block.stride(0) * esz, len(peer_ptrs),
+                                         arr, int(peer_row_stride_bytes), _stream(block)), "sq_push_columns")
+    launch_count += 1
+
+
 def check_device():
     """Synchronise and raise SegQuantError(SQ_ERR_DEVICE_TIMEOUT) if a kernel reported a bounded wait that ran out."""
     L.check(L.load().sq_check_device(), "sq_check_device")

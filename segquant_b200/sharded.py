@@ -1,17 +1,32 @@
 """Column-sharded SegmentLinear: output features split over the ranks of a torch.distributed
-process group (one process per GPU), activations replicated, one all-gather of output slices.
+process group (one process per GPU), activations replicated, one exchange of output column blocks.
 
 The reference has no distributed code at all; this is the multi-GPU form of its layer asked for by
 the large-N GEMM sweep.  Rank r owns rows [r*N/g, (r+1)*N/g) of the weight (with their scales and
-bias), quantises its own copy of x (cheaper than broadcasting the quantised bytes), runs the fused
-layer forward on its slice and the slices are exchanged with NCCL `all_gather_into_tensor` over
-NVLink.  The exchange moves (g-1)/g * M*N*2 bytes in and out of every GPU, which at B200 tensor
-rates costs more than the GEMM itself for every K <= 12288; `forward` therefore reports nothing
-by itself -- bench.py times the GEMM phase and the whole step separately.
+bias), quantises its own copy of x (cheaper than broadcasting the quantised bytes: quantising reads
+3 bytes per element from HBM, receiving them would move 1 byte per element over NVLink, which is an
+order of magnitude slower) and runs the fused layer forward on its slice.  Three ways to exchange:
 
-forward_fused() is the fused form: the peers' output buffers are mapped into every process (symmetric
-memory) and the GEMM epilogue stores each finished tile into all of them, so the exchange overlaps the
-mainloop tile by tile and no gather kernel or interleave copy runs; only a barrier follows.
+forward()        the baseline: NCCL `all_gather_into_tensor` of the [M, N/g] slices into a (g, M, N/g) buffer, then
+                 a permuting copy into [M, N].
+forward_push()   every rank's [M, N] result lives in symmetric memory; the GEMM writes the rank's column block in
+                 place, then ONE kernel (ops.push_columns) stores that block into the same columns of every peer's
+                 matrix: final layout, whole 512-byte row segments on the wire, no gather buffer, no permute.
+forward_fused()  the exchange inside the GEMM epilogue: every finished tile goes to the rank's own matrix and to every
+                 peer's by TMA stores while the mainloop of the next tile runs.  Wins when the GEMM is long enough to
+                 hide the stores; its 32-byte row segments make it slower than forward_push() when the exchange, not
+                 the GEMM, sets the time.
+A one-word all-reduce on the compute stream orders the ranks after either of the last two.
+
+Buffer rule of forward_push / forward_fused: results are views of TWO symmetric buffers used alternately.  The view
+returned by call n is overwritten by PEERS during their call n + 2, which they can only start after this rank has
+passed the barrier of call n + 1; so anything enqueued on the compute stream BEFORE this rank's call n + 1 may read
+call n's result, and nothing later may.  (With a single buffer a peer's call n + 1 could overwrite the result while this
+rank's consumers of call n were still running: the barrier after the GEMM only orders the GEMMs.)
+
+The exchange moves (g-1)/g * M*N*2 bytes in and out of every GPU, which at B200 tensor rates costs more than the GEMM
+itself for every K <= 12288 at g = 8; bench.py therefore reports GEMM-only, exchange and total times separately, next
+to the NVLink-bound ceiling.
 """
 import torch
 import torch.distributed as dist
@@ -24,6 +39,12 @@ def shard_range(n_total, world, rank):
         raise ValueError(f"N={n_total} is not divisible by world size {world}")
     per = n_total // world
     return rank * per, (rank + 1) * per
+
+
+def row_range(m_total, world, rank):
+    """[begin, end) of the input rows rank `rank` brings in from the host (forward_from_host_rows)."""
+    per = (m_total + world - 1) // world
+    return min(rank * per, m_total), min((rank + 1) * per, m_total)
 
 
 def assemble(gathered):
@@ -50,6 +71,7 @@ class ColumnShardedSegLinear:
 
     def __init__(self, local_layer, rank, world, n_total, group=None):
         self.layer, self.rank, self.world, self.n_total, self.group = local_layer, rank, world, n_total, group
+        self._bufs, self._peer_ptrs, self._flag, self._calls = None, None, None, 0
 
     @classmethod
     def from_full(cls, x_calib, weight, bias, rank, world, kernel_type="Wint8Aint8", dual_scale=False, seg_mode="input",
@@ -71,6 +93,10 @@ class ColumnShardedSegLinear:
         layer.finish_calibrate()
         return cls(layer, rank, world, n_total, group)
 
+    def _device(self):
+        opt = getattr(self.layer, "optimizer", None)
+        return opt.weight_manager.device() if opt is not None else torch.device("cpu")
+
     def local_forward(self, x):
         return self.layer(x)
 
@@ -82,39 +108,90 @@ class ColumnShardedSegLinear:
 
     __call__ = forward
 
-    # ---- fused all-gather: the GEMM epilogue stores every tile into all ranks' [M, N] buffers ----------
-    def enable_fused_gather(self, max_rows, dtype=torch.bfloat16):
-        """Allocate this rank's [max_rows, N] output in symmetric memory and exchange the mappings (one
-        rendezvous; NCCL group).  After this, forward_fused() replaces local GEMM + all-gather + interleave."""
+    # ---- exchanges through symmetric memory --------------------------------------------------------------
+    def enable_symmetric(self, max_rows, dtype=torch.bfloat16):
+        """Allocate this rank's two [max_rows, N] result buffers in symmetric memory and exchange the mappings (one
+        rendezvous each; NCCL group).  Needed once before forward_push() / forward_fused()."""
         import torch.distributed._symmetric_memory as symm
-        dev = self.layer.bias_data.device if self.layer.bias_data is not None else self.layer.optimizer.weight_manager.device()
+        dev = self._device()
         group = self.group if self.group is not None else dist.group.WORLD
-        self._full = symm.empty((max_rows, self.n_total), dtype=dtype, device=dev)
-        self._handle = symm.rendezvous(self._full, group)
-        self._peer_ptrs = [int(p) for r, p in enumerate(self._handle.buffer_ptrs) if r != self.rank]
+        self._bufs, self._peer_ptrs = [], []
+        for _ in range(2):
+            buf = symm.empty((max_rows, self.n_total), dtype=dtype, device=dev)
+            handle = symm.rendezvous(buf, group)
+            self._bufs.append(buf)
+            self._peer_ptrs.append([int(p) for r, p in enumerate(handle.buffer_ptrs) if r != self.rank])
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._calls = 0
 
-    def forward_fused(self, x):
-        """x [M, K] (same on every rank).  Every rank's epilogue writes its column slice into its own buffer
-        (TMA stores) and into every peer's buffer (plain stores over NVLink); a one-word all-reduce then orders all
-        ranks' kernels before anyone reads.  Returns this rank's full [M, N] result (a view of the symmetric buffer:
-        it is overwritten by the next call)."""
+    enable_fused_gather = enable_symmetric      # earlier name
+
+    def _next_buffer(self, m):
+        if self._bufs is None:
+            raise RuntimeError("call enable_symmetric(max_rows) first")
+        if m > self._bufs[0].shape[0]:
+            raise ValueError(f"{m} rows exceed the {self._bufs[0].shape[0]} rows the symmetric buffers were sized for")
+        i = self._calls & 1
+        self._calls += 1
+        return self._bufs[i][:m], self._peer_ptrs[i]
+
+    def _barrier(self):
+        dist.all_reduce(self._flag, group=self.group)   # stream-ordered: completes after every rank's stores were issued and landed
+
+    def forward_push(self, x):
+        """x [M, K] (same on every rank).  GEMM into this rank's columns of its own matrix, then one push of that block to
+        every peer, then the barrier.  Returns this rank's full [M, N] result (see the buffer rule in the module docstring)."""
+        from . import ops
         m = x.shape[0]
         lo, hi = shard_range(self.n_total, self.world, self.rank)
-        full = self._full[:m]
-        self.layer(x.unsqueeze(0), out=full[:, lo:hi].unsqueeze(0), peer_outputs=(self._peer_ptrs, self.n_total, lo))
-        dist.all_reduce(self._flag, group=self.group)   # stream-ordered barrier: completes after every rank's GEMM
+        full, peers = self._next_buffer(m)
+        mine = full[:, lo:hi]
+        self.layer(x.unsqueeze(0), out=mine.unsqueeze(0))
+        esz = full.element_size()
+        ops.push_columns(mine, [p + lo * esz for p in peers], self.n_total * esz)
+        self._barrier()
         return full
 
-    # bytes one GPU sends to its peers above which the NCCL all-gather is faster than the fused stores (measured on
-    # 2 and 8 B200s: the epilogue's 32-row x 16-column boxes are 32-byte row segments on NVLink, which costs bandwidth
-    # once the exchange, not the GEMM, sets the time)
-    FUSED_MAX_BYTES = 70 * 1024 * 1024
+    def forward_fused(self, x):
+        """x [M, K] (same on every rank).  Every rank's epilogue writes its column block into its own matrix and into
+        every peer's (TMA stores over NVLink) while the next tile's mainloop runs; then the barrier.  Returns this rank's
+        full [M, N] result (see the buffer rule in the module docstring)."""
+        m = x.shape[0]
+        lo, hi = shard_range(self.n_total, self.world, self.rank)
+        full, peers = self._next_buffer(m)
+        self.layer(x.unsqueeze(0), out=full[:, lo:hi].unsqueeze(0), peer_outputs=(peers, self.n_total, lo))
+        self._barrier()
+        return full
+
+    # bytes one GPU sends to its peers above which pushing the finished block is faster than storing tile by tile from the
+    # epilogue (measured on 2 and 8 B200s)
+    FUSED_MAX_BYTES = 24 * 1024 * 1024
 
     def forward_auto(self, x):
-        """Fused exchange for small and medium outputs, NCCL all-gather for large ones.  x [M, K]."""
-        out_bytes = x.shape[0] * (self.n_total // self.world) * 2 * (self.world - 1)
-        if getattr(self, "_full", None) is not None and x.dim() == 2 and x.shape[0] <= self._full.shape[0] \
-                and out_bytes <= self.FUSED_MAX_BYTES:
-            return self.forward_fused(x)
-        return self.forward(x)
+        """Fused exchange while the GEMM can hide it, block push for large outputs, NCCL all-gather without symmetric
+        memory.  x [M, K]."""
+        if self._bufs is None or x.dim() != 2 or x.shape[0] > self._bufs[0].shape[0]:
+            return self.forward(x)
+        out_bytes = x.shape[0] * (self.n_total // self.world) * self._bufs[0].element_size() * (self.world - 1)
+        return self.forward_fused(x) if out_bytes <= self.FUSED_MAX_BYTES else self.forward_push(x)
+
+    def forward_from_host_rows(self, x_rows_host, m_total, exchange="auto"):
+        """End-to-end form for inputs that start in HOST memory: every rank copies only ITS row block of x
+        (row_range(m_total, world, rank), pinned memory) over PCIe, the blocks are all-gathered over NVLink into the
+        replicated [M, K] activation (rows are contiguous, so the gather is the final layout), then the sharded forward
+        runs.  The whole input crosses PCIe once in total instead of once per rank."""
+        dev = self._device()
+        k = x_rows_host.shape[1]
+        lo, hi = row_range(m_total, self.world, self.rank)
+        per = (m_total + self.world - 1) // self.world
+        x_full = torch.empty((per * self.world, k), dtype=x_rows_host.dtype, device=dev)
+        x_full[lo:hi].copy_(x_rows_host, non_blocking=True)
+        if dist.get_backend(self.group) == "nccl":
+            dist.all_gather_into_tensor(x_full, x_full[self.rank * per:(self.rank + 1) * per], group=self.group)
+        else:
+            parts = [torch.empty((per, k), dtype=x_full.dtype, device=dev) for _ in range(self.world)]
+            dist.all_gather(parts, x_full[self.rank * per:(self.rank + 1) * per].contiguous(), group=self.group)
+            x_full = torch.cat(parts)
+        x = x_full[:m_total]
+        fn = {"auto": self.forward_auto, "push": self.forward_push, "fused": self.forward_fused, "nccl": self.forward}[exchange]
+        return fn(x)

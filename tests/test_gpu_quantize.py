@@ -46,6 +46,7 @@ def test_quantize_real_path_equals_reference_quantize_and_round_trips(golden, na
     y = qm(x, c)
     assert ops.launch_count - n0 == 2 * 6                                 # quantise + GEMM per replaced linear: the native path ran
     want = torch.from_numpy(g["y"]).to(DEV)
+    y = y.detach()
     rel = float((y - want).abs().max() / want.abs().max())
     assert rel <= 1e-2 and cosine(y, want) >= 0.9999, (rel, cosine(y, want))   # stated tolerance vs the reference's fake-quant model
     buf = io.BytesIO()
@@ -70,10 +71,18 @@ def test_quantize_w4a8_svd_segments_packed_layout_round_trip(native_lib):
     y_float = model(*batches[0][0])
     qm = quantize(model, batches, cfg, seg_map=seg_map, dual_scale=["norm_lin", "ff.2"])
     h = 64
+    # storage: [N, K/2] bytes row-major (what the GEMM's TMA loads read); iter_view() hands out the reference's
+    # (segments, bytes) form: contiguous per N-chunk, gathered per K-slice
     wt = qm.norm_lin.optimizer.weight_manager
-    assert wt.packed and wt.weight_tensor.dtype == torch.uint8 and wt.weight_tensor.shape == (6, h * h // 2)     # (S, N/S * K / 2)
+    assert wt.packed and wt.weight_tensor.dtype == torch.uint8 and wt.weight_tensor.shape == (6 * h, h // 2)
+    assert wt.iter_view().shape == (6, h * h // 2) and wt.iter_view().data_ptr() == wt.weight_tensor.data_ptr()
     wk = qm.ff[2].optimizer.weight_manager
-    assert wk.packed and wk.weight_tensor.shape == (h, 4 * h // 2)                                                 # [N, K/2]
+    assert wk.packed and wk.weight_tensor.shape == (h, 4 * h // 2)
+    seg_bytes = wk.iter_view()
+    assert seg_bytes.shape == (2, h * (2 * h) // 2)
+    full = ops.unpack_int4(wk.weight_tensor.reshape(-1)).view(h, 4 * h)
+    for s_ in range(2):                                     # segment s of the reference layout = packed W[:, s K/2 : (s+1) K/2]
+        assert torch.equal(ops.unpack_int4(seg_bytes[s_].contiguous()).view(h, 2 * h), full[:, s_ * 2 * h:(s_ + 1) * 2 * h])
     assert qm.to_q.optimizer.weight_manager.weight_tensor.numel() == h * h // 2
     x, c = batches[0][0]
     y = qm(x, c)

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from segquant_b200.sharded import ColumnShardedSegLinear, all_gather_slices, assemble, shard_range
+from segquant_b200.sharded import ColumnShardedSegLinear, all_gather_slices, assemble, row_range, shard_range
 
 
 def test_shard_range_and_assemble():
@@ -20,6 +20,7 @@ def test_shard_range_and_assemble():
     parts = torch.arange(2 * 3 * 4).view(2, 3, 4)
     full = assemble(parts)
     assert full.shape == (3, 8) and torch.equal(full[:, :4], parts[0]) and torch.equal(full[:, 4:], parts[1])
+    assert [row_range(5, 2, r) for r in range(2)] == [(0, 3), (3, 5)] and row_range(2, 4, 3) == (2, 2)
 
 
 def _free_port():
@@ -49,6 +50,13 @@ def _worker(rank, world, port, ret):
         layer = ColumnShardedSegLinear(_PlainSlice(w[lo:hi], b[lo:hi]), rank, world, 12)
         y = layer(x)
         ok = torch.allclose(y, x @ w.t() + b, atol=1e-6) and y.shape == (5, 3, 12)
+        # host-sharded input: every rank brings its own row block, the blocks are gathered, then the sharded forward runs
+        x2 = torch.randn(5, 16, generator=g)                       # 5 rows over 2 ranks: blocks of 3 and 2
+        r0, r1 = row_range(5, world, rank)
+        y2 = layer.forward_from_host_rows(x2[r0:r1].clone(), 5, exchange="nccl")
+        ok = ok and y2.shape == (5, 12) and torch.allclose(y2, x2 @ w.t() + b, atol=1e-6)
+        with pytest.raises(RuntimeError):
+            layer.forward_push(x2)                                  # symmetric buffers were never set up
         buf = all_gather_slices(torch.full((2, 3), float(rank)))
         ok = ok and buf.shape == (world, 2, 3) and all(bool((buf[r] == r).all()) for r in range(world))
         ret[rank] = bool(ok)
