@@ -326,7 +326,10 @@ int sq_seg_linear(const sq_act_quant_args* q, const sq_gemm_args* g, sq_stream_t
  * library routine).
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- * that device current); make that first call before starting any stream capture.
+ * that device current); make that first call before starting any stream capture.  With the runtime's
+ * lazy module loading that first call is also where the device reserves the array itself: if the
+ * device cannot hold it the call returns SQ_ERR_CUDA and nothing is launched, so a process with a
+ * frozen memory budget should make this first call while it still sets that budget up.
  * All calls share the one array, and it keeps whatever the last call left there: two calls whose GPU
  * work can overlap (different streams, or different host threads) race on it and must be ordered by
  * the caller.  Nothing in it needs to be cleared between calls.

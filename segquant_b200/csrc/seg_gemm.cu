@@ -338,7 +338,10 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
     p.bn = sched.bn;
     p.dual_db = (dual && p.bn <= 128) ? 1 : 0;
-    p.all_magic = max_unit_k(a->num_segs, a->seg_bounds, a->group_size) <= 224 ? 1 : 0;
+    // short units of an integer kind: accumulators start from a magic bit pattern and are read as floats (seg_gemm_kernels.cuh);
+    // the dump (tests) and peer-store variants of the epilogue use plain conversions on accumulators that start from zero
+    p.all_magic = (a->kind != SQ_GEMM_W8A8_F8 && a->acc_dump_dev == nullptr && a->num_peer_outputs == 0 &&
+                   max_unit_k(a->num_segs, a->seg_bounds, a->group_size) <= 224) ? 1 : 0;
     p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
 

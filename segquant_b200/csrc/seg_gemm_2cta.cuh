@@ -138,7 +138,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int BKS = BK * KSUB;   // K covered by one stage
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_ld[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_bp[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
@@ -166,7 +166,6 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(smem_u32(&bar_empty[i]), 1);
             mbar_init(smem_u32(&bar_cvt[i]), 8);
             mbar_init(smem_u32(&bar_bp[i]), 1);
-            mbar_init(smem_u32(&bar_ld[i]), 4);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_tmem_full[i]), 1);
@@ -192,6 +191,13 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     cluster_sync_all();   // both CTAs' barriers exist before anything can signal them
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    if (p.all_magic) {   // both CTAs fill their own tensor memory before the leader's first MMA may write either
+        if (warp >= 4 && warp < 12) tmem_fill_magic(tmem_base, warp);
+        tc_fence_before();
+        __syncthreads();
+        cluster_sync_all();
+        tc_fence_after();
+    }
 
     const int tiles_per_batch = p.tiles_m * p.tiles_n;   // tiles_m counts 256-row tiles here
     const long long first_tile = cluster_id_x();
@@ -258,7 +264,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
                     int u_end = k_beg;
-                    uint32_t accumulate = 0;
+                    uint32_t accumulate = p.all_magic ? 1u : 0u;
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
                         if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
@@ -286,7 +292,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             cur_buf = buf;
                             d_pos = tmem_base + buf * BN;
                             d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                            accumulate = 0;
+                            accumulate = p.all_magic ? 1u : 0u;
                             u_end = unit_end(p, s, kb);
                             ++au;
                         }
@@ -322,7 +328,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     cur_buf = buf;
                                     d_pos = tmem_base + buf * BN;
                                     d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                                    accumulate = 0;
+                                    accumulate = p.all_magic ? 1u : 0u;
                                     u_end = unit_end(p, s, k);
                                     ++au;
                                 }
@@ -382,7 +388,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         const int left = k_end - kb;
                         const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;
                         // packed bytes sit in the upper half of the buffer they expand into: pull every chunk into
-                        // registers, meet the other expansion warps on a bounded barrier, then write
+                        // registers, meet the other expansion warps on a hardware barrier, then write
                         uint4 pk[KSUB][4];
 #pragma unroll
                         for (int jsub = 0; jsub < KSUB; ++jsub) {
@@ -395,9 +401,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 }
                             }
                         }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
-                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");   // see the one-CTA kernel: all four warps passed the same phase of bar_bp
 #pragma unroll
                         for (int jsub = 0; jsub < KSUB; ++jsub) {
                             if (jsub >= nsub) break;

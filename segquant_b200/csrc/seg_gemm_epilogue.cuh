@@ -19,9 +19,10 @@
 // no cursor arithmetic, no global loads, no divisions.  Tensor-memory loads are software-pipelined
 // (the next chunk is in flight while the current one is converted), the table is read with 128-bit
 // broadcast loads, the fp32 math uses the packed two-wide instructions, and int32 -> fp32 uses one
-// integer add and one float subtract (both full rate) instead of the quarter-rate conversion when every
-// unit of the launch has K_unit <= 224, which guarantees |acc| < 2^22.  All forms are exact, so results
-// do not depend on which ran.
+// float subtract (full rate, packed) instead of the quarter-rate conversion when every unit of the launch has
+// K_unit <= 224, which guarantees |acc| < 2^22: tensor memory is then pre-filled with the bit pattern of 1.5 * 2^23
+// (kMagicBits), so an accumulator read as a float is 12582912 + sum.  All forms are exact, so results do not depend on
+// which ran.
 #pragma once
 
 constexpr int kMagicMaxUnitK = 224;
@@ -40,7 +41,7 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[16]) {
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
                    "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                  :
-                 : "memory");
+                 SQ_TMEM_CLOBBER);
 }
 // Tile index -> batch, first row of THIS CTA's 128 rows, first column of the tile.
 template <bool PAIR>
@@ -55,22 +56,28 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, long long tile,
 // ---------------------------------------------------------------------------------------------
 // Scale-table builder: 64 threads (warps 2 and 3).
 // ---------------------------------------------------------------------------------------------
-struct BuilderRegs {
-    float sw[4];     // weight scales of columns t, t+64, t+128, t+192 of the tile
-    float sx, sxn;   // segment activation scales (per-tensor mode)
-    float rx[2];     // per-token activation scales of rows t, t+64 (per-token mode)
-    float rxn[2];
-    float bias[4];   // bias of the same four columns (loaded for the last unit of a tile only)
-};
-
 // Every address formed here is in bounds even for columns / rows outside the problem (the index is
 // clamped to a valid one and the value replaced afterwards), and the optional pointers (bias, per-token
 // scales) are only dereferenced inside a block guarded by a warp-uniform test, through plain loads: a
 // load the compiler is free to speculate (a read-only intrinsic under a select) must never see a null
 // or out-of-range address.
+//
+// The builder must keep up with units that are a single K stage long (weight-scale groups of 128: a new table
+// every ~540 cycles of MMA work), so its loop carries as little as possible: only the four weight scales of the NEXT
+// unit are prefetched into registers (their loads are strided by the group count and miss the small L1 that is left
+// beside 227 KB of shared memory) together with the segment's activation scale; bias and
+// per-token scales, needed once per tile or only by per-token layers, are loaded where they are written.  Holding a
+// full second copy of every field in registers spilled to local memory under the control warps' small register
+// allowance, and those local round trips made the builder, not the drain, the slowest stage of the pipeline.
 template <bool DUAL>
-__device__ __forceinline__ void builder_load(const GemmParams& p, BuilderRegs& r, int t, int b, int m0, int n0, int s, int g,
-                                             bool per_token, bool want_bias) {
+__device__ __forceinline__ void builder_load_sw(const GemmParams& p, float (&sw)[4], float& sx, float& sxn, int t, int b, int n0, int s,
+                                                int g, bool per_token) {
+    sx = 1.0f;
+    sxn = 1.0f;
+    if (!per_token) {      // one uniform load each; fetched a unit ahead like the weight scales (an L1 miss here costs an L2 round trip)
+        sx = p.sx[b * p.sx_bs + s * p.sx_ss];
+        if (DUAL) sxn = p.sx_neg[b * p.sx_bs + s * p.sx_ss];
+    }
     const long long sw_base = b * p.sw_bs + s * p.sw_ss + g * p.sw_gs;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -78,43 +85,7 @@ __device__ __forceinline__ void builder_load(const GemmParams& p, BuilderRegs& r
         const bool valid = c < p.bn && n0 + c < p.N;
         const long long n = valid ? n0 + c : n0;          // n0 < N always
         const float w = load_sw(p, sw_base + n * p.sw_cs);
-        r.sw[i] = valid ? w : 1.0f;
-        r.bias[i] = 0.0f;
-    }
-    if (want_bias) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c = t + 64 * i;
-            const bool valid = c < p.bn && n0 + c < p.N;
-            const long long idx = b * p.bias_bs + (valid ? n0 + c : n0);
-            float v;
-            if (p.bias_dtype == SQ_F32) v = static_cast<const float*>(p.bias)[idx];
-            else if (p.bias_dtype == SQ_F16) v = __half2float(static_cast<const __half*>(p.bias)[idx]);
-            else v = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[idx]);
-            r.bias[i] = valid ? v : 0.0f;
-        }
-    }
-    const long long sx_base = b * p.sx_bs + s * p.sx_ss;
-    r.sx = 1.0f;
-    r.sxn = 1.0f;
-    r.rx[0] = r.rx[1] = 1.0f;
-    r.rxn[0] = r.rxn[1] = 1.0f;
-    if (!per_token) {
-        r.sx = p.sx[sx_base];
-        if (DUAL) r.sxn = p.sx_neg[sx_base];
-    } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const long long mm = m0 + t + 64 * j;
-            const bool valid = mm < p.M;
-            const long long m = valid ? mm : 0;            // row 0 always exists
-            const float a = p.sx[sx_base + m * p.sx_rs];
-            r.rx[j] = valid ? a : 1.0f;
-            if (DUAL) {
-                const float an = p.sx_neg[sx_base + m * p.sx_rs];
-                r.rxn[j] = valid ? an : 1.0f;
-            }
-        }
+        sw[i] = valid ? w : 1.0f;
     }
 }
 
@@ -125,52 +96,79 @@ __device__ __forceinline__ void table_builder(const GemmParams& p, uint8_t* tab,
     const int lane = threadIdx.x & 31;
     const bool per_token = p.sx_rs != 0;
     uint32_t au = 0;
-    BuilderRegs cur, nxt;
+    float sw_cur[4], sw_nxt[4], sx, sxn, sx_nxt = 1.0f, sxn_nxt = 1.0f;
     for (long long tile = first_tile; tile < p.total_tiles; tile += tile_step) {
         int b, m0, n0;
         tile_coords<PAIR>(p, tile, rank, b, m0, n0);
-        int s = 0, k = 0, g = 0;   // unit cursor: segment, first K index, weight group of k (k / group_size)
-        builder_load<DUAL>(p, cur, t, b, m0, n0, s, g, per_token, p.bias != nullptr && p.units == 1);
+        int s = 0, g = 0;   // unit cursor: segment and weight group (segments and groups are walked, never divided)
+        builder_load_sw<DUAL>(p, sw_cur, sx, sxn, t, b, n0, s, g, per_token);
         for (int u = 0; u < p.units; ++u, ++au) {
-            // end of this unit and cursor of the next one (segments and groups are walked, never divided)
             const int seg_end = p.seg_bounds[s + 1];
             const int grp_end = p.group_size > 0 ? (g + 1) * p.group_size : seg_end;
             const int ke = grp_end < seg_end ? grp_end : seg_end;
             const int s2 = ke == seg_end ? s + 1 : s;
-            (void)k;
             const int g2 = (p.group_size > 0 && ke == grp_end) ? g + 1 : g;
-            if (u + 1 < p.units) builder_load<DUAL>(p, nxt, t, b, m0, n0, s2, g2, per_token, p.bias != nullptr && u + 2 == p.units);
+            if (u + 1 < p.units) builder_load_sw<DUAL>(p, sw_nxt, sx_nxt, sxn_nxt, t, b, n0, s2, g2, per_token);
 
             const uint32_t slot = au & (kTabSlots - 1);
             const uint32_t par = (au / kTabSlots) & 1u;
+#ifdef SQ_TRACE_EPI
+            if (threadIdx.x == 64 && blockIdx.x == 0 && au < 500) g_trace[8 * au + 5] = clock64();
+#endif
             if (!mbar_wait(bar_tab_empty + slot * 8, par ^ 1u, abort_flag, kWaitTabEmpty, p.wait_cycles)) return;
+#ifdef SQ_TRACE_EPI
+            if (threadIdx.x == 64 && blockIdx.x == 0 && au < 500) g_trace[8 * au + 6] = clock64();
+#endif
             uint8_t* sl = tab + slot * kTabSlotBytes;
+            const long long sx_base = b * p.sx_bs + s * p.sx_ss;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int c = t + 64 * i;
-                float r = 1.0f / (cur.sx * cur.sw[i]);
-                float rn = DUAL ? 1.0f / (cur.sxn * cur.sw[i]) : 0.0f;
+                // correctly rounded reciprocal of the scale product (the value 1.0f / x has, without the division's slow path)
+                float r = __frcp_rn(sx * sw_cur[i]);
+                float rn = DUAL ? __frcp_rn(sxn * sw_cur[i]) : 0.0f;
                 if (KIND == SQ_GEMM_W4A8) { r *= 0.0625f; rn *= 0.0625f; }   // int4 weights are expanded as 16*w
                 reinterpret_cast<float*>(sl)[c] = r;
                 if (DUAL) reinterpret_cast<float*>(sl + kSlotRNeg)[c] = rn;
             }
-            if (p.bias != nullptr && u + 1 == p.units) {
+            if (p.bias != nullptr && u + 1 == p.units) {     // warp-uniform: the tile's bias, as fp32, rides in its last unit's slot
 #pragma unroll
-                for (int i = 0; i < 4; ++i) reinterpret_cast<float*>(sl + kSlotBias)[t + 64 * i] = cur.bias[i];
+                for (int i = 0; i < 4; ++i) {
+                    const int c = t + 64 * i;
+                    const bool valid = c < p.bn && n0 + c < p.N;
+                    const long long idx = b * p.bias_bs + (valid ? n0 + c : n0);
+                    float v;
+                    if (p.bias_dtype == SQ_F32) v = static_cast<const float*>(p.bias)[idx];
+                    else if (p.bias_dtype == SQ_F16) v = __half2float(static_cast<const __half*>(p.bias)[idx]);
+                    else v = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[idx]);
+                    reinterpret_cast<float*>(sl + kSlotBias)[c] = valid ? v : 0.0f;
+                }
             }
-            if (per_token) {
+            if (per_token) {                                 // warp-uniform
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    reinterpret_cast<float*>(sl + kSlotRx)[t + 64 * j] = 1.0f / cur.rx[j];
-                    if (DUAL) reinterpret_cast<float*>(sl + kSlotRxNeg)[t + 64 * j] = 1.0f / cur.rxn[j];
+                    const long long mm = m0 + t + 64 * j;
+                    const bool valid = mm < p.M;
+                    const long long m = valid ? mm : 0;      // row 0 always exists
+                    const float a = p.sx[sx_base + m * p.sx_rs];
+                    reinterpret_cast<float*>(sl + kSlotRx)[t + 64 * j] = valid ? __frcp_rn(a) : 1.0f;
+                    if (DUAL) {
+                        const float an = p.sx_neg[sx_base + m * p.sx_rs];
+                        reinterpret_cast<float*>(sl + kSlotRxNeg)[t + 64 * j] = valid ? __frcp_rn(an) : 1.0f;
+                    }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tab_full + slot * 8);
-            cur = nxt;
+#ifdef SQ_TRACE_EPI
+            if (threadIdx.x == 64 && blockIdx.x == 0 && au < 500) g_trace[8 * au + 7] = clock64();
+#endif
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sw_cur[i] = sw_nxt[i];
+            sx = sx_nxt;
+            sxn = sxn_nxt;
             s = s2;
             g = g2;
-            k = ke;
         }
     }
 }
@@ -197,14 +195,23 @@ __device__ __forceinline__ void fma16(float* acc, const uint32_t (&v)[16], const
             float2 f;
             if constexpr (KIND == SQ_GEMM_W8A8_F8) {
                 f = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            } else if constexpr (MAGIC) {   // exact for accumulators in [-2^22, 2^22)
-                f = __fadd2_rn(make_float2(__uint_as_float(v[j] + 0x4B400000u), __uint_as_float(v[j + 1] + 0x4B400000u)), unmagic);
+            } else if constexpr (MAGIC) {   // the accumulator started from kMagicBits: its bits ARE the float 12582912 + sum
+#ifdef SQ_DRAIN_SCALAR
+                f = make_float2(__uint_as_float(v[j]) - 12582912.0f, __uint_as_float(v[j + 1]) - 12582912.0f);
+#else
+                f = __fadd2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), unmagic);
+#endif
             } else {
                 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])), static_cast<float>(static_cast<int32_t>(v[j + 1])));
             }
+#ifdef SQ_DRAIN_SCALAR
+            acc[j] = fmaf(f.x, r.x, acc[j]);
+            acc[j + 1] = fmaf(f.y, r.y, acc[j + 1]);
+#else
             const float2 a = __ffma2_rn(f, r, make_float2(acc[j], acc[j + 1]));
             acc[j] = a.x;
             acc[j + 1] = a.y;
+#endif
         }
     }
 }
@@ -220,32 +227,81 @@ __device__ __forceinline__ void dump16(const GemmParams& p, const uint32_t (&v)[
         if (ncol + j < p.N) d[j] = KIND == SQ_GEMM_W4A8 ? (static_cast<int32_t>(v[j]) >> 4) : static_cast<int32_t>(v[j]);
 }
 
-// Drain of one unit: the tensor-memory load of the next 16-column chunk is in flight while the current
+// Drain of one unit: the tensor-memory load of the next batch of 16-column chunks is in flight while the current
 // one is consumed.  rt_pos / t_pos address the positive side; the negative side sits BN floats /
 // neg_cols TMEM columns further.  The variant (MAGIC, PER_TOKEN, DUMP) is chosen once per unit so the
 // code that runs is one contiguous block.
+// Chunks (of 16 columns) fetched per tensor-memory round trip, and whether the next batch is in flight while the
+// current one is consumed (tcgen05.wait::ld waits for ALL loads the thread has issued, so more bytes in flight means a
+// bigger batch).  Measured on layers whose units are one K stage long (weight-scale groups of 128), INT8 and W4A8:
+// batches of 32 or 64 columns are not faster than 16 (409 us vs 431 / 435 us at 4608 x 9216 x 3072), and 64-column
+// batches spill in the W4A8 epilogue, which has 200 registers instead of 224 -- the round trip is not what bounds the drain.
+#ifndef SQ_DRAIN_NB
+#define SQ_DRAIN_NB 1
+#endif
+#ifndef SQ_DRAIN_DB
+#define SQ_DRAIN_DB 1
+#endif
+
+// Orders every later use of the 16 registers after the statements above it (an empty volatile asm that "writes" them).
+__device__ __forceinline__ void touch16(uint32_t (&r)[16]) {
+    asm volatile(""
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 SQ_TMEM_CLOBBER);
+}
+
 template <int KIND, bool DUAL, bool MAGIC, bool PER_TOKEN, bool DUMP>
 __device__ __forceinline__ void drain_unit(const GemmParams& p, float (&acc)[128], uint32_t t_pos, const float* rt_pos, int hcols,
                                            float rxm, float rxnm, int b, int unit_in_tile, int m, bool row_ok, int ncol0) {
     constexpr int SIDES = DUAL ? 2 : 1;
+    constexpr int NB = SQ_DRAIN_NB;                   // chunks per batch
+    constexpr bool DB = SQ_DRAIN_DB != 0;             // double-buffered batches
     const int nld = (hcols >> 4) * SIDES;             // 16-column chunks per unit, sides interleaved
     const uint32_t neg_cols = p.dual_db ? 128u : static_cast<uint32_t>(BN);
-    uint32_t va[16], vb[16];
-    tmem_ld_x16(t_pos, va);
-    tmem_ld_wait_on(va);
+    uint32_t buf[DB ? 2 : 1][NB][16];
+    MagicRegs mg;
+    if constexpr (MAGIC) magic_regs_init(mg);
+    auto chunk_addr = [&](int i) {
+        return t_pos + static_cast<uint32_t>((i / SIDES) * 16) + ((DUAL && (i & 1)) ? neg_cols : 0u);
+    };
+    auto load_batch = [&](int i0, uint32_t (&dst)[NB][16]) {
 #pragma unroll
-    for (int i = 0; i < 8 * SIDES; ++i) {
-        if (i >= nld) break;
-        uint32_t (&cur)[16] = (i & 1) ? vb : va;
-        uint32_t (&nxt)[16] = (i & 1) ? va : vb;
-        if (i + 1 < nld)
-            tmem_ld_x16(t_pos + static_cast<uint32_t>(((i + 1) / SIDES) * 16) + ((DUAL && ((i + 1) & 1)) ? neg_cols : 0u), nxt);
-        const int c0 = (i / SIDES) * 16;
-        const bool neg = DUAL && (i & 1);
-        fma16<KIND, MAGIC, PER_TOKEN>(&acc[c0], cur, rt_pos + (neg ? BN : 0) + c0, neg ? rxnm : rxm);
-        if (DUMP && row_ok) dump16<KIND>(p, cur, b, unit_in_tile, SIDES, neg ? 1 : 0, m, ncol0 + c0);
-        if (i + 1 < nld) tmem_ld_wait_on(nxt);
+        for (int j = 0; j < NB; ++j)
+            if (i0 + j < nld) tmem_ld_x16(chunk_addr(i0 + j), dst[j]);
+    };
+    auto wait_batch = [&](uint32_t (&dst)[NB][16]) {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < NB; ++j) touch16(dst[j]);
+    };
+    load_batch(0, buf[0]);
+    wait_batch(buf[0]);
+#pragma unroll
+    for (int i0 = 0; i0 < 8 * SIDES; i0 += NB) {
+        if (i0 >= nld) break;
+        uint32_t (&cur)[NB][16] = buf[DB ? ((i0 / NB) & 1) : 0];
+        uint32_t (&nxt)[NB][16] = buf[DB ? (((i0 / NB) & 1) ^ 1) : 0];
+        if (DB && i0 + NB < nld) load_batch(i0 + NB, nxt);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int i = i0 + j;
+            if (i < nld) {
+                const int c0 = (i / SIDES) * 16;
+                const bool neg = DUAL && (i & 1);
+                if constexpr (MAGIC)   // chunk i is in registers: put the magic pattern back for the unit that accumulates here next
+                    tmem_st_x16(chunk_addr(i), mg);
+                fma16<KIND, MAGIC, PER_TOKEN>(&acc[c0], cur[j], rt_pos + (neg ? BN : 0) + c0, neg ? rxnm : rxm);
+                if (DUMP && row_ok) dump16<KIND>(p, cur[j], b, unit_in_tile, SIDES, neg ? 1 : 0, m, ncol0 + c0);
+            }
+        }
+        if (i0 + NB < nld) {
+            if (!DB) load_batch(i0 + NB, nxt);
+            wait_batch(nxt);
+        }
     }
+    if constexpr (MAGIC) tmem_st_wait();   // the refill has landed before the buffer is handed back to the MMA warp
 }
 
 // One tile for one epilogue warp.  `bar_tmem_empty` is the address arrivals go to: the CTA's own

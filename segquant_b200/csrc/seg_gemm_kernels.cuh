@@ -168,6 +168,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
     }
 }
 
+// Tensor-memory loads / stores / waits are volatile (kept in program order among themselves and with the barrier
+// operations) but do not clobber "memory": they touch nothing the compiler can see, and a memory clobber would pin the
+// epilogue's shared-memory table reads between them instead of letting them be issued early.
+#ifndef SQ_TMEM_CLOBBER
+#define SQ_TMEM_CLOBBER
+#endif
 // 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -176,9 +182,49 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
-        : "memory");
+        SQ_TMEM_CLOBBER);
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" :: SQ_TMEM_CLOBBER); }
+// 32 lanes x 8 consecutive 32-bit columns (thread t writes lane base + t) from 8 registers.  The refill of the magic
+// pattern passes the SAME eight registers every time (MagicRegs): a store needs its sources in one consecutive block,
+// and values the compiler cannot see through stay in the block they were first put in, so no copies are made per store.
+struct MagicRegs {
+    uint32_t r[8];
+};
+__device__ __forceinline__ void magic_regs_init(MagicRegs& m) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) asm volatile("mov.b32 %0, 0x4B400000;" : "=r"(m.r[i]));
+}
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const MagicRegs& m) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(m.r[0]), "r"(m.r[1]), "r"(m.r[2]), "r"(m.r[3]), "r"(m.r[4]), "r"(m.r[5]), "r"(m.r[6]), "r"(m.r[7])
+        SQ_TMEM_CLOBBER);
+}
+// 16 columns
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const MagicRegs& m) {
+    tmem_st_x8(taddr, m);
+    tmem_st_x8(taddr + 8u, m);
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" :: SQ_TMEM_CLOBBER); }
+
+// Bit pattern of 1.5 * 2^23.  An int32 accumulator that STARTS at this value and then collects a sum n with
+// |n| < 2^22 holds, read as a float, exactly 12582912 + n: the epilogue gets float(n) with one subtraction instead of
+// an integer add plus a subtraction (or a quarter-rate conversion).  Used when every accumulation unit of the launch is
+// short (GemmParams::all_magic): the epilogue warps fill tensor memory with the pattern before the first tile and put it
+// back after every chunk they drain, and the MMA warp always accumulates onto what it finds.
+constexpr uint32_t kMagicBits = 0x4B400000u;
+
+// Epilogue warp `warp` (4..11) fills its lane quarter of one half of tensor memory (256 columns) with the magic pattern.
+__device__ __forceinline__ void tmem_fill_magic(uint32_t tmem_base, int warp) {
+    const uint32_t lane_q = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t col0 = static_cast<uint32_t>((warp - 4) >> 2) * 256u;
+    MagicRegs mg;
+    magic_regs_init(mg);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) tmem_st_x16(tmem_base + lane_q + col0 + c * 16, mg);
+    tmem_st_wait();
+}
 
 template <uint32_t N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -408,7 +454,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr bool kW4 = C::kW4;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_ld[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_cvt[8], bar_tmem_full[2], bar_tmem_empty[2], bar_tab_full[kTabSlots], bar_tab_empty[kTabSlots];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
@@ -431,7 +477,6 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_u32(&bar_full[i]), 1);
             mbar_init(smem_u32(&bar_empty[i]), 1);
             mbar_init(smem_u32(&bar_cvt[i]), 4);
-            mbar_init(smem_u32(&bar_ld[i]), 4);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bar_tmem_full[i]), 1);
@@ -456,6 +501,12 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    if (p.all_magic) {   // warp-uniform: integer accumulators start from the magic pattern (see kMagicBits)
+        if (warp >= 4 && warp < 12) tmem_fill_magic(tmem_base, warp);
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
 
     const int tiles_per_batch = p.tiles_m * p.tiles_n;
 
@@ -511,7 +562,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
                     int u_end = k_beg;  // forces "new unit" at the first step of the segment
-                    uint32_t accumulate = 0;
+                    uint32_t accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
                     uint32_t d_pos = 0, d_neg = 0;
                     for (int kb = k_beg; ok && kb < k_end; kb += BK) {
                         SQ_FINE(0);
@@ -538,7 +589,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             cur_buf = buf;
                             d_pos = tmem_base + buf * BN;
                             d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                            accumulate = 0;
+                            accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
                             u_end = unit_end(p, s, kb);
                             ++au;
                         }
@@ -570,7 +621,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                     cur_buf = buf;
                                     d_pos = tmem_base + buf * BN;
                                     d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                                    accumulate = 0;
+                                    accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
                                     u_end = unit_end(p, s, k);
                                     ++au;
                                 }
@@ -630,7 +681,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         // term (row % 8) and qd do not depend on i, so the destination offsets inside a row are constants.
                         // Rows < 128 expand into the lower half, which holds no packed bytes: done first, straight from
                         // shared memory.  Rows >= 128 overwrite the packed area: their chunks are pulled into registers
-                        // up front, the four expansion warps meet on a (bounded) barrier once everybody has read, and only
+                        // up front, the four expansion warps meet on a barrier once everybody has read, and only
                         // then are they written.
                         const int row0 = ct >> 2, qd = ct & 3;
                         const int o0 = ((2 * qd) ^ (row0 & 7)) * 16, o1 = ((2 * qd + 1) ^ (row0 & 7)) * 16;
@@ -662,9 +713,11 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
                             if (row0 + 32 * i < p.bn) expand_store(lo4[i], i);
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_ld[st]));
-                        if (!mbar_wait(smem_u32(&bar_ld[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
+                        // Hardware barrier among the 128 expansion threads (an mbarrier round trip here cost ~200 cycles per
+                        // stage, 6 % of the kernel).  It cannot be left waiting by a warp that gave up: all four warps have just
+                        // passed the SAME phase of bar_full, which either completed (then each of them sees it completed: the phase
+                        // cannot advance before all four have arrived on bar_cvt below) or did not (then none of them gets here).
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
                         SQ_CVT(3);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)

@@ -60,7 +60,7 @@ struct GemmParams {
     int peer_tma;             // they are written by TMA stores (OutMaps::peer) rather than by the threads
     void* peer_y[SQ_MAX_PEERS];
     long long peer_rs, peer_co;
-    int all_magic;  // every accumulation unit has K <= 224: int32 accumulators stay inside [-2^22, 2^22)
+    int all_magic;  // integer kind, every accumulation unit has K <= 224 (|sum| < 2^22), no dump / peer stores: accumulators start from kMagicBits
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
     long long wait_cycles;  // SM cycles after which a bounded wait gives up (default 4e9, about 2 s)
 };

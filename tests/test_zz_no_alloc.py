@@ -5,8 +5,11 @@ process with a frozen memory budget, a loop barred from the allocator).
 Called through the C ABI and compared with sq_seg_linear (caller-provided scratch) on the same
 inputs, twice in a row with different shapes so that bytes left behind by the first call cannot
 help the second.  Both entry points run the same kernels, so the outputs must be identical; the
-comparison still uses the 1e-5 relative bound of the other GPU tests.  Collected last so a run that
-stops at the first failure has already run everything else; passes alone in a fresh process too.
+comparison still uses the 1e-5 relative bound of the other GPU tests.  The result is also held against
+the CPU oracle (bf16 output within one rounding step), and the property in the entry point's name is
+checked directly: once the first call on the device has been made, the free device memory the driver
+reports does not move across further calls.  Collected last so a run that stops at the first failure
+has already run everything else; passes alone in a fresh process too.
 """
 import ctypes
 
@@ -16,6 +19,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
+from oracle import oracle as O
 from segquant_b200 import _lib as L
 
 DEV = "cuda:0"
@@ -94,6 +98,22 @@ def test_static_scratch_forward_matches_caller_scratch_forward(native_lib):
         a, b = y_new.float().cpu().numpy(), y_ref.float().cpu().numpy()
         assert not np.isnan(a).any()
         assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
+        # against the CPU oracle: its own quantise and exact integer / fp32 GEMM on the same inputs
+        okind, oq = (O.GEMM_I8, O.Q_INT8) if kind == L.SQ_GEMM_W8A8_I8 else (O.GEMM_F8, O.Q_E4M3)
+        sxn_np = sxn.cpu().numpy() if dual else None
+        xq_o = O.quantize_act(x.float().cpu().numpy(), bounds, sx.cpu().numpy(), sx_neg=sxn_np, out_kind=oq)
+        want = O.seg_gemm(okind, xq_o[0] if dual else xq_o, wq.cpu().numpy(), bounds, sx.cpu().numpy(), sw.cpu().numpy(),
+                          xq_neg=xq_o[1] if dual else None, sx_neg=sxn_np, bias=bias.cpu().numpy())
+        want16 = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+        assert np.abs(a - want16).max() <= 2.0 ** -8 * np.abs(want16).max()
+        # no device allocation: free memory as the driver reports it is the same before and after further calls
+        # (tensors were all created above; the first call on this device, which looks up the array's address, is behind us)
+        free0, _ = torch.cuda.mem_get_info()
+        for _ in range(3):
+            L.check(lib.sq_seg_linear_static(ctypes.byref(q2), ctypes.byref(g2), _stream()), "sq_seg_linear_static")
+        torch.cuda.synchronize()
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0, f"device memory moved by {free0 - free1} bytes across sq_seg_linear_static calls"
     assert lib.sq_device_status() == 0
 
 
