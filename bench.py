@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 HM, HK, HN, HS, HSEED = 16384, 12288, 3072, 4, 5
 HEAD_NAME = f"config[4] point: W8A8 INT8 SegLinear M={HM} K={HK} N={HN}, {HS} K-segments (scales log-uniform in [0.25, 32]), bf16 in/out, seed {HSEED}"
 # profiles/seg_gemm2_int8_16384x3072x12288.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline GEMM
-HEAD_TRAFFIC_NCU = None
+HEAD_TRAFFIC_NCU = 515.3e6
 HEAD_TRAFFIC_SRC = "profiles/seg_gemm2_int8_16384x3072x12288.md"
 
 
@@ -563,7 +563,7 @@ def run_ours(args):
 
     # ---- sustained: the same step looped for more than a second (N = 1)
     sustained = None
-    if world == 1:
+    if world == 1 and not args.quick:
         n_sus = max(50, int(1300.0 / ms_step))
         ts0 = sampler.mark()
         ms_sus = timed(step, n_sus, warmup=0)
@@ -620,14 +620,15 @@ def run_ours(args):
                 host_y.copy_(y_full[o_lo:o_hi], non_blocking=True)
         e2e_mode = ("ColumnShardedSegLinear.forward_from_host_rows: every rank copies its 1/g of the input rows from pinned host memory, "
                     "the rows are all-gathered over NVLink, sharded forward + exchange, every rank reads back its 1/g of the output rows")
-    e2e_run(3)
+    e2e_steps = 1 if args.quick else args.steps
+    e2e_run(1 if args.quick else 3)
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
-    e2e_run(args.steps)
+    e2e_run(e2e_steps)
     e3.record()
     barrier()
-    (e2e_ms,) = max_over_ranks([e2.elapsed_time(e3) / args.steps])
+    (e2e_ms,) = max_over_ranks([e2.elapsed_time(e3) / e2e_steps])
     clocks = None
     if rank == 0:
         time.sleep(0.15)
@@ -638,7 +639,7 @@ def run_ours(args):
 
     status = ops.device_status()
     configs = None
-    if world == 1 and rank == 0 and args.configs != "none":
+    if world == 1 and rank == 0 and args.configs != "none" and not args.quick:
         del x, xq, y_loc
         torch.cuda.empty_cache()
         configs = config_entries(dev, peaks)
@@ -675,7 +676,7 @@ def run_ours(args):
             line["sharded"] = sharded
         if configs:
             line["configs"] = configs
-        if world == 1 and args.configs != "none":
+        if world == 1 and args.configs != "none" and not args.quick:
             line["cpu_baseline"] = {k: v for k, v in cpu_headline().items() if k != "ms_per_step"}
         else:
             line["cpu_baseline"] = {"value": None, "unit": "TOPS", "cores": os.cpu_count(), "kind": "reference",
@@ -946,6 +947,18 @@ def run_sweep(args):
         raise SystemExit(f"bench.py sweep: a point is {worst:.3e} away from the oracle (bar 2^-8)")
 
 
+def run_configs(args):
+    """The `configs` block of the default line on its own (configs 0-2 as layers; config 3 with --configs all / gpu):
+    what the ncu captures of those kernels run."""
+    from segquant_b200 import ops
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    out = config_entries(dev, load_peaks(), steps=args.steps)
+    if args.configs != "none":
+        out["config3_mmdit_step"] = mmdit_entry(dev, steps=max(2, args.steps // 4), cpu=args.configs == "all")
+    print(json.dumps({"metric": "seglinear_configs", "n_gpus": 1, "data": "synthetic", "configs": out, "device_status": ops.device_status()}), flush=True)
+
+
 def run_kernels(args):
     """The HBM-bound kernels alone on [rows, 12288] tensors (larger than L2): activation quantise (bf16 / fp32, single,
     DualScale, dynamic per-token), weight quantise (int8, packed int4 with group scales), int4 unpack, and the fused
@@ -1008,11 +1021,15 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="layer", choices=["layer", "mmdit", "sweep", "kernels"],
-                    help="layer (default, the headline line), mmdit (synthetic denoise step), sweep (GEMM sweep), "
-                         "kernels (the HBM-bound quantise / unpack kernels against the measured copy bandwidth)")
+    ap.add_argument("--workload", default="layer", choices=["layer", "configs", "mmdit", "sweep", "kernels"],
+                    help="layer (default, the headline line), configs (only the per-configuration entries of that line), mmdit "
+                         "(synthetic denoise step), sweep (GEMM sweep), kernels (the HBM-bound quantise / unpack kernels against "
+                         "the measured copy bandwidth)")
     ap.add_argument("--configs", default="all", choices=["all", "gpu", "none"],
                     help="layer at N = 1: also measure the other BASELINE configurations (all), without their CPU baselines (gpu), or not at all (none)")
+    ap.add_argument("--quick", action="store_true",
+                    help="layer: only the timed headline loop (no sustained leg, one end-to-end step, no configs, no CPU baseline): "
+                         "what the ncu captures of the headline kernels run")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "fused", "nccl"], help="layer at N > 1: how output column blocks are exchanged")
     ap.add_argument("--out-proj-segments", type=int, default=1, help="mmdit: K-segments of the attention output projections (1 or 24)")
     ap.add_argument("--mmdit-batch", type=int, default=0, help="mmdit: batch per GPU (default 2 on one GPU, 16 / N on N)")
@@ -1037,6 +1054,8 @@ def main():
         run_sweep(args)
     elif args.workload == "kernels":
         run_kernels(args)
+    elif args.workload == "configs":
+        run_configs(args)
     else:
         run_ours(args)
 

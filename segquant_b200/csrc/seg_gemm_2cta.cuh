@@ -212,43 +212,47 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t ph = 0;
             bool ok = true;
             const uint32_t tx_sub = 2u * kABytes * (DUAL ? 2 : 1) + (kW4 ? 0u : static_cast<uint32_t>(p.bn) * BK);   // both CTAs, one sub-tile
-            for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
-                const int b = static_cast<int>(tile / tiles_per_batch);
-                const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
-                const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
-                const int n0 = (rem % p.tiles_n) * p.bn + static_cast<int>(rank) * hb;
-                const int ab = p.a_batched ? b : 0;
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
-                    const int wk_off = p.w_seg_as_batch ? k_beg : 0;
-                    for (int k = k_beg; k < k_end; k += BKS) {
-                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
-                        if (lane == 0) {
-                            SQ_STAMP(0, 2 * trace_it);
-                            const int left = k_end - k;
-                            const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;   // sub-tiles that hold data
-                            const uint32_t full_leader = map_to_rank(smem_u32(&bar_full[st]), 0);
-                            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[st]), tx_sub * nsub);
-                            const uint32_t bp = smem_u32(&bar_bp[st]);
-                            if (kW4) mbar_arrive_expect_tx(bp, static_cast<uint32_t>(hb) * (BK / 2) * nsub);
-#pragma unroll
-                            for (int j = 0; j < KSUB; ++j) {
-                                if (j >= nsub) break;
-                                const int kj = k + j * BK;
-                                tma_load_3d_2sm(stage_a(st, j), &map_a, kj, m0, ab, full_leader);
-                                if (DUAL) tma_load_3d_2sm(stage_an(st, j), &map_an, kj, m0, ab, full_leader);
-                                if (kW4) tma_load_3d(stage_bp(st, j), &map_w, (kj - wk_off) >> 1, n0, wb, bp);
-                                else tma_load_3d_2sm(stage_b(st, j), &map_w, kj - wk_off, n0, wb, full_leader);
+            // one elected lane runs the whole loop: waits, issue and commits are single-thread work, and a warp that walks the
+            // loop together pays a divergence / reconvergence round trip at every lane-0 block (~150-200 cycles per stage)
+            if (lane == 0) {
+                for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+                    const int b = static_cast<int>(tile / tiles_per_batch);
+                    const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+                    const int m0 = (rem / p.tiles_n) * BM2 + static_cast<int>(rank) * BM;
+                    const int n0 = (rem % p.tiles_n) * p.bn + static_cast<int>(rank) * hb;
+                    const int ab = p.a_batched ? b : 0;
+                    for (int s = 0; ok && s < p.num_segs; ++s) {
+                        const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                        const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
+                        const int wk_off = p.w_seg_as_batch ? k_beg : 0;
+                        for (int k = k_beg; k < k_end; k += BKS) {
+                            if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
+                            {
+                                SQ_STAMP(0, 2 * trace_it);
+                                const int left = k_end - k;
+                                const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;   // sub-tiles that hold data
+                                const uint32_t full_leader = map_to_rank(smem_u32(&bar_full[st]), 0);
+                                if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[st]), tx_sub * nsub);
+                                const uint32_t bp = smem_u32(&bar_bp[st]);
+                                if (kW4) mbar_arrive_expect_tx(bp, static_cast<uint32_t>(hb) * (BK / 2) * nsub);
+    #pragma unroll
+                                for (int j = 0; j < KSUB; ++j) {
+                                    if (j >= nsub) break;
+                                    const int kj = k + j * BK;
+                                    tma_load_3d_2sm(stage_a(st, j), &map_a, kj, m0, ab, full_leader);
+                                    if (DUAL) tma_load_3d_2sm(stage_an(st, j), &map_an, kj, m0, ab, full_leader);
+                                    if (kW4) tma_load_3d(stage_bp(st, j), &map_w, (kj - wk_off) >> 1, n0, wb, bp);
+                                    else tma_load_3d_2sm(stage_b(st, j), &map_w, kj - wk_off, n0, wb, full_leader);
+                                }
                             }
+                            SQ_STAMP(0, 2 * trace_it + 1);
+                            ++trace_it;
+                            if (++st == kStages) { st = 0; ph ^= 1u; }
                         }
-                        if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
-                        ++trace_it;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
                 }
             }
+            __syncwarp();
         } else if (warp == 1 && rank == 0) {
             // ===== MMA issuer (leader CTA only) =====
             const uint32_t idesc = (make_idesc<KIND>() & ~(0x1Fu << 24)) | (static_cast<uint32_t>(BM2 >> 4) << 24) |
@@ -260,105 +264,108 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t cur_buf = 0;
             int trace_mma = 0; (void)trace_mma;
             bool ok = true;
-            for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    int u_end = k_beg;
-                    uint32_t accumulate = p.all_magic ? 1u : 0u;
-                    uint32_t d_pos = 0, d_neg = 0;
-                    for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
-                        if (kW4) {
-                            if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
-                        }
-                        tc_fence_after();
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
-                        // sub-tile j of an operand starts (tile bytes >> 4) descriptor units after sub-tile j-1
-                        const uint32_t a_lo = smem_desc_lo(stage_a(st, 0));
-                        const uint32_t an_lo = smem_desc_lo(stage_an(st, 0));
-                        const uint32_t b_lo = smem_desc_lo(stage_b(st, 0));
-                        const int kmax = (k_end - kb) < BKS ? (k_end - kb) : BKS;
-                        if (kb == u_end) {
-                            // the stage opens a new unit: hand the finished TMEM buffer to both CTAs' epilogues and take the
-                            // other one, once, before any MMA of the stage
-                            if (kb != k_beg && lane == 0) {
-                                umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
-                                umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+            // one elected lane runs the whole loop: waits, issue and commits are single-thread work, and a warp that walks the
+            // loop together pays a divergence / reconvergence round trip at every lane-0 block (~150-200 cycles per stage)
+            if (lane == 0) {
+                for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
+                    for (int s = 0; ok && s < p.num_segs; ++s) {
+                        const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                        int u_end = k_beg;
+                        uint32_t accumulate = p.all_magic ? 1u : 0u;
+                        uint32_t d_pos = 0, d_neg = 0;
+                        for (int kb = k_beg; ok && kb < k_end; kb += BKS) {
+                            if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
+                            if (kW4) {
+                                if (!mbar_wait_cluster(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
                             }
-                            const uint32_t buf = one_buf ? 0u : (au & 1u);
-                            const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
                             tc_fence_after();
-                            cur_buf = buf;
-                            d_pos = tmem_base + buf * BN;
-                            d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                            accumulate = p.all_magic ? 1u : 0u;
-                            u_end = unit_end(p, s, kb);
-                            ++au;
-                        }
-                        if (kb + kmax <= u_end) {
-                            if (lane == 0) {
-#pragma unroll
-                                for (int i = 0; i < BKS / UMMA_K; ++i) {
-                                    if (i * UMMA_K < kmax) {
-                                        constexpr int kPerSub = BK / UMMA_K;
-                                        const uint32_t ao = (i / kPerSub) * (kABytes >> 4) + 2 * (i % kPerSub);
-                                        const uint32_t bo = (i / kPerSub) * (C::kBHalfBytes >> 4) + 2 * (i % kPerSub);
-                                        const uint64_t db = smem_desc(b_lo + bo);
-                                        const uint32_t accf = i == 0 ? accumulate : 1u;
-                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + ao), db, idesc, accf);
-                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + ao), db, idesc, accf);
-                                    }
+                            SQ_STAMP(1, 3 * trace_mma);
+                            // sub-tile j of an operand starts (tile bytes >> 4) descriptor units after sub-tile j-1
+                            const uint32_t a_lo = smem_desc_lo(stage_a(st, 0));
+                            const uint32_t an_lo = smem_desc_lo(stage_an(st, 0));
+                            const uint32_t b_lo = smem_desc_lo(stage_b(st, 0));
+                            const int kmax = (k_end - kb) < BKS ? (k_end - kb) : BKS;
+                            if (kb == u_end) {
+                                // the stage opens a new unit: hand the finished TMEM buffer to both CTAs' epilogues and take the
+                                // other one, once, before any MMA of the stage
+                                if (kb != k_beg) {
+                                    umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                                    umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
                                 }
+                                const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                                if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                tc_fence_after();
+                                cur_buf = buf;
+                                d_pos = tmem_base + buf * BN;
+                                d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                                accumulate = p.all_magic ? 1u : 0u;
+                                u_end = unit_end(p, s, kb);
+                                ++au;
                             }
-                            accumulate = 1;
-                        } else {
-                            // a unit ends inside this stage
-                            for (int kk = 0; kk < kmax; kk += UMMA_K) {
-                                const int k = kb + kk;
-                                if (k == u_end) {
-                                    if (lane == 0) {
-                                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
-                                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+                            if (kb + kmax <= u_end) {
+                                {
+    #pragma unroll
+                                    for (int i = 0; i < BKS / UMMA_K; ++i) {
+                                        if (i * UMMA_K < kmax) {
+                                            constexpr int kPerSub = BK / UMMA_K;
+                                            const uint32_t ao = (i / kPerSub) * (kABytes >> 4) + 2 * (i % kPerSub);
+                                            const uint32_t bo = (i / kPerSub) * (C::kBHalfBytes >> 4) + 2 * (i % kPerSub);
+                                            const uint64_t db = smem_desc(b_lo + bo);
+                                            const uint32_t accf = i == 0 ? accumulate : 1u;
+                                            umma_2sm<KIND>(d_pos, smem_desc(a_lo + ao), db, idesc, accf);
+                                            if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + ao), db, idesc, accf);
+                                        }
                                     }
-                                    const uint32_t buf = one_buf ? 0u : (au & 1u);
-                                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                    if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
-                                    tc_fence_after();
-                                    cur_buf = buf;
-                                    d_pos = tmem_base + buf * BN;
-                                    d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                                    accumulate = p.all_magic ? 1u : 0u;
-                                    u_end = unit_end(p, s, k);
-                                    ++au;
-                                }
-                                if (lane == 0) {
-                                    const uint32_t sub = static_cast<uint32_t>(kk) / BK, within = (static_cast<uint32_t>(kk) % BK) >> 4;
-                                    const uint64_t db = smem_desc(b_lo + sub * (C::kBHalfBytes >> 4) + within);
-                                    umma_2sm<KIND>(d_pos, smem_desc(a_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
-                                    if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
                                 }
                                 accumulate = 1;
+                            } else {
+                                // a unit ends inside this stage
+                                for (int kk = 0; kk < kmax; kk += UMMA_K) {
+                                    const int k = kb + kk;
+                                    if (k == u_end) {
+                                        {
+                                            umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                                            umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
+                                        }
+                                        const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                        const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                                        if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                        tc_fence_after();
+                                        cur_buf = buf;
+                                        d_pos = tmem_base + buf * BN;
+                                        d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                                        accumulate = p.all_magic ? 1u : 0u;
+                                        u_end = unit_end(p, s, k);
+                                        ++au;
+                                    }
+                                    {
+                                        const uint32_t sub = static_cast<uint32_t>(kk) / BK, within = (static_cast<uint32_t>(kk) % BK) >> 4;
+                                        const uint64_t db = smem_desc(b_lo + sub * (C::kBHalfBytes >> 4) + within);
+                                        umma_2sm<KIND>(d_pos, smem_desc(a_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
+                                        if (DUAL) umma_2sm<KIND>(d_neg, smem_desc(an_lo + sub * (kABytes >> 4) + within), db, idesc, accumulate);
+                                    }
+                                    accumulate = 1;
+                                }
+                                if (!ok) break;
                             }
-                            if (!ok) break;
+                            SQ_STAMP(1, 3 * trace_mma + 1);
+                            {   // stage free in both CTAs once these MMAs have read it
+                                umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 0));
+                                umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 1));
+                            }
+                            SQ_STAMP(1, 3 * trace_mma + 2);
+                            ++trace_mma;
+                            if (++st == kStages) { st = 0; ph ^= 1u; }
                         }
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 1);
-                        if (lane == 0) {   // stage free in both CTAs once these MMAs have read it
-                            umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 0));
-                            umma_commit_2sm(map_to_rank(smem_u32(&bar_empty[st]), 1));
+                        if (ok) {
+                            umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
+                            umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
                         }
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 2);
-                        ++trace_mma;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
-                    if (ok && lane == 0) {
-                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 0));
-                        umma_commit_2sm(map_to_rank(smem_u32(&bar_tmem_full[cur_buf]), 1));
-                    }
-                    __syncwarp();
                 }
             }
+            __syncwarp();
         } else if (warp >= 2) {
             // ===== warps 2-3 (both CTAs): per-unit scale tables for this CTA's epilogue =====
             table_builder<KIND, DUAL, true>(p, tab, smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, first_tile,

@@ -512,7 +512,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (warp < 4) {
         // ------------------------------------------------------------------ producer / MMA warps
-        // Each role's whole warp walks the (warp-uniform) loops and polls the barriers; lane 0 issues.
+        // The producer and the MMA issuer are ONE thread each (lane 0 of their warps); the other lanes wait at the end.
         reg_dec<kW4 ? 40 : 56>();
         if (warp == 0) {
             // ===== TMA producer =====
@@ -520,34 +520,38 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             int st = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                const int b = static_cast<int>(tile / tiles_per_batch);
-                const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
-                const int m0 = (rem / p.tiles_n) * BM;
-                const int n0 = (rem % p.tiles_n) * p.bn;
-                const int ab = p.a_batched ? b : 0;
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
-                    const int wk_off = p.w_seg_as_batch ? k_beg : 0;
-                    for (int k = k_beg; k < k_end; k += BK) {
-                        if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
-                        if (lane == 0) {
-                            SQ_STAMP(0, 2 * trace_it);
-                            const uint32_t full = smem_u32(&bar_full[st]);
-                            mbar_arrive_expect_tx(full, kABytes * (DUAL ? 2 : 1) + static_cast<uint32_t>(p.bn) * (kW4 ? BK / 2 : BK));
-                            tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
-                            if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
-                            if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
-                            else tma_load_3d(stage_b(st), &map_w, k - wk_off, n0, wb, full);
+            // one elected lane runs the whole loop: waits, issue and commits are single-thread work, and a warp that walks the
+            // loop together pays a divergence / reconvergence round trip at every lane-0 block (~150-200 cycles per stage)
+            if (lane == 0) {
+                for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+                    const int b = static_cast<int>(tile / tiles_per_batch);
+                    const int rem = static_cast<int>(tile - static_cast<long long>(b) * tiles_per_batch);
+                    const int m0 = (rem / p.tiles_n) * BM;
+                    const int n0 = (rem % p.tiles_n) * p.bn;
+                    const int ab = p.a_batched ? b : 0;
+                    for (int s = 0; ok && s < p.num_segs; ++s) {
+                        const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                        const int wb = p.w_seg_as_batch ? s : (p.w_batched ? b : 0);
+                        const int wk_off = p.w_seg_as_batch ? k_beg : 0;
+                        for (int k = k_beg; k < k_end; k += BK) {
+                            if (!mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1u, abort_flag, kWaitEmpty, p.wait_cycles)) { ok = false; break; }
+                            {
+                                SQ_STAMP(0, 2 * trace_it);
+                                const uint32_t full = smem_u32(&bar_full[st]);
+                                mbar_arrive_expect_tx(full, kABytes * (DUAL ? 2 : 1) + static_cast<uint32_t>(p.bn) * (kW4 ? BK / 2 : BK));
+                                tma_load_3d(stage_a(st), &map_a, k, m0, ab, full);
+                                if (DUAL) tma_load_3d(stage_an(st), &map_an, k, m0, ab, full);
+                                if (kW4) tma_load_3d(stage_bp(st), &map_w, (k - wk_off) >> 1, n0, wb, full);
+                                else tma_load_3d(stage_b(st), &map_w, k - wk_off, n0, wb, full);
+                            }
+                            SQ_STAMP(0, 2 * trace_it + 1);
+                            ++trace_it;
+                            if (++st == kStages) { st = 0; ph ^= 1u; }
                         }
-                        if (lane == 0) SQ_STAMP(0, 2 * trace_it + 1);
-                        ++trace_it;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
                 }
             }
+            __syncwarp();
         } else if (warp == 1) {
             // ===== MMA issuer =====
             const uint32_t idesc = make_idesc<KIND>() | (static_cast<uint32_t>(p.bn >> 3) << 17);
@@ -558,94 +562,97 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t cur_buf = 0;  // buffer of the unit being accumulated
             int trace_mma = 0; (void)trace_mma;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                for (int s = 0; ok && s < p.num_segs; ++s) {
-                    const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    int u_end = k_beg;  // forces "new unit" at the first step of the segment
-                    uint32_t accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
-                    uint32_t d_pos = 0, d_neg = 0;
-                    for (int kb = k_beg; ok && kb < k_end; kb += BK) {
-                        SQ_FINE(0);
-                        if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
-                        if (kW4) {
-                            if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
-                        }
-                        SQ_FINE(1);
-                        tc_fence_after();
-                        SQ_FINE(2);
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma);
-                        const uint32_t a_lo = smem_desc_lo(stage_a(st));
-                        const uint32_t an_lo = smem_desc_lo(stage_an(st));
-                        const uint32_t b_lo = smem_desc_lo(stage_b(st));
-                        const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
-                        if (kb == u_end) {
-                            // the stage opens a new unit (the common place for a boundary): hand the finished TMEM
-                            // buffer to the epilogue and take the other one, once, before any MMA of the stage
-                            if (kb != k_beg && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
-                            const uint32_t buf = one_buf ? 0u : (au & 1u);
-                            const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                            if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+            // one elected lane runs the whole loop: waits, issue and commits are single-thread work, and a warp that walks the
+            // loop together pays a divergence / reconvergence round trip at every lane-0 block (~150-200 cycles per stage)
+            if (lane == 0) {
+                for (long long tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+                    for (int s = 0; ok && s < p.num_segs; ++s) {
+                        const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
+                        int u_end = k_beg;  // forces "new unit" at the first step of the segment
+                        uint32_t accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
+                        uint32_t d_pos = 0, d_neg = 0;
+                        for (int kb = k_beg; ok && kb < k_end; kb += BK) {
+                            SQ_FINE(0);
+                            if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
+                            if (kW4) {
+                                if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
+                            }
+                            SQ_FINE(1);
                             tc_fence_after();
-                            cur_buf = buf;
-                            d_pos = tmem_base + buf * BN;
-                            d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                            accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
-                            u_end = unit_end(p, s, kb);
-                            ++au;
-                        }
-                        if (kb + kmax <= u_end) {
-                            // the whole stage lies inside the current unit: no checks between the MMAs
-                            if (lane == 0) {
-#pragma unroll
-                                for (int i = 0; i < BK / UMMA_K; ++i) {
-                                    if (i * UMMA_K < kmax) {
-                                        const uint64_t db = smem_desc(b_lo + 2 * i);
-                                        const uint32_t accf = i == 0 ? accumulate : 1u;
-                                        umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, accf);
-                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, accf);
-                                        SQ_FINE(3 + i);
+                            SQ_FINE(2);
+                            SQ_STAMP(1, 3 * trace_mma);
+                            const uint32_t a_lo = smem_desc_lo(stage_a(st));
+                            const uint32_t an_lo = smem_desc_lo(stage_an(st));
+                            const uint32_t b_lo = smem_desc_lo(stage_b(st));
+                            const int kmax = (k_end - kb) < BK ? (k_end - kb) : BK;
+                            if (kb == u_end) {
+                                // the stage opens a new unit (the common place for a boundary): hand the finished TMEM
+                                // buffer to the epilogue and take the other one, once, before any MMA of the stage
+                                if (kb != k_beg) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
+                                const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                tc_fence_after();
+                                cur_buf = buf;
+                                d_pos = tmem_base + buf * BN;
+                                d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                                accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
+                                u_end = unit_end(p, s, kb);
+                                ++au;
+                            }
+                            if (kb + kmax <= u_end) {
+                                // the whole stage lies inside the current unit: no checks between the MMAs
+                                {
+    #pragma unroll
+                                    for (int i = 0; i < BK / UMMA_K; ++i) {
+                                        if (i * UMMA_K < kmax) {
+                                            const uint64_t db = smem_desc(b_lo + 2 * i);
+                                            const uint32_t accf = i == 0 ? accumulate : 1u;
+                                            umma<KIND>(d_pos, smem_desc(a_lo + 2 * i), db, idesc, accf);
+                                            if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + 2 * i), db, idesc, accf);
+                                            SQ_FINE(3 + i);
+                                        }
                                     }
                                 }
-                            }
-                            accumulate = 1;
-                        } else {
-                            // a unit ends inside this stage (segment bounds or groups that are not multiples of 128)
-                            for (int kk = 0; kk < kmax; kk += UMMA_K) {
-                                const int k = kb + kk;
-                                if (k == u_end) {
-                                    if (lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
-                                    const uint32_t buf = one_buf ? 0u : (au & 1u);
-                                    const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                    if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
-                                    tc_fence_after();
-                                    cur_buf = buf;
-                                    d_pos = tmem_base + buf * BN;
-                                    d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
-                                    accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
-                                    u_end = unit_end(p, s, k);
-                                    ++au;
-                                }
-                                if (lane == 0) {
-                                    const uint64_t db = smem_desc(b_lo + (kk >> 4));
-                                    umma<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
-                                    if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
-                                }
                                 accumulate = 1;
+                            } else {
+                                // a unit ends inside this stage (segment bounds or groups that are not multiples of 128)
+                                for (int kk = 0; kk < kmax; kk += UMMA_K) {
+                                    const int k = kb + kk;
+                                    if (k == u_end) {
+                                        umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
+                                        const uint32_t buf = one_buf ? 0u : (au & 1u);
+                                        const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
+                                        if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                        tc_fence_after();
+                                        cur_buf = buf;
+                                        d_pos = tmem_base + buf * BN;
+                                        d_neg = tmem_base + (p.dual_db ? buf * BN + 128 : BN);
+                                        accumulate = p.all_magic ? 1u : 0u;   // all_magic: the buffer holds the magic pattern, never garbage
+                                        u_end = unit_end(p, s, k);
+                                        ++au;
+                                    }
+                                    {
+                                        const uint64_t db = smem_desc(b_lo + (kk >> 4));
+                                        umma<KIND>(d_pos, smem_desc(a_lo + (kk >> 4)), db, idesc, accumulate);
+                                        if (DUAL) umma<KIND>(d_neg, smem_desc(an_lo + (kk >> 4)), db, idesc, accumulate);
+                                    }
+                                    accumulate = 1;
+                                }
+                                if (!ok) break;
                             }
-                            if (!ok) break;
+                            SQ_STAMP(1, 3 * trace_mma + 1);
+                            umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
+                            SQ_STAMP(1, 3 * trace_mma + 2);
+                            SQ_FINE(7);
+                            ++trace_mma;
+                            if (++st == kStages) { st = 0; ph ^= 1u; }
                         }
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 1);
-                        if (lane == 0) umma_commit(smem_u32(&bar_empty[st]));  // stage free once these MMAs have read it
-                        if (lane == 0) SQ_STAMP(1, 3 * trace_mma + 2);
-                        SQ_FINE(7);
-                        ++trace_mma;
-                        __syncwarp();
-                        if (++st == kStages) { st = 0; ph ^= 1u; }
+                        if (ok) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));  // last unit of the segment
                     }
-                    if (ok && lane == 0) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));  // last unit of the segment
-                    __syncwarp();
                 }
             }
+            __syncwarp();
         } else {
             // ===== warps 2-3: per-unit scale tables for the epilogue =====
             table_builder<KIND, DUAL, false>(p, tab, smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, blockIdx.x,
