@@ -300,6 +300,16 @@ int sq_gemm(const sq_gemm_args* args, sq_stream_t stream);
 int sq_push_columns(const void* src_dev, int64_t rows, int64_t width_bytes, int64_t src_row_stride_bytes,
                     int32_t num_peers, void* const* peer_dst_dev, int64_t dst_row_stride_bytes, sq_stream_t stream);
 
+/* Stream-ordered barrier between the `world` ranks of a sharded layer (one rank per GPU; at most SQ_MAX_PEERS + 1),
+ * the step after sq_push_columns or a sq_gemm with peer outputs.  flags_dev is a HOST array of `world` device pointers:
+ * entry j is rank j's array of `world` 32-bit words (peer memory mapped into this process; entry `rank` is this rank's own
+ * array), all zero before the first call.  `epoch` is the call's number, 1, 2, ... , the same on every rank.  The kernel
+ * publishes everything this GPU wrote before it (system-scope fence), stores epoch into word [rank] of every peer's array
+ * and waits until its own words have reached epoch.  The wait is bounded like every wait of this library: when it runs
+ * out the kernel returns and sq_check_device() reports SQ_ERR_DEVICE_TIMEOUT with wait id 10 and the peer's rank in the
+ * place of the block.  No counterpart in the reference. */
+int sq_peer_barrier(int32_t rank, int32_t world, void* const* flags_dev, uint32_t epoch, sq_stream_t stream);
+
 /* Number of accumulation units sq_gemm will use for these segment bounds / group size
    (the `units` of the acc_dump layout).  Negative = error. */
 int sq_gemm_num_units(int32_t num_segs, const int32_t* seg_bounds, int32_t group_size);

@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = (
     "sq_version", "sq_last_error", "sq_status_string", "sq_device_status",
     "sq_quantize_act", "sq_quantize_act_dynamic", "sq_norm_quantize_act", "sq_residual_norm_quantize_act", "sq_gated_residual", "sq_quantize_weight", "sq_unpack_int4",
     "sq_gemm", "sq_gemm_num_units", "sq_seg_linear", "sq_seg_linear_static",
-    "sq_check_device", "sq_set_wait_limit_cycles", "sq_wait_probe", "sq_set_gemm_schedule", "sq_push_columns",
+    "sq_check_device", "sq_set_wait_limit_cycles", "sq_wait_probe", "sq_set_gemm_schedule", "sq_push_columns", "sq_peer_barrier",
 )
 
 
@@ -152,6 +152,8 @@ def load():
     lib.sq_wait_probe.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
     lib.sq_set_gemm_schedule.restype = ctypes.c_int
     lib.sq_set_gemm_schedule.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.sq_peer_barrier.restype = ctypes.c_int
+    lib.sq_peer_barrier.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint32, ctypes.c_void_p]
     lib.sq_push_columns.restype = ctypes.c_int
     lib.sq_push_columns.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
                                     ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_void_p]

@@ -36,6 +36,7 @@ int set_wait_limit(long long cycles);
 int wait_probe(long long limit_cycles, int* out_dev, cudaStream_t st);
 int push_columns(const void* src, long long rows, long long width_bytes, long long src_row_stride, int n_peers,
                  void* const* peer_dst, long long dst_row_stride, cudaStream_t st);
+int peer_barrier(int rank, int world, void* const* flags, unsigned epoch, cudaStream_t st);
 
 }  // namespace sq
 
@@ -144,6 +145,11 @@ int sq_push_columns(const void* src_dev, int64_t rows, int64_t width_bytes, int6
     sq::clear_error();
     return sq::push_columns(src_dev, rows, width_bytes, src_row_stride_bytes, num_peers, peer_dst_dev, dst_row_stride_bytes,
                             static_cast<cudaStream_t>(stream));
+}
+
+int sq_peer_barrier(int32_t rank, int32_t world, void* const* flags_dev, uint32_t epoch, sq_stream_t stream) {
+    sq::clear_error();
+    return sq::peer_barrier(rank, world, flags_dev, epoch, static_cast<cudaStream_t>(stream));
 }
 
 int sq_gemm_num_units(int32_t num_segs, const int32_t* seg_bounds, int32_t group_size) {

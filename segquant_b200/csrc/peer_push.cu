@@ -48,6 +48,76 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const __grid_constant__ 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Stream-ordered barrier between the ranks of a sharded layer, one rank per GPU, over flag words in peer-mapped memory.
+// Every rank owns an array of `world` 32-bit words (zero at start).  Call number `epoch` (1, 2, ... : the same on every
+// rank, the calls are collective) stores `epoch` into word [rank] of every peer's array - after a system-scope fence, so
+// everything this GPU wrote before the launch (its GEMM's or push kernel's stores into the peers' matrices) is visible
+// to whoever sees the flag - and waits until its own words [j] have reached `epoch` for every peer j.  Epochs only
+// grow, so the words are never reset and a late reader cannot miss one.  One small kernel instead of an all-reduce.
+// The wait is bounded (the limit of every other wait of this library): when it runs out the kernel records
+// (peer << 8 | kWaitPeerBarrier) in this file's status word, which sq_device_status() / sq_check_device() report, and
+// returns.  Ranks must run on different GPUs: kernels that wait for one another cannot share one.
+constexpr int kWaitPeerBarrier = 10;
+static __device__ unsigned long long g_wait_status = 0ull;
+
+struct BarrierParams {
+    uint32_t* flags[SQ_MAX_PEERS + 1];   // every rank's array, own included
+    int rank, world;
+    uint32_t epoch;
+    long long limit;
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant__ BarrierParams p) {
+    const int j = threadIdx.x;
+    if (j >= p.world || j == p.rank) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[j] + p.rank), "r"(p.epoch) : "memory");
+    const uint32_t* mine = p.flags[p.rank] + j;
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int32_t>(v - p.epoch) >= 0) break;
+        if (clock64() - t0 > p.limit) {
+            atomicCAS(&g_wait_status, 0ull, (static_cast<unsigned long long>(j) << 8) | static_cast<unsigned>(kWaitPeerBarrier));
+            break;
+        }
+        __nanosleep(64);
+    }
+}
+
+long long wait_limit_cycles();   // seg_gemm.cu
+
+int peer_barrier(int rank, int world, void* const* flags, unsigned epoch, cudaStream_t st) {
+    SQ_REQUIRE(world >= 1 && world <= SQ_MAX_PEERS + 1 && rank >= 0 && rank < world, SQ_ERR_INVALID_ARG,
+               "sq_peer_barrier: rank %d / world %d out of range (at most %d ranks)", rank, world, SQ_MAX_PEERS + 1);
+    if (world == 1) return SQ_OK;
+    SQ_REQUIRE(flags != nullptr, SQ_ERR_INVALID_ARG, "sq_peer_barrier: flags is NULL");
+    BarrierParams p;
+    for (int j = 0; j <= SQ_MAX_PEERS; ++j) {
+        p.flags[j] = j < world ? static_cast<uint32_t*>(flags[j]) : nullptr;
+        if (j < world)
+            SQ_REQUIRE(flags[j] != nullptr && reinterpret_cast<uintptr_t>(flags[j]) % 4 == 0, SQ_ERR_INVALID_ARG,
+                       "sq_peer_barrier: flags[%d] is NULL or not 4-byte aligned", j);
+    }
+    p.rank = rank;
+    p.world = world;
+    p.epoch = epoch;
+    p.limit = wait_limit_cycles();
+    peer_barrier_kernel<<<1, 32, 0, st>>>(p);
+    SQ_CUDA_OK(cudaGetLastError());
+    return SQ_OK;
+}
+
+// reads and clears this file's status word (see read_device_status in seg_gemm.cu)
+long long push_read_status() {
+    unsigned long long v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_wait_status, sizeof(v)) != cudaSuccess) return SQ_ERR_CUDA;
+    if (v != 0 && cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(zero)) != cudaSuccess) return SQ_ERR_CUDA;
+    return static_cast<long long>(v);
+}
+
 int push_columns(const void* src, long long rows, long long width_bytes, long long src_row_stride, int n_peers,
                  void* const* peer_dst, long long dst_row_stride, cudaStream_t st) {
     SQ_REQUIRE(rows >= 0 && width_bytes >= 0, SQ_ERR_INVALID_ARG, "sq_push_columns: negative size");

@@ -18,6 +18,8 @@ static int g_last_tu = 0;   // (kind * 2 + dual) of the last launch; the trace r
 #define SQ_FOR_EACH_TU(X) X(SQ_GEMM_W8A8_I8, false) X(SQ_GEMM_W8A8_I8, true) X(SQ_GEMM_W8A8_F8, false) X(SQ_GEMM_W8A8_F8, true) \
                           X(SQ_GEMM_W4A8, false) X(SQ_GEMM_W4A8, true)
 
+long long push_read_status();   // peer_push.cu
+
 long long read_device_status() {
     if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_CUDA;
     long long first = 0;
@@ -29,6 +31,11 @@ long long read_device_status() {
     }
     SQ_FOR_EACH_TU(SQ_X)
 #undef SQ_X
+    {
+        const long long v = push_read_status();   // the peer barrier's word (peer_push.cu)
+        if (v < 0) return v;
+        if (first == 0) first = v;
+    }
     return first;
 }
 
@@ -163,6 +170,7 @@ int set_wait_limit(long long cycles) {
     return SQ_OK;
 }
 int forced_ksub() { return overrides().ksub; }
+long long wait_limit_cycles() { return overrides().wait_cycles; }
 bool gemv_disabled() { return overrides().no_gemv != 0; }
 
 // Schedule choice against wave quantisation.  The persistent grid runs ceil(tiles / slots) rounds
@@ -173,7 +181,7 @@ struct Schedule {
     int bn;
     bool two_cta;
 };
-static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind) {
+static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind, bool no192 = false) {
     const int force_bn = overrides().bn, force_cta2 = overrides().cta2;
     const int widths[3] = {256, 192, 128};
     Schedule best{256, false};
@@ -188,6 +196,7 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;
         for (int w : widths) {
             if (force_bn && w != force_bn) continue;
+            if (no192 && w == 192) continue;
             const long long tiles = batch * ((M + rows - 1) / rows) * ((N + w - 1) / w);
             const long long rounds = (tiles + slots - 1) / slots;
             // SM cycles, fitted to in-kernel timelines: a K stage costs the issuing thread a fixed ~500 cycles
@@ -333,7 +342,15 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     p.wait_cycles = overrides().wait_cycles;
     // a handful of rows: stream the weights once on the CUDA cores instead of padding 128-row tensor-core tiles
     if (gemv_applies(a, dual)) return launch_gemv(p, a, dual, st);
-    const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind);
+    // Fused all-gather: stores to peers should be whole 128-byte lines ([16 rows x 128 bytes] boxes, see store_output).
+    // That needs TMA-storable outputs and a tile whose per-warp column count is a multiple of the box (not 192 wide);
+    // otherwise peers get the 16-column boxes of the plain store path.
+    const long long oesz = a->out_dtype == SQ_F32 ? 4 : 2;
+    const bool y_tma_ok = (reinterpret_cast<uintptr_t>(a->y_dev) & 15u) == 0 && (a->y_row_stride * oesz) % 16 == 0 &&
+                          a->y_row_stride >= a->N;
+    const bool want_wide = a->num_peer_outputs > 0 && y_tma_ok && overrides().bn != 192;
+    const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind, want_wide);
+    p.peer_wide = want_wide ? 1 : 0;
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
     p.bn = sched.bn;
@@ -373,19 +390,24 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
         p.y_tma = 0;
         if (aligned) {
             const uint64_t y_bstride = a->batch > 1 ? a->y_batch_stride * esz : static_cast<uint64_t>(a->y_row_stride) * esz * a->M;
-            rc = make_map(&my.y, a->y_dev, a->N * esz, a->M, a->batch, a->y_row_stride * esz, y_bstride, 16 * esz, 32, false, "y");
+            // box: [32 rows x 16 columns], or with wide peer stores [16 rows x 128 bytes] read from a swizzled staging area
+            const uint32_t box_bytes = p.peer_wide ? 128u : static_cast<uint32_t>(16 * esz);
+            const uint32_t box_rows = p.peer_wide ? 16u : 32u;
+            const bool box_swz = p.peer_wide != 0;
+            rc = make_map(&my.y, a->y_dev, a->N * esz, a->M, a->batch, a->y_row_stride * esz, y_bstride, box_bytes, box_rows, box_swz, "y");
             if (rc != SQ_OK) return rc;
             p.y_tma = 1;
             // peers: the map starts at their column offset, so the kernel uses the coordinates of y
             for (int j = 0; j < a->num_peer_outputs; ++j) {
                 const uint8_t* base = static_cast<const uint8_t*>(a->peer_y_dev[j]) + a->peer_col_offset * esz;
                 rc = make_map(&my.peer[j], base, a->N * esz, a->M, 1, a->peer_row_stride * esz,
-                              static_cast<uint64_t>(a->peer_row_stride) * esz * a->M, 16 * esz, 32, false, "peer_y");
+                              static_cast<uint64_t>(a->peer_row_stride) * esz * a->M, box_bytes, box_rows, box_swz, "peer_y");
                 if (rc != SQ_OK) return rc;
             }
             p.peer_tma = a->num_peer_outputs > 0 ? 1 : 0;
         }
     }
+    if (!p.y_tma) p.peer_wide = 0;
     // B tile rows staged per CTA: the whole tile, or half of it in a CTA pair
     const uint32_t w_box_rows = sched.two_cta ? p.bn / 2 : p.bn;
     if (w4) rc = make_map(&mw, a->wq_dev, w_row_bytes, a->N, w_nb, a->wq_row_stride, w_bstride, BK / 2, w_box_rows, false, "wq(int4)");

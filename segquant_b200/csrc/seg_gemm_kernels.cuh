@@ -353,6 +353,93 @@ __device__ __forceinline__ void store_peers(const GemmParams& p, const float (&o
     }
 }
 
+// 16 output columns of row `r` of a box with 128-byte rows laid out with the 128-byte swizzle (16-byte piece index XOR
+// row % 8: what a SWIZZLE_128B tensor map expects, and free of bank conflicts for lanes writing one row each).
+// `piece0` = index of the first 16-byte piece of these columns inside the row (0, 2, 4, 6 / 0, 4).
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk_swz(uint8_t* box, int r, int piece0, const float (&v)[16]) {
+    uint8_t* row = box + r * 128;
+    const int x = r & 7;
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<float4*>(row + (((piece0 + i) ^ x) << 4)) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                OutT lo = from_float<OutT>(v[8 * i + 2 * j]);
+                OutT hi = from_float<OutT>(v[8 * i + 2 * j + 1]);
+                w[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+                       (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+            }
+            *reinterpret_cast<uint4*>(row + (((piece0 + i) ^ x) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// Fused all-gather with wide boxes.  Per 128 bytes of output row (CPB 16-column chunks: 64 columns of a 16-bit type, 32
+// of fp32) the warp's 2 KB staging area is filled twice - rows 0-15 by lanes 0-15, then rows 16-31 by lanes 16-31 - and
+// each time one TMA store per destination (this GPU's matrix and every peer's) moves [16 rows x 128 bytes]: whole
+// 128-byte lines on NVLink instead of the 32-byte row pieces of a 16-column box.  The host only asks for this with tile
+// widths whose per-warp column count is a multiple of the box (bn 128 / 256), so a box never reaches into the columns
+// of the neighbouring warp; columns past N and rows past M are clipped by the tensor map.
+template <int CPB>
+__device__ __forceinline__ void store_output_wide(const GemmParams& p, const OutMaps* map_y, const float (&acc)[128], int nch,
+                                                  int m_warp, long long ncol0, uint8_t* stage, int lane, const float* bias_s) {
+    if (m_warp >= p.M) return;                       // nothing of this warp's 32 rows exists (warp-uniform)
+    const int esz = CPB == 4 ? 2 : 4;
+    const uint32_t stage_u32 = smem_u32(stage);
+    const int row16 = lane & 15;
+#pragma unroll
+    for (int g = 0; g < 8 / CPB; ++g) {              // boxes along the warp's columns
+        const int ch0 = g * CPB;
+        const long long nc0 = ncol0 + ch0 * 16;
+        if (ch0 >= nch || nc0 >= p.N) break;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if (m_warp + 16 * half >= p.M) break;    // warp-uniform
+            if (lane == 0) bulk_wait_read<0>();      // the staging area has been read by the previous box's stores
+            __syncwarp();
+            if ((lane >> 4) == half) {
+#pragma unroll
+                for (int cb = 0; cb < CPB; ++cb) {
+                    const int ch = ch0 + cb;
+                    if (ch < nch) {                  // chunks past N only fill bytes the tensor map clips
+                        float o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) o[j] = acc[ch * 16 + j];
+                        if (p.bias != nullptr) {
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; ++j4) {
+                                const float4 bv = reinterpret_cast<const float4*>(bias_s + ch * 16)[j4];   // 0 beyond column N
+                                o[4 * j4 + 0] += bv.x;
+                                o[4 * j4 + 1] += bv.y;
+                                o[4 * j4 + 2] += bv.z;
+                                o[4 * j4 + 3] += bv.w;
+                            }
+                        }
+                        if (CPB == 2) store_row_chunk_swz<float>(stage, row16, cb * 4, o);
+                        else if (p.out_dtype == SQ_F16) store_row_chunk_swz<__half>(stage, row16, cb * 2, o);
+                        else store_row_chunk_swz<__nv_bfloat16>(stage, row16, cb * 2, o);
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                const int c0 = static_cast<int>(nc0) * esz;   // the maps are byte-typed
+                const int r0 = m_warp + 16 * half;
+                tma_store_3d(&map_y->y, stage_u32, c0, r0, 0);
+                for (int j = 0; j < p.n_peers; ++j) tma_store_3d(&map_y->peer[j], stage_u32, c0, r0, 0);
+                bulk_commit();
+            }
+        }
+    }
+}
+
 // Bias, cast and store of one thread's output row segment (up to 128 columns held in acc[]).
 // bias_s: this thread's columns of the tile's bias in shared memory, as fp32 (written by the table builder).
 // Aligned outputs go through shared memory and TMA stores (one [32 rows x 16 columns] box per warp and
@@ -365,6 +452,13 @@ __device__ __forceinline__ void store_output(const GemmParams& p, const OutMaps*
                                              long long b, long long m, int m_warp, bool row_ok, long long ncol0,
                                              uint8_t* stage, int lane, const float* bias_s) {
     const int esz = p.out_dtype == SQ_F32 ? 4 : 2;
+    if constexpr (PEERS) {
+        if (p.peer_wide) {
+            if (esz == 2) store_output_wide<4>(p, map_y, acc, nch, m_warp, ncol0, stage, lane, bias_s);
+            else store_output_wide<2>(p, map_y, acc, nch, m_warp, ncol0, stage, lane, bias_s);
+            return;
+        }
+    }
     if (p.y_tma) {
         if (m_warp >= p.M) return;                           // nothing of this warp's 32 rows exists (warp-uniform)
         const uint32_t stage_u32 = smem_u32(stage);

@@ -381,6 +381,20 @@ def push_columns(block, peer_ptrs, peer_row_stride_bytes):
     launch_count += 1
 
 
+def peer_barrier(rank, flag_ptrs, epoch, device):
+    """Stream-ordered barrier over flag words in peer-mapped memory (sq_peer_barrier): flag_ptrs[j] = device address of
+    rank j's array of len(flag_ptrs) uint32 words, epoch = number of this collective call (1, 2, ...)."""
+    global launch_count
+    world = len(flag_ptrs)
+    if world == 1:
+        return
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in flag_ptrs])
+    with torch.cuda.device(device):
+        L.check(L.load().sq_peer_barrier(int(rank), world, arr, int(epoch) & 0xFFFFFFFF,
+                                         ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)), "sq_peer_barrier")
+    launch_count += 1
+
+
 def check_device():
     """Synchronise and raise SegQuantError(SQ_ERR_DEVICE_TIMEOUT) if a kernel reported a bounded wait that ran out."""
     L.check(L.load().sq_check_device(), "sq_check_device")

@@ -13,10 +13,10 @@ forward_push()   every rank's [M, N] result lives in symmetric memory; the GEMM 
                  place, then ONE kernel (ops.push_columns) stores that block into the same columns of every peer's
                  matrix: final layout, whole 512-byte row segments on the wire, no gather buffer, no permute.
 forward_fused()  the exchange inside the GEMM epilogue: every finished tile goes to the rank's own matrix and to every
-                 peer's by TMA stores while the mainloop of the next tile runs.  Wins when the GEMM is long enough to
-                 hide the stores; its 32-byte row segments make it slower than forward_push() when the exchange, not
-                 the GEMM, sets the time.
-A one-word all-reduce on the compute stream orders the ranks after either of the last two.
+                 peer's by TMA stores ([32 rows x 128 bytes] boxes: whole 128-byte lines on NVLink) while the mainloop
+                 of the next tiles runs, so the transfer overlaps the math tile by tile.
+A barrier kernel on the compute stream (ops.peer_barrier: flag words in symmetric memory, a system-scope fence, a bounded
+wait) orders the ranks after either of the last two.
 
 Buffer rule of forward_push / forward_fused: results are views of TWO symmetric buffers used alternately.  The view
 returned by call n is overwritten by PEERS during their call n + 2, which they can only start after this rank has
@@ -71,7 +71,7 @@ class ColumnShardedSegLinear:
 
     def __init__(self, local_layer, rank, world, n_total, group=None):
         self.layer, self.rank, self.world, self.n_total, self.group = local_layer, rank, world, n_total, group
-        self._bufs, self._peer_ptrs, self._flag, self._calls = None, None, None, 0
+        self._bufs, self._peer_ptrs, self._flags, self._flag_ptrs, self._epoch, self._calls = None, None, None, None, 0, 0
 
     @classmethod
     def from_full(cls, x_calib, weight, bias, rank, world, kernel_type="Wint8Aint8", dual_scale=False, seg_mode="input",
@@ -121,7 +121,14 @@ class ColumnShardedSegLinear:
             handle = symm.rendezvous(buf, group)
             self._bufs.append(buf)
             self._peer_ptrs.append([int(p) for r, p in enumerate(handle.buffer_ptrs) if r != self.rank])
-        self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        # barrier words: one array of `world` uint32 per rank, zero before anybody's first barrier
+        flags = symm.empty((64,), dtype=torch.int32, device=dev)
+        flags.zero_()
+        torch.cuda.synchronize(dev)
+        handle = symm.rendezvous(flags, group)
+        self._flags, self._flag_ptrs = flags, [int(p) for p in handle.buffer_ptrs]
+        dist.barrier(group=group)                      # every rank's words are zero before the first epoch is stored
+        self._epoch = 0
         self._calls = 0
 
     enable_fused_gather = enable_symmetric      # earlier name
@@ -136,7 +143,11 @@ class ColumnShardedSegLinear:
         return self._bufs[i][:m], self._peer_ptrs[i]
 
     def _barrier(self):
-        dist.all_reduce(self._flag, group=self.group)   # stream-ordered: completes after every rank's stores were issued and landed
+        """Stream-ordered: completes on this rank once every rank has issued it, i.e. after every rank's stores into this
+        rank's matrix have landed.  Epochs count the collective calls, the same on every rank."""
+        from . import ops
+        self._epoch += 1
+        ops.peer_barrier(self.rank, self._flag_ptrs, self._epoch, self._device())
 
     def forward_push(self, x):
         """x [M, K] (same on every rank).  GEMM into this rank's columns of its own matrix, then one push of that block to
@@ -163,17 +174,12 @@ class ColumnShardedSegLinear:
         self._barrier()
         return full
 
-    # bytes one GPU sends to its peers above which pushing the finished block is faster than storing tile by tile from the
-    # epilogue (measured on 2 and 8 B200s)
-    FUSED_MAX_BYTES = 24 * 1024 * 1024
-
     def forward_auto(self, x):
-        """Fused exchange while the GEMM can hide it, block push for large outputs, NCCL all-gather without symmetric
-        memory.  x [M, K]."""
+        """The fused exchange wherever the symmetric buffers allow it (measured faster than GEMM + block push at 2 and 4
+        GPUs: the stores ride under the mainloop), the NCCL all-gather otherwise.  x [M, K]."""
         if self._bufs is None or x.dim() != 2 or x.shape[0] > self._bufs[0].shape[0]:
             return self.forward(x)
-        out_bytes = x.shape[0] * (self.n_total // self.world) * self._bufs[0].element_size() * (self.world - 1)
-        return self.forward_fused(x) if out_bytes <= self.FUSED_MAX_BYTES else self.forward_push(x)
+        return self.forward_fused(x)
 
     def forward_from_host_rows(self, x_rows_host, m_total, exchange="auto"):
         """End-to-end form for inputs that start in HOST memory: every rank copies only ITS row block of x
