@@ -442,6 +442,31 @@ def mmdit_entry(dev, steps=5, cpu=True):
     return entry
 
 
+def mmdit_dp_entry(dist, world, rank, dev, steps=3):
+    """config[3] at N > 1: the denoise step batch-data-parallel, 16 samples split over the ranks (replicas: no collective
+    inside the step, so a rank's time is the one-GPU time at its local batch).  Every rank runs; rank 0 gets the entry."""
+    from segquant_b200.mmdit import GraphedStep, SyntheticMMDiT, synthetic_inputs
+    batch = max(1, 16 // world)
+    model = SyntheticMMDiT(dev)
+    inputs = synthetic_inputs(batch, dev, seed=100 + rank)
+    model.calibrate(*inputs)
+    torch.cuda.synchronize()
+    step = GraphedStep(model, *inputs)
+    dist.barrier()
+    ms = timed(lambda: step(*inputs), steps, warmup=3)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    ts = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(ts, t)
+    per_rank = [float(v.item()) for v in ts]
+    lin_ops = model.linear_ops(batch) * world
+    del step, model
+    torch.cuda.empty_cache()
+    return {"workload": f"config[3]: synthetic MMDiT denoise step, batch-data-parallel: 16 samples over {world} GPUs ({batch} per GPU), "
+                        "one CUDA graph per step and rank, no collective inside the step",
+            "batch_per_gpu": batch, "ms": max(per_rank), "ms_per_rank": per_rank, "samples_per_s": batch * world / max(per_rank) * 1e3,
+            "linear_tops_useful": lin_ops / max(per_rank) / 1e9}
+
+
 # ---------------------------------------------------------------------------------------------
 # our arm: the headline layer
 # ---------------------------------------------------------------------------------------------
@@ -645,6 +670,11 @@ def run_ours(args):
         configs = config_entries(dev, peaks)
         configs["config3_mmdit_step"] = mmdit_entry(dev, cpu=args.configs == "all")
         status = status or ops.device_status()
+    if world > 1 and args.configs != "none" and not args.quick:
+        del x, xq, y_loc, cs
+        torch.cuda.empty_cache()
+        configs = {"config3_mmdit_step": mmdit_dp_entry(dist, world, rank, dev)}
+        status = status or ops.device_status()
     if rank == 0:
         achieved = 2.0 * HM * n_loc * HK / g_ms / 1e9
         line = {
@@ -804,19 +834,30 @@ def run_sweep(args):
         okind = {"int8": O.GEMM_I8, "fp8": O.GEMM_F8, "w4a8": O.GEMM_W4A8}
         oq = {"int8": O.Q_INT8, "fp8": O.Q_E4M3, "w4a8": O.Q_INT8}
     worst = 0.0
+    bar_ptrs, bar_words, epoch = None, None, [0]
+
+    def rank_barrier():      # stream-ordered: every rank's kernels before it are complete, and their stores visible, after it
+        epoch[0] += 1
+        ops.peer_barrier(rank, bar_ptrs, epoch[0], dev)
+
     for (N, K) in nks:
         if N % world:
             continue
         lo, hi = shard_range(N, world, rank)
         n_loc = hi - lo
-        full = peers = flag = None
-        if world > 1 and args.fused_gather:
+        full = peers = None
+        if world > 1 and not args.no_symmetric:
             # every rank's [M, N] result buffer, mapped into all processes: epilogue stores / block pushes go to all of them
             import torch.distributed._symmetric_memory as symm
             full = symm.empty((max(Ms), N), dtype=torch.bfloat16, device=dev)
             handle = symm.rendezvous(full, dist.group.WORLD)
             peers = [int(p_) for r_, p_ in enumerate(handle.buffer_ptrs) if r_ != rank]
-            flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            if bar_ptrs is None:        # barrier words (ops.peer_barrier), zero before anybody's first epoch
+                bar_words = symm.empty((64,), dtype=torch.int32, device=dev)
+                bar_words.zero_()
+                torch.cuda.synchronize()
+                bar_ptrs = [int(p_) for p_ in symm.rendezvous(bar_words, dist.group.WORLD).buffer_ptrs]
+                dist.barrier()
         w = (torch.randn(n_loc, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
         for name, ktype, wkind, group in modes:
             qmax = {L.SQ_Q_INT8: 127.0, L.SQ_Q_E4M3: 448.0, L.SQ_Q_INT4: 7.0}[wkind]
@@ -898,12 +939,12 @@ def run_sweep(args):
                         def fwd_fused():
                             ops.seg_linear(ktype, x.unsqueeze(0), wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides,
                                            out=mine.unsqueeze(0), peer_outputs=(peers, N, lo))
-                            dist.all_reduce(flag)      # stream-ordered: every rank's kernel is complete after it
+                            rank_barrier()
 
                         def fwd_push():
                             ops.seg_linear(ktype, x.unsqueeze(0), wq3, n_loc, bounds, sx, sw, group_size=group, sw_strides=strides, out=mine.unsqueeze(0))
                             ops.push_columns(mine, [p_ + lo * 2 for p_ in peers], N * 2)
-                            dist.all_reduce(flag)
+                            rank_barrier()
                         res = []
                         for fn in (fwd_fused, fwd_push):
                             full.zero_()
@@ -1037,8 +1078,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="mmdit: skip the CPU baseline (one fake-quant block on the host cores)")
     ap.add_argument("--sweep-m", default="256,1024,4096,16384")
     ap.add_argument("--sweep-iters", type=int, default=10)
-    ap.add_argument("--fused-gather", action="store_true",
-                    help="sweep at N > 1: also time the exchanges through symmetric memory (fused epilogue stores, block push)")
+    ap.add_argument("--fused-gather", action="store_true", help="sweep at N > 1: accepted for old command lines; the symmetric-memory "
+                                                               "exchanges are timed unless --no-symmetric is given")
+    ap.add_argument("--no-symmetric", action="store_true",
+                    help="sweep at N > 1: time only the NCCL all-gather, not the exchanges through symmetric memory (fused epilogue stores, block push)")
     ap.add_argument("--no-check", action="store_true", help="sweep: skip the per-point check against the CPU oracle")
     ap.add_argument("--sweep-nk", default="", help="sweep: comma list of NxK pairs (default: the seven shapes of config[4])")
     ap.add_argument("--sweep-modes", default="int8,fp8,w4a8")

@@ -174,12 +174,22 @@ class ColumnShardedSegLinear:
         self._barrier()
         return full
 
+    # planning figures for forward_auto: 8-bit tensor rate a shard's GEMM reaches and the rate one GPU pushes into NVLink
+    GEMM_OPS_PER_S = 2.8e15
+    LINK_BYTES_PER_S = 0.7e12
+
     def forward_auto(self, x):
-        """The fused exchange wherever the symmetric buffers allow it (measured faster than GEMM + block push at 2 and 4
-        GPUs: the stores ride under the mainloop), the NCCL all-gather otherwise.  x [M, K]."""
+        """Fused exchange while the GEMM is long enough to carry the stores under its mainloop (measured at 2 and 4 GPUs on
+        the large layers: fused beats GEMM + block push), block push when the exchange alone outlasts the GEMM (every tile
+        round then ends in a burst of stores the mainloop cannot hide, and the push kernel moves bytes faster than the
+        epilogue's boxes), the NCCL all-gather without symmetric buffers.  x [M, K]."""
         if self._bufs is None or x.dim() != 2 or x.shape[0] > self._bufs[0].shape[0]:
             return self.forward(x)
-        return self.forward_fused(x)
+        m, k = x.shape
+        per = self.n_total // self.world
+        t_gemm = 2.0 * m * per * k / self.GEMM_OPS_PER_S
+        t_link = m * per * self._bufs[0].element_size() * (self.world - 1) / self.LINK_BYTES_PER_S
+        return self.forward_fused(x) if t_gemm >= 0.8 * t_link else self.forward_push(x)
 
     def forward_from_host_rows(self, x_rows_host, m_total, exchange="auto"):
         """End-to-end form for inputs that start in HOST memory: every rank copies only ITS row block of x
