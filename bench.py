@@ -979,13 +979,13 @@ def run_sweep(args):
                           "config": {"workload": "config[4]: GEMM sweep, layer = activation quantise + GEMM + epilogue, bf16 in/out, "
                                                  "N column-sharded over the ranks", "iters": args.sweep_iters},
                           "correctness": {"checked": check, "worst_max_rel_vs_oracle": worst if check else None,
-                                          "bar": "bf16 output of 64 rows per point within one bf16 step (2^-8 relative to the largest value) of the "
+                                          "bar": "bf16 output of 64 rows per point within one bf16 step of the largest value (2^-7 relative to it: 8 significant bits) of the "
                                                  "CPU oracle's fp32 result rounded to bf16"},
                           "device_status": status, "points": points}), flush=True)
     if world > 1:
         dist.destroy_process_group()
-    if check and worst > 2.0 ** -8:
-        raise SystemExit(f"bench.py sweep: a point is {worst:.3e} away from the oracle (bar 2^-8)")
+    if check and worst > 2.0 ** -7:
+        raise SystemExit(f"bench.py sweep: a point is {worst:.3e} away from the oracle (bar 2^-7, one bf16 step of the largest value)")
 
 
 def run_configs(args):

@@ -181,7 +181,7 @@ struct Schedule {
     int bn;
     bool two_cta;
 };
-static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind, bool no192 = false) {
+static Schedule pick_schedule(long long M, long long N, long long K, long long batch, bool dual, int kind, bool no192 = false, int longest_unit = 1 << 30) {
     const int force_bn = overrides().bn, force_cta2 = overrides().cta2;
     const int widths[3] = {256, 192, 128};
     Schedule best{256, false};
@@ -192,6 +192,10 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
         // measured on B200: the CTA pair wins for 8-bit weights once K is long enough to amortise its longer
         // prologue; int4 expansion and short K run faster on single CTAs
         if (force_cta2 < 0 && mode == 1 && (kind == SQ_GEMM_W4A8 || K < 2048)) continue;
+        // units of one or two K stages (weight-scale groups of 128 / 256): every unit is a hand-over between the issuing
+        // thread and both CTAs' epilogues, which costs the pair more than its cheaper stages save (measured: INT8 with
+        // groups of 128 at 4608 x 9216 x 3072 takes 394 us on pairs, 284 us on single CTAs)
+        if (force_cta2 < 0 && mode == 1 && longest_unit <= 256) continue;
         const long long rows = mode ? BM2 : BM;
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;
         for (int w : widths) {
@@ -349,7 +353,8 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     const bool y_tma_ok = (reinterpret_cast<uintptr_t>(a->y_dev) & 15u) == 0 && (a->y_row_stride * oesz) % 16 == 0 &&
                           a->y_row_stride >= a->N;
     const bool want_wide = a->num_peer_outputs > 0 && y_tma_ok && overrides().bn != 192;
-    const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind, want_wide);
+    const int longest_unit = max_unit_k(a->num_segs, a->seg_bounds, a->group_size);
+    const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind, want_wide, longest_unit);
     p.peer_wide = want_wide ? 1 : 0;
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
@@ -358,7 +363,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     // short units of an integer kind: accumulators start from a magic bit pattern and are read as floats (seg_gemm_kernels.cuh);
     // the dump (tests) and peer-store variants of the epilogue use plain conversions on accumulators that start from zero
     p.all_magic = (a->kind != SQ_GEMM_W8A8_F8 && a->acc_dump_dev == nullptr && a->num_peer_outputs == 0 &&
-                   max_unit_k(a->num_segs, a->seg_bounds, a->group_size) <= 224) ? 1 : 0;
+                   longest_unit <= 224) ? 1 : 0;
     p.tiles_n = static_cast<int>((a->N + p.bn - 1) / p.bn);
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * a->batch;
 
