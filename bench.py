@@ -265,6 +265,34 @@ def split_timed(quant, gemm, steps):
     return (sum(e[0].elapsed_time(e[1]) for e in ev) / steps, sum(e[1].elapsed_time(e[2]) for e in ev) / steps)
 
 
+def graph_timed(fn, n, replays=3):
+    """Mean milliseconds per call of fn with `n` calls recorded once into a CUDA graph and the replay timed by CUDA events:
+    layers that run tens of microseconds are otherwise bound by the Python / ctypes launch path (15-40 us per call), not by
+    the GPU.  fn may rotate over operand sets: the rotation is part of what is recorded."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    cur = torch.cuda.current_stream()
+    side = torch.cuda.Stream()
+    side.wait_stream(cur)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(n):
+                fn()
+    cur.wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    del graph
+    return e0.elapsed_time(e1) / (n * replays)
+
+
 def layer_bound(M, N, K, in_bytes, out_bytes, w_bytes_per_el, dual, peaks):
     """Roofline bound of a layer step in ms: max(useful-or-issued ops / tensor peak, algorithmic bytes / HBM bandwidth)."""
     tensor = 2.0 * peaks["tensor"]
@@ -308,11 +336,20 @@ def config_entries(dev, peaks, steps=20):
                      sw_strides=f["sw_strides"], bias=b, out_dtype=xx.dtype, out=y)
             state["i"] += 1
 
+        def gemm_only():
+            gemm()
+
+        def quant_only():
+            quant()
+            state["i"] += 1
+
         def step():
             quant()
             gemm()
-        ms = timed(step, steps)
-        q_ms, g_ms = split_timed(quant, gemm, steps)
+        n = max(steps, 4 * len(fs))
+        ms = graph_timed(step, n)
+        g_ms = graph_timed(gemm_only, n)       # every xq buffer of the rotation was filled by the steps above
+        q_ms = graph_timed(quant_only, n)
         return ms, q_ms, g_ms
 
     # ---- config[0]: INT8, 4 K-segments, fp32 in / out, M=4096 K=N=1536, seed 0
@@ -406,11 +443,14 @@ def config_entries(dev, peaks, steps=20):
         def step():
             quant()
             gemm()
-        ms = timed(step, steps)
-        q_ms, g_ms = split_timed(quant, gemm, steps)
+        ms = graph_timed(step, steps)
+        q_ms, g_ms = graph_timed(quant, steps), graph_timed(gemm, steps)
         entries[name] = {"N": N, "K": K, "dual_scale": dual, "ms": ms, "tops_useful": 2.0 * M * N * K / ms / 1e9, "act_quant_ms": q_ms,
                          "kernel_ms": g_ms, "kernel_frac_of_2x_bf16": 2.0 * M * N * K * (2 if dual else 1) / g_ms / 1e9 / peak8}
         del x, wq, wq3, xq, xqn, y
+    out["timing"] = ("every entry: `steps` launches recorded once into a CUDA graph, the replay timed by CUDA events (ms = quantise + GEMM per "
+                     "forward, kernel_ms / act_quant_ms = the kernel alone, back to back); configs 0 and 1 rotate over four operand sets "
+                     "so activations and weights come from HBM")
     out["config2_w4a8_g128"] = {"workload": "config[2]: W4A8, int4 weights + bf16 group scales (g=128), bf16, M=4608, seed 2 "
                                             "(operands 50-170 MB per projection: weights partly L2-resident between steps, activations from HBM)",
                                 "kernel": "seg_gemm_kernel<W4A8>", "projections": entries,
