@@ -174,22 +174,14 @@ class ColumnShardedSegLinear:
         self._barrier()
         return full
 
-    # planning figures for forward_auto: 8-bit tensor rate a shard's GEMM reaches and the rate one GPU pushes into NVLink
-    GEMM_OPS_PER_S = 2.8e15
-    LINK_BYTES_PER_S = 0.7e12
-
     def forward_auto(self, x):
-        """Fused exchange while the GEMM is long enough to carry the stores under its mainloop (measured at 2 and 4 GPUs on
-        the large layers: fused beats GEMM + block push), block push when the exchange alone outlasts the GEMM (every tile
-        round then ends in a burst of stores the mainloop cannot hide, and the push kernel moves bytes faster than the
-        epilogue's boxes), the NCCL all-gather without symmetric buffers.  x [M, K]."""
+        """The fused exchange wherever the symmetric buffers allow it: measured the fastest of the three at 314 of 336
+        points of the GEMM sweep on 2 GPUs and 137 of 144 on 4 (also where the exchange outlasts the GEMM several times
+        over: the stores start as soon as the first tiles finish instead of after the last one); the NCCL all-gather
+        otherwise.  x [M, K]."""
         if self._bufs is None or x.dim() != 2 or x.shape[0] > self._bufs[0].shape[0]:
             return self.forward(x)
-        m, k = x.shape
-        per = self.n_total // self.world
-        t_gemm = 2.0 * m * per * k / self.GEMM_OPS_PER_S
-        t_link = m * per * self._bufs[0].element_size() * (self.world - 1) / self.LINK_BYTES_PER_S
-        return self.forward_fused(x) if t_gemm >= 0.8 * t_link else self.forward_push(x)
+        return self.forward_fused(x)
 
     def forward_from_host_rows(self, x_rows_host, m_total, exchange="auto"):
         """End-to-end form for inputs that start in HOST memory: every rank copies only ITS row block of x
