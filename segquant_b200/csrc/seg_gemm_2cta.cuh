@@ -204,7 +204,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const long long tile_step = cluster_count_x();
 
     if (warp < 4) {
-        reg_dec<kW4 ? 40 : 56>();
+        reg_dec<kW4 ? SQ_W4_CTRL : kCtrlRegs>();
         if (warp == 0) {
             // ===== TMA producer (both CTAs) =====
             int trace_it = 0; (void)trace_it;
@@ -373,7 +373,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp < 12) {
         // ===== epilogue (both CTAs): same as the one-CTA kernel on this CTA's 128 rows =====
-        reg_inc<kW4 ? 200 : 224>();
+        reg_inc<kW4 ? kEpiRegsW4 : kEpiRegs>();
         epilogue_role<KIND, DUAL, true>(p, &map_y, tmem_base, tab, smem_u32(&bar_tmem_full[0]), map_to_rank(smem_u32(&bar_tmem_empty[0]), 0),
                                         smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, first_tile, tile_step,
                                         static_cast<int>(rank), warp, lane,
@@ -382,7 +382,7 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
         // ===== int4 -> int8 expansion of this CTA's half of the weight tile (W4A8, both CTAs) =====
         if constexpr (kW4) {
-            reg_dec<72>();
+            reg_dec<SQ_W4_CVT>();
             const int ct = threadIdx.x - 384;
             int st = 0;
             uint32_t ph = 0;

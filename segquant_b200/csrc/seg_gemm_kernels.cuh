@@ -607,7 +607,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp < 4) {
         // ------------------------------------------------------------------ producer / MMA warps
         // The producer and the MMA issuer are ONE thread each (lane 0 of their warps); the other lanes wait at the end.
-        reg_dec<kW4 ? 40 : 56>();
+        reg_dec<kW4 ? SQ_W4_CTRL : kCtrlRegs>();
         if (warp == 0) {
             // ===== TMA producer =====
             int trace_it = 0; (void)trace_it;
@@ -754,7 +754,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ epilogue warps
-        reg_inc<kW4 ? 200 : 224>();
+        reg_inc<kW4 ? kEpiRegsW4 : kEpiRegs>();
         epilogue_role<KIND, DUAL, false>(p, &map_y, tmem_base, tab, smem_u32(&bar_tmem_full[0]), smem_u32(&bar_tmem_empty[0]),
                                          smem_u32(&bar_tab_full[0]), smem_u32(&bar_tab_empty[0]), abort_flag, blockIdx.x, gridDim.x, 0,
                                          warp, lane, smem_gen + kStages * C::kStageBytes + C::kTabBytes + (warp - 4) * 2048);
@@ -762,7 +762,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else {
         // ------------------------------------------------------------------ int4 -> int8 expansion warps (W4A8)
         if constexpr (kW4) {
-            reg_dec<72>();
+            reg_dec<SQ_W4_CVT>();
             const int ct = threadIdx.x - 384;  // 0..127
             uint32_t it = 0;
             bool ok = true;

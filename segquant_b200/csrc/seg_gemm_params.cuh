@@ -29,6 +29,21 @@ enum WaitCode : int { kWaitProbe = 9, kWaitEmpty = 1, kWaitFull = 2, kWaitTmemEm
 
 constexpr int BM2 = 256;  // tile rows of a CTA pair
 
+// Register allowances (setmaxnreg) of the W4A8 kernels' control warps (producer, MMA issuer, table builders) and int4
+// expansion warps; the eight epilogue warps take 200.  4 * control + 8 * 200 + 4 * expansion <= 2048.
+// setmaxnreg moves registers inside the pool the CTA was LAUNCHED with (threads x the kernel's launch allowance, 168 for
+// 384 threads and 128 for 512), not inside the SM's whole register file: a request beyond that pool is never granted and
+// the warp waits for ever.  The static_asserts below keep every role split inside the pool.
+#ifndef SQ_W4_CTRL
+#define SQ_W4_CTRL 40
+#endif
+#ifndef SQ_W4_CVT
+#define SQ_W4_CVT 72
+#endif
+constexpr int kCtrlRegs = 56, kEpiRegs = 224, kEpiRegsW4 = 200;
+static_assert(4 * kCtrlRegs + 8 * kEpiRegs <= 12 * 168, "register split of the 384-thread kernels exceeds the launch pool");
+static_assert(4 * SQ_W4_CTRL + 8 * kEpiRegsW4 + 4 * SQ_W4_CVT <= 16 * 128, "register split of the 512-thread kernels exceeds the launch pool");
+
 struct GemmParams {
     long long M, N, K;
     int batch;
