@@ -189,12 +189,19 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
     const double nst = static_cast<double>((K + BK - 1) / BK);   // 128-byte K stages per tile
     for (int mode = 0; mode < 2; ++mode) {
         if (force_cta2 >= 0 && mode != force_cta2) continue;
-        // measured on B200: the CTA pair wins for 8-bit weights once K is long enough to amortise its longer
-        // prologue; int4 expansion and short K run faster on single CTAs
-        if (force_cta2 < 0 && mode == 1 && (kind == SQ_GEMM_W4A8 || K < 2048)) continue;
+        // measured on B200: the CTA pair wins once K is long enough to amortise its longer prologue.  Below K = 2048 the
+        // two are within noise of each other in situ for 8-bit weights (8192 x 6144 x 1536 alone, operands L2-resident:
+        // 64.6 us on pairs, 71.7 us on single CTAs; the same layers inside the MMDiT step: 0.1 ms per step slower on
+        // pairs), so single CTAs stay; int4 weights gain from K = 1024 wherever there are two full rounds of pair tiles,
+        // because each CTA expands only its half of the weight tile (4608 x 9216 x 1536: 64 us against 84 us; with
+        // K = 3072: 103 us against 146 us).
+        if (force_cta2 < 0 && mode == 1 && K < 2048) {
+            const long long pair_tiles = batch * ((M + BM2 - 1) / BM2) * ((N + 255) / 256);
+            if (kind != SQ_GEMM_W4A8 || K < 1024 || pair_tiles < 2 * (kNumSMs / 2)) continue;
+        }
         // units of one or two K stages (weight-scale groups of 128 / 256): every unit is a hand-over between the issuing
-        // thread and both CTAs' epilogues, which costs the pair more than its cheaper stages save (measured: INT8 with
-        // groups of 128 at 4608 x 9216 x 3072 takes 394 us on pairs, 284 us on single CTAs)
+        // thread and both CTAs' epilogues, and the layer is bound by its epilogue either way (measured: INT8 with groups of
+        // 128 at 4608 x 9216 x 3072 takes 281-294 us on pairs, 284 us on single CTAs)
         if (force_cta2 < 0 && mode == 1 && longest_unit <= 256) continue;
         const long long rows = mode ? BM2 : BM;
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;

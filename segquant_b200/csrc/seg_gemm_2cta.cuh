@@ -49,14 +49,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
     return done;
 }
-// Bounded wait with cluster-scope acquire (pairs with arrivals made by the other CTA).
+// Bounded wait on a barrier that the other CTA of the pair also arrives at (see mbar_arrive_cluster for the semantics).
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const long long t0 = clock64();
@@ -386,12 +386,15 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int ct = threadIdx.x - 384;
             int st = 0;
             uint32_t ph = 0;
+            uint32_t it = 0; (void)it;   // stage counter of the trace stamps
             bool ok = true;
             for (long long tile = first_tile; ok && tile < p.total_tiles; tile += tile_step) {
                 for (int s = 0; ok && s < p.num_segs; ++s) {
                     const int k_beg = p.seg_bounds[s], k_end = p.seg_bounds[s + 1];
-                    for (int kb = k_beg; kb < k_end; kb += BKS) {
+                    for (int kb = k_beg; kb < k_end; kb += BKS, ++it) {
+                        SQ_CVT(0);
                         if (!mbar_wait(smem_u32(&bar_bp[st]), ph, abort_flag, kWaitFullCvt, p.wait_cycles)) { ok = false; break; }
+                        SQ_CVT(1);
                         const int left = k_end - kb;
                         const int nsub = left >= BKS ? KSUB : (left + BK - 1) / BK;
                         // packed bytes sit in the upper half of the buffer they expand into: pull every chunk into
@@ -408,7 +411,9 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 }
                             }
                         }
+                        SQ_CVT(2);
                         asm volatile("bar.sync 1, 128;" ::: "memory");   // see the one-CTA kernel: all four warps passed the same phase of bar_bp
+                        SQ_CVT(3);
 #pragma unroll
                         for (int jsub = 0; jsub < KSUB; ++jsub) {
                             if (jsub >= nsub) break;
@@ -433,9 +438,12 @@ seg_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 *reinterpret_cast<uint4*>(drow + c1 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
                             }
                         }
+                        SQ_CVT(4);
                         fence_proxy_async_smem();
+                        SQ_CVT(5);
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bar_cvt[st]), 0));
+                        SQ_CVT(6);
                         if (++st == kStages) { st = 0; ph ^= 1u; }
                     }
                 }

@@ -79,8 +79,12 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival on a barrier of this CTA or of the other CTA of the pair (cluster address).  Default semantics (release at CTA
+// scope): what the waiter consumes is tensor memory, ordered by the tcgen05 fences on both sides, or shared memory written
+// for the async proxy, ordered by the writer's fence.proxy.async; a cluster-scope release here was measured at 1100-1900
+// cycles per arrival (it was the longest step of the int4 expansion warps and of every accumulator hand-back of a pair).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
