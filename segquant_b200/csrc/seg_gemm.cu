@@ -208,6 +208,10 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
         for (int w : widths) {
             if (force_bn && w != force_bn) continue;
             if (no192 && w == 192) continue;
+            // DualScale with units of one or two K stages: only 128-column tiles leave room for two accumulator pairs in
+            // tensor memory, so that a unit's drain overlaps the next unit's MMAs (int4, groups of 128, 4608 x 3072 x 12288:
+            // 783 us against 858 us with 256-column tiles)
+            if (!force_bn && dual && longest_unit <= 256 && w > 128) continue;
             const long long tiles = batch * ((M + rows - 1) / rows) * ((N + w - 1) / w);
             const long long rounds = (tiles + slots - 1) / slots;
             // SM cycles, fitted to in-kernel timelines: a K stage costs the issuing thread a fixed ~500 cycles
