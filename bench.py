@@ -679,12 +679,14 @@ def run_ours(args):
         e2e_mode = ("SegmentLinear.forward(x, out=) fed from pinned host memory; copy-in, forward and read-back of consecutive steps "
                     "overlap on three streams (double-buffered)")
     else:
+        from segquant_b200.sharded import HostRowPipeline
+        pipe = HostRowPipeline(cs, HM, HK, torch.bfloat16, torch.bfloat16, exchange=exchange)
+
         def e2e_run(n):
-            for i in range(n):
-                y_full = cs.forward_from_host_rows(host_x[i & 1], HM, exchange=exchange)
-                host_y.copy_(y_full[o_lo:o_hi], non_blocking=True)
-        e2e_mode = ("ColumnShardedSegLinear.forward_from_host_rows: every rank copies its 1/g of the input rows from pinned host memory, "
-                    "the rows are all-gathered over NVLink, sharded forward + exchange, every rank reads back its 1/g of the output rows")
+            pipe.run(n, host_x, host_y)
+        e2e_mode = ("sharded.HostRowPipeline: every rank copies its 1/g of the input rows from pinned host memory, the rows are "
+                    "all-gathered over NVLink, sharded forward + exchange, every rank reads back its 1/g of the output rows; copy-in, "
+                    "compute and read-back of consecutive steps overlap on three streams (double-buffered)")
     e2e_steps = 1 if args.quick else args.steps
     e2e_run(1 if args.quick else 3)
     barrier()

@@ -203,3 +203,76 @@ class ColumnShardedSegLinear:
         x = x_full[:m_total]
         fn = {"auto": self.forward_auto, "push": self.forward_push, "fused": self.forward_fused, "nccl": self.forward}[exchange]
         return fn(x)
+
+
+class HostRowPipeline:
+    """End-to-end driver of a column-sharded layer for inputs that live in HOST memory, one step in flight per stage.
+
+    Per step every rank copies ITS row block of x from pinned host memory (copy stream), all-gathers the blocks over NVLink
+    and runs the sharded forward (compute stream), and reads its row block of the result back into pinned host memory
+    (read-back stream); consecutive steps overlap on the three streams, with two device input buffers used alternately.
+    The rank's output rows are first copied to a private device buffer ON THE COMPUTE STREAM: the layer's symmetric result
+    buffers may be overwritten by peers as soon as this rank has issued its next forward (see the module docstring), so
+    nothing outside the compute stream may read them.  Without CUDA (gloo tests) the same steps run one after the other."""
+
+    def __init__(self, layer, m_total, k, in_dtype, out_dtype, exchange="auto"):
+        self.layer, self.m_total, self.exchange = layer, m_total, exchange
+        dev = layer._device()
+        self.dev, self.cuda = dev, dev.type == "cuda"
+        w, r = layer.world, layer.rank
+        self.per = (m_total + w - 1) // w
+        self.lo, self.hi = row_range(m_total, w, r)
+        self.x = [torch.empty((self.per * w, k), dtype=in_dtype, device=dev) for _ in range(2)]
+        self.y_rows = [torch.empty((self.hi - self.lo, layer.n_total), dtype=out_dtype, device=dev) for _ in range(2)]
+        if self.cuda:
+            self.s_in, self.s_cmp, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            self.ev_in, self.ev_cmp, self.ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+
+    def _compute(self, b):
+        lay = self.layer
+        xf = self.x[b]
+        mine = xf[lay.rank * self.per:(lay.rank + 1) * self.per]
+        if dist.get_backend(lay.group) == "nccl":
+            dist.all_gather_into_tensor(xf, mine, group=lay.group)
+        else:
+            parts = [torch.empty_like(mine) for _ in range(lay.world)]
+            dist.all_gather(parts, mine.contiguous(), group=lay.group)
+            xf.copy_(torch.cat(parts))
+        fn = {"auto": lay.forward_auto, "push": lay.forward_push, "fused": lay.forward_fused, "nccl": lay.forward}[self.exchange]
+        y = fn(xf[:self.m_total])
+        self.y_rows[b].copy_(y[self.lo:self.hi])
+
+    def step(self, i, x_rows_host, y_rows_host):
+        """Enqueue step i: x_rows_host = this rank's rows of x (pinned), y_rows_host receives this rank's rows of y."""
+        b = i & 1
+        if not self.cuda:
+            self.x[b][self.lo:self.hi].copy_(x_rows_host)
+            self._compute(b)
+            y_rows_host.copy_(self.y_rows[b])
+            return
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(self.ev_cmp[b])            # the forward two steps ago has consumed x[b]
+            self.x[b][self.lo:self.hi].copy_(x_rows_host, non_blocking=True)
+            self.ev_in[b].record(self.s_in)
+        with torch.cuda.stream(self.s_cmp):
+            self.s_cmp.wait_event(self.ev_in[b])
+            self.s_cmp.wait_event(self.ev_out[b])           # y_rows[b] has been read back
+            self._compute(b)
+            self.ev_cmp[b].record(self.s_cmp)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_cmp[b])
+            y_rows_host.copy_(self.y_rows[b], non_blocking=True)
+            self.ev_out[b].record(self.s_out)
+
+    def run(self, n, x_rows_host, y_rows_host):
+        """n steps from the two alternating pinned inputs x_rows_host[0 / 1]; returns after everything is enqueued and the
+        caller's current stream has been made to wait for all three streams."""
+        if self.cuda:
+            cur = torch.cuda.current_stream(self.dev)
+            for s in (self.s_in, self.s_cmp, self.s_out):
+                s.wait_stream(cur)
+        for i in range(n):
+            self.step(i, x_rows_host[i & 1], y_rows_host)
+        if self.cuda:
+            for s in (self.s_in, self.s_cmp, self.s_out):
+                cur.wait_stream(s)

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from segquant_b200.sharded import ColumnShardedSegLinear, all_gather_slices, assemble, row_range, shard_range
+from segquant_b200.sharded import ColumnShardedSegLinear, HostRowPipeline, all_gather_slices, assemble, row_range, shard_range
 
 
 def test_shard_range_and_assemble():
@@ -55,6 +55,14 @@ def _worker(rank, world, port, ret):
         r0, r1 = row_range(5, world, rank)
         y2 = layer.forward_from_host_rows(x2[r0:r1].clone(), 5, exchange="nccl")
         ok = ok and y2.shape == (5, 12) and torch.allclose(y2, x2 @ w.t() + b, atol=1e-6)
+        # the same through the step pipeline (on CPU its three stages run one after the other)
+        pipe = HostRowPipeline(layer, 5, 16, torch.float32, torch.float32, exchange="nccl")
+        y_rows = torch.empty((r1 - r0, 12))
+        x3 = torch.randn(5, 16, generator=g)
+        pipe.run(3, [x2[r0:r1].clone(), x3[r0:r1].clone()], y_rows)     # steps 0, 1, 2 -> the last one used x2 again
+        ok = ok and torch.allclose(y_rows, (x2 @ w.t() + b)[r0:r1], atol=1e-6)
+        pipe.run(2, [x2[r0:r1].clone(), x3[r0:r1].clone()], y_rows)
+        ok = ok and torch.allclose(y_rows, (x3 @ w.t() + b)[r0:r1], atol=1e-6)
         with pytest.raises(RuntimeError):
             layer.forward_push(x2)                                  # symmetric buffers were never set up
         buf = all_gather_slices(torch.full((2, 3), float(rank)))
