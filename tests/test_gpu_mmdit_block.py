@@ -81,7 +81,7 @@ def test_joint_block_real_size_against_fake_quant_restatement(native_lib):
     c_act = Fn.silu(torch.randn(B, H, generator=g)).to(torch.bfloat16).to(DEV)
 
     def run(call, norm_call):
-        i2, t2, pend_i, pend_t = blk.forward(img, txt, c_act, call, norm_call)
+        i2, t2, pend_i, pend_t, _ = blk.forward(img, txt, c_act, call, norm_call)
         return _gated_add(i2, *pend_i).float(), _gated_add(t2, *pend_t).float()      # apply the residuals the block left pending
 
     with torch.no_grad():
