@@ -713,6 +713,11 @@ static void launch_norm(const ActQuantParams& p, bool dual, const void* shift, c
     const long long rows = p.batch * p.M;
     int block = 256;
     int grid = grid_for(rows);
+    const long long per_lane_words = (p.K / Unit<T>::E + 31) / 32;
+    // as many CTAs as are resident at once (3 or 4 per SM, see the kernel's launch bounds): each walks several 8-row items
+    // and fills its shared-memory table once per batch sample instead of once per item
+    const int resident = kNumSMs * ((per_lane_words <= 6 && res.y == nullptr) ? 4 : 3);
+    if (grid > resident) grid = resident;
     if (rows <= static_cast<long long>(kNumSMs) * 32) {
         block = 64;
         grid = static_cast<int>((rows + 1) / 2 < 1 ? 1 : (rows + 1) / 2);
