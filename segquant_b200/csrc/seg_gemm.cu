@@ -202,7 +202,12 @@ static Schedule pick_schedule(long long M, long long N, long long K, long long b
         // units of one or two K stages (weight-scale groups of 128 / 256): every unit is a hand-over between the issuing
         // thread and both CTAs' epilogues, and the layer is bound by its epilogue either way (measured: INT8 with groups of
         // 128 at 4608 x 9216 x 3072 takes 281-294 us on pairs, 284 us on single CTAs)
-        if (force_cta2 < 0 && mode == 1 && longest_unit <= 256) continue;
+        // int4 weights are the exception: with 128-byte K stages (launch_2cta) a pair's CTAs expand half a tile each, and
+        // the layer is 3-5 % faster than on single CTAs (groups of 128: 297 against 311 us at 4608 x 9216 x 3072, DualScale
+        // 4608 x 3072 x 12288 759 against 783 us)
+        const bool w4_short = kind == SQ_GEMM_W4A8 && longest_unit <= 256;
+        if (force_cta2 < 0 && mode == 1 && longest_unit <= 256 && !w4_short) continue;
+        if (force_cta2 < 0 && mode == 0 && w4_short) continue;
         const long long rows = mode ? BM2 : BM;
         const long long slots = mode ? kNumSMs / 2 : kNumSMs;
         for (int w : widths) {
@@ -367,6 +372,7 @@ int gemm(const sq_gemm_args* a, cudaStream_t st) {
     const int longest_unit = max_unit_k(a->num_segs, a->seg_bounds, a->group_size);
     const Schedule sched = pick_schedule(a->M, a->N, a->K, a->batch, dual, a->kind, want_wide, longest_unit);
     p.peer_wide = want_wide ? 1 : 0;
+    p.short_units = longest_unit <= 256 ? 1 : 0;
     const int tile_rows = sched.two_cta ? BM2 : BM;
     p.tiles_m = static_cast<int>((a->M + tile_rows - 1) / tile_rows);
     p.bn = sched.bn;

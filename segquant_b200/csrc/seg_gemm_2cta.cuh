@@ -512,6 +512,7 @@ template <int KIND, bool DUAL>
 static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& man, const CUtensorMap& mw, const OutMaps& my, const GemmParams& p, cudaStream_t st) {
     constexpr bool can2 = Cfg2<KIND, DUAL, 2>::kStagesRaw >= 2;
     bool want2 = can2;
+    if (p.short_units) want2 = false;   // a unit per stage: 256-byte stages would put a unit boundary inside every stage
     if (forced_ksub() != 0) want2 = can2 && forced_ksub() != 1;
     if constexpr (can2) {
         if (want2) return launch_2cta_k<KIND, DUAL, 2>(ma, man, mw, my, p, st);

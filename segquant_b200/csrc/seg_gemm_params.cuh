@@ -76,6 +76,7 @@ struct GemmParams {
     void* peer_y[SQ_MAX_PEERS];
     long long peer_rs, peer_co;
     int peer_wide;            // fused all-gather with [16 rows x 128 bytes] boxes (see store_output) instead of [32 rows x 16 columns]
+    int short_units;  // every accumulation unit is one or two K stages long (weight-scale groups of 128 / 256): pairs use 128-byte K stages
     int all_magic;  // integer kind, every accumulation unit has K <= 224 (|sum| < 2^22), no dump / peer stores: accumulators start from kMagicBits
     int dual_db;  // DualScale with bn <= 128: four TMEM buffers (pos/neg x 2), epilogue overlaps the next tile
     long long wait_cycles;  // SM cycles after which a bounded wait gives up (default 4e9, about 2 s)
