@@ -100,6 +100,24 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return done;
 }
+// The same test with a suspend-time hint (nanoseconds): the thread may sleep in hardware until the phase completes instead
+// of returning early to poll again.  Used by the MMA issuer of the one-CTA kernel with 8-bit weights: that kernel runs at
+// its shared-memory roofline, every poll of a barrier is one more shared-memory access, and with the hint its K = 1536
+// layers are 4-6 % faster when run back to back (8192 x 6144 x 1536: 71.2 -> 67.9 us; inside the MMDiT step, among other
+// kernels, the difference is within noise).  Measured and left alone: the same hint on the producer's,
+// table builders' and epilogue's waits (no change), on the int4 expansion path (3 % slower) and on the pair kernel's
+// issuer (1 % slower on the headline layer).
+__device__ __forceinline__ uint32_t mbar_try_wait_relaxed(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(20000)
+        : "memory");
+    return done;
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -108,12 +126,13 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Bounded wait: gives up after `limit` SM cycles (GemmParams::wait_cycles, 4e9 = about 2 s unless the host changed
 // it), or as soon as another role has raised the abort flag.  (Backing off with nanosleep was measured: no gain for the epilogue, slower hand-offs.)  The timeout uses the SM-local cycle counter: reading %globaltimer costs microseconds.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit,
+                                          bool relaxed = false) {
+    if (relaxed ? mbar_try_wait_relaxed(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
 #pragma unroll 1
     for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (relaxed ? mbar_try_wait_relaxed(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((it & 1023u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > limit) {
@@ -671,7 +690,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         uint32_t d_pos = 0, d_neg = 0;
                         for (int kb = k_beg; ok && kb < k_end; kb += BK) {
                             SQ_FINE(0);
-                            if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles)) { ok = false; break; }
+                            if (!mbar_wait(smem_u32(&bar_full[st]), ph, abort_flag, kWaitFull, p.wait_cycles, !kW4)) { ok = false; break; }
                             if (kW4) {
                                 if (!mbar_wait(smem_u32(&bar_cvt[st]), ph, abort_flag, kWaitCvt, p.wait_cycles)) { ok = false; break; }
                             }
@@ -689,7 +708,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 if (kb != k_beg) umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
                                 const uint32_t buf = one_buf ? 0u : (au & 1u);
                                 const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles, !kW4)) { ok = false; break; }
                                 tc_fence_after();
                                 cur_buf = buf;
                                 d_pos = tmem_base + buf * BN;
@@ -721,7 +740,7 @@ seg_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                         umma_commit(smem_u32(&bar_tmem_full[cur_buf]));
                                         const uint32_t buf = one_buf ? 0u : (au & 1u);
                                         const uint32_t tph = one_buf ? (au & 1u) : ((au >> 1) & 1u);
-                                        if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles)) { ok = false; break; }
+                                        if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), tph ^ 1u, abort_flag, kWaitTmemEmpty, p.wait_cycles, !kW4)) { ok = false; break; }
                                         tc_fence_after();
                                         cur_buf = buf;
                                         d_pos = tmem_base + buf * BN;
