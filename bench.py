@@ -420,6 +420,7 @@ def config_entries(dev, peaks, steps=20):
         sw16 = (7.0 / w.float().view(N, K // G, G).abs().amax(-1)).to(torch.bfloat16).contiguous()
         wq = torch.empty(N * K // 2, dtype=torch.uint8, device=dev)
         ops.quantize_weight(w, wq, sw16.float().contiguous(), L.SQ_Q_INT4, group_size=G)
+        sw16 = sw16.t().contiguous()       # group-major (K / G, N) for the GEMM: a unit's scales are contiguous
         wq3 = wq.view(1, N, K // 2)
         xf = x.float()
         if dual:
@@ -437,7 +438,7 @@ def config_entries(dev, peaks, steps=20):
             ops.quantize_act(x, bounds, sx, sxn, L.SQ_Q_INT8, out=xq, out_neg=xqn)
 
         def gemm():
-            ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, sx, sw16, xq_neg=xqn, sx_neg=sxn, group_size=G, sw_strides=(0, 0, 1, K // G),
+            ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, sx, sw16, xq_neg=xqn, sx_neg=sxn, group_size=G, sw_strides=(0, 0, N, 1),
                      out_dtype=torch.bfloat16, out=y)
 
         def step():
@@ -904,10 +905,12 @@ def run_sweep(args):
         for name, ktype, wkind, group in modes:
             qmax = {L.SQ_Q_INT8: 127.0, L.SQ_Q_E4M3: 448.0, L.SQ_Q_INT4: 7.0}[wkind]
             if group:
-                sw = (qmax / w.float().view(n_loc, K // group, group).abs().amax(-1)).contiguous()
+                sw_ng = (qmax / w.float().view(n_loc, K // group, group).abs().amax(-1)).contiguous()
                 wq = torch.empty(n_loc * K // 2, dtype=torch.uint8, device=dev)
-                ops.quantize_weight(w, wq, sw, wkind, group_size=group)
-                wq3, strides = wq.view(1, n_loc, K // 2), (0, 0, 1, K // group)
+                ops.quantize_weight(w, wq, sw_ng, wkind, group_size=group)
+                # the GEMM takes the group scales group-major, (K / g, N): one accumulation unit's scales are then contiguous
+                sw = sw_ng.t().contiguous()
+                wq3, strides = wq.view(1, n_loc, K // 2), (0, 0, n_loc, 1)
             else:
                 sw = (qmax / w.float().abs().amax(-1)).contiguous()
                 kb = K // 2 if wkind == L.SQ_Q_INT4 else K          # bytes per weight row
@@ -939,7 +942,7 @@ def run_sweep(args):
                         rows = torch.linspace(0, M - 1, 64).long().unique()
                         xr = x[rows].float().cpu().numpy()
                         xq_ref = O.quantize_act(xr, bounds, sx.cpu().numpy(), out_kind=oq[name])
-                        sw_o = sw.t().contiguous().cpu().numpy() if group else sw.cpu().numpy()
+                        sw_o = sw.cpu().numpy()            # group-major (K / g, N) is also the oracle's layout
                         y_ref = O.seg_gemm(okind[name], xq_ref, wq.cpu().numpy() if wkind == L.SQ_Q_INT4 else wq.view(n_loc, K).cpu().numpy(),
                                            bounds, sx.cpu().numpy(), sw_o, group_size=group)
                         want = torch.from_numpy(y_ref).to(torch.bfloat16).float().numpy()

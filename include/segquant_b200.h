@@ -235,7 +235,10 @@ int sq_unpack_int4(const void* packed_dev, void* out_dev, int64_t numel, sq_stre
  *   sx  = sx_dev [b*sx_batch_stride + s*sx_seg_stride + m*sx_row_stride]
  *   sw  = sw_dev [b*sw_batch_stride + s*sw_seg_stride + g*sw_group_stride + n*sw_col_stride]
  * with s the segment and g = k / group_size the weight group of the unit.  Strides may be 0
- * (broadcast).  sw_dev is fp32, or bf16 when sw_is_bf16 != 0.
+ * (broadcast).  sw_dev is fp32, or bf16 when sw_is_bf16 != 0.  Any layout the strides can describe is accepted; with
+ * weight groups the group-major one, (K / group_size, N) with sw_col_stride = 1 and sw_group_stride = N, is the fast one:
+ * the kernel builds one table of N-tile scales per unit, and in the (N, K / group_size) layout those are strided by the
+ * group count (measured: int4 weights, groups of 128, 16384 x 3072 x 12288: 1.28 ms group-major, 1.70 ms column-major).
  *
  * Alignment: K and every segment bound a multiple of 32 (the reference needs K % 16 for
  * 8-bit and K % 32 for int4: real_gemm.cu:199-203); group_size a multiple of 32; operand row and

@@ -95,7 +95,9 @@ class BaseOptimizer:
             bounds = wm.bounds
             S = self.chunks
             if group:
-                sw_t, strides = sw[0].contiguous(), (0, 0, 1, K // group)     # (N, G)
+                # group-major copy (G, N): the scales of one accumulation unit are then 1 KB contiguous for the GEMM's table
+                # builders instead of N values strided by the group count (which costs layers with many groups a third)
+                sw_t, strides = sw[0].t().contiguous(), (0, 0, N, 1)
             elif sw.numel() == S:
                 sw_t, strides = sw.reshape(S).contiguous(), (0, 1, 0, 0)      # one scalar per segment
             else:
@@ -105,7 +107,7 @@ class BaseOptimizer:
             bounds = [0, K]
             S = self.chunks
             if group:
-                sw_t, strides = sw.reshape(N, K // group).contiguous(), (0, 0, 1, K // group)
+                sw_t, strides = sw.reshape(N, K // group).t().contiguous(), (0, 0, N, 1)   # group-major, see above
             elif sw.numel() == S:
                 sw_t, strides = sw.reshape(S).repeat_interleave(N // S).contiguous(), (0, 0, 0, 1)
             else:
