@@ -420,7 +420,10 @@ def config_entries(dev, peaks, steps=20):
         sw16 = (7.0 / w.float().view(N, K // G, G).abs().amax(-1)).to(torch.bfloat16).contiguous()
         wq = torch.empty(N * K // 2, dtype=torch.uint8, device=dev)
         ops.quantize_weight(w, wq, sw16.float().contiguous(), L.SQ_Q_INT4, group_size=G)
-        sw16 = sw16.t().contiguous()       # group-major (K / G, N) for the GEMM: a unit's scales are contiguous
+        sw_strides = (0, 0, 1, K // G)     # (N, K / G): what DualScale layers measure fastest with
+        if not dual:
+            sw16 = sw16.t().contiguous()   # group-major (K / G, N): a unit's scales are contiguous for the table builders
+            sw_strides = (0, 0, N, 1)
         wq3 = wq.view(1, N, K // 2)
         xf = x.float()
         if dual:
@@ -438,7 +441,7 @@ def config_entries(dev, peaks, steps=20):
             ops.quantize_act(x, bounds, sx, sxn, L.SQ_Q_INT8, out=xq, out_neg=xqn)
 
         def gemm():
-            ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, sx, sw16, xq_neg=xqn, sx_neg=sxn, group_size=G, sw_strides=(0, 0, N, 1),
+            ops.gemm(L.SQ_GEMM_W4A8, xq, wq3, N, bounds, sx, sw16, xq_neg=xqn, sx_neg=sxn, group_size=G, sw_strides=sw_strides,
                      out_dtype=torch.bfloat16, out=y)
 
         def step():

@@ -96,8 +96,13 @@ class BaseOptimizer:
             S = self.chunks
             if group:
                 # group-major copy (G, N): the scales of one accumulation unit are then 1 KB contiguous for the GEMM's table
-                # builders instead of N values strided by the group count (which costs layers with many groups a third)
-                sw_t, strides = sw[0].t().contiguous(), (0, 0, N, 1)
+                # builders instead of N values strided by the group count (which costs layers with many groups a third).
+                # DualScale layers keep (N, G): their 128-column tiles re-use each 32-byte sector of a column's scales for
+                # the following units, and measure 8 % faster that way (int4, 4608 x 3072 x 12288: 788 against 854 us).
+                if self.dual_scale:
+                    sw_t, strides = sw[0].contiguous(), (0, 0, 1, K // group)
+                else:
+                    sw_t, strides = sw[0].t().contiguous(), (0, 0, N, 1)
             elif sw.numel() == S:
                 sw_t, strides = sw.reshape(S).contiguous(), (0, 1, 0, 0)      # one scalar per segment
             else:
@@ -107,7 +112,10 @@ class BaseOptimizer:
             bounds = [0, K]
             S = self.chunks
             if group:
-                sw_t, strides = sw.reshape(N, K // group).t().contiguous(), (0, 0, N, 1)   # group-major, see above
+                if self.dual_scale:
+                    sw_t, strides = sw.reshape(N, K // group).contiguous(), (0, 0, 1, K // group)
+                else:
+                    sw_t, strides = sw.reshape(N, K // group).t().contiguous(), (0, 0, N, 1)   # group-major, see above
             elif sw.numel() == S:
                 sw_t, strides = sw.reshape(S).repeat_interleave(N // S).contiguous(), (0, 0, 0, 1)
             else:
