@@ -175,7 +175,7 @@ class ColumnShardedSegLinear:
         return full
 
     def forward_auto(self, x):
-        """The fused exchange wherever the symmetric buffers allow it: measured the fastest of the three at 314 of 336
+        """The fused exchange wherever the symmetric buffers allow it: measured the fastest of the three at 325 of 336
         points of the GEMM sweep on 2 GPUs and 137 of 144 on 4 (also where the exchange outlasts the GEMM several times
         over: the stores start as soon as the first tiles finish instead of after the last one); the NCCL all-gather
         otherwise.  x [M, K]."""
