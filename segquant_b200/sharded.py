@@ -176,7 +176,7 @@ class ColumnShardedSegLinear:
 
     def forward_auto(self, x):
         """The fused exchange wherever the symmetric buffers allow it: measured the fastest of the three at 325 of 336
-        points of the GEMM sweep on 2 GPUs and 137 of 144 on 4 (also where the exchange outlasts the GEMM several times
+        points of the GEMM sweep on 2 GPUs and 138 of 144 on 4 (also where the exchange outlasts the GEMM several times
         over: the stores start as soon as the first tiles finish instead of after the last one); the NCCL all-gather
         otherwise.  x [M, K]."""
         if self._bufs is None or x.dim() != 2 or x.shape[0] > self._bufs[0].shape[0]:
